@@ -1,0 +1,157 @@
+/*
+ * h3attn — C ABI of the B200 (sm_100a) attention path for the Pika H3 Flex joint video+audio DiT.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, and returns an int32 status
+ * (0 = H3A_OK, negative = error; h3a_status_string() names it).  Nothing throws or aborts across the
+ * boundary.  Unless a comment says otherwise the library allocates nothing on the device, keeps no
+ * pointer after it returns, and is stream-ordered and asynchronous: the caller owns every buffer,
+ * the workspace and the status word, and may call from several host threads on different streams.
+ *
+ * What each entry point replaces in the reference project (Pika-Labs/Pika-H3-Flex): the reference
+ * runs its DiT through `self.model(**model_inputs)` (src/pika_h3/core/wrapper.py:248) with the kwargs
+ * assembled at src/pika_h3/core/wrapper.py:192-204; the per-block attention between the
+ * `to_q/to_k/to_v` and `to_out.0` projections (module names fixed by src/pika_h3/core/loader.py:9)
+ * lives in the un-vendored `diffusers` build pinned at pyproject.toml:12 (file
+ * models/transformers/transformer_minimax_h3.py, identity pinned at src/pika_h3/runtime.py:9).
+ * The functions below are what a binding for that per-block attention calls.
+ */
+#ifndef H3ATTN_H_
+#define H3ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define H3A_VERSION_MAJOR 0
+#define H3A_VERSION_MINOR 1
+
+/* status codes */
+enum {
+  H3A_OK = 0,
+  H3A_ERR_ARG = -1,     /* null pointer, bad enum, bad flag */
+  H3A_ERR_ALIGN = -2,   /* pointer not 16-byte aligned, stride not a multiple of 16 bytes */
+  H3A_ERR_SHAPE = -3,   /* head dim != 128, batch != 1, empty or oversized extent */
+  H3A_ERR_ARCH = -4,    /* current device is not compute capability 10.x */
+  H3A_ERR_LAUNCH = -5,  /* CUDA runtime / driver call failed */
+  H3A_ERR_TIMEOUT = -6, /* a bounded device-side wait ran out (read back from the status word) */
+  H3A_ERR_WORKSPACE = -7, /* workspace missing or too small */
+  H3A_ERR_DRIVER = -8   /* driver entry point for tensor-map encoding not found */
+};
+
+/* attention modes */
+enum {
+  H3A_MODE_DENSE_BF16 = 0,   /* Q, K, V bf16 */
+  H3A_MODE_FP8_QK = 1,       /* Q, K e4m3 with per-(head, 128-token) fp32 scales; V bf16 */
+  H3A_MODE_BLOCK_SPARSE = 2  /* bf16, only the 128x128 key tiles listed in the CSR block index */
+};
+
+/* rotary pair conventions */
+enum {
+  H3A_ROPE_INTERLEAVED = 0, /* pair j = dims (2j, 2j+1) */
+  H3A_ROPE_HALF = 1         /* pair j = dims (j, j + 64) */
+};
+
+/* flags for h3a_prep_params.flags */
+#define H3A_PREP_FP8 1u /* write e4m3 Q/K and per-(head, 128-token) scales instead of bf16 */
+
+/*
+ * Forward attention  O = softmax(Q K^T * softmax_scale) V, non-causal, one document (batch 1, as the
+ * reference: src/pika_h3/core/wrapper.py:231-232).
+ * Tensors are addressed as x[l * stride_l + h * stride_h + c], c in [0,128) contiguous; strides are in
+ * ELEMENTS of that tensor's type, so [L,H,128] and [H,L,128] (and Ulysses views of either) need no copy.
+ * Lq may differ from Lk (cross-attention to a short text sequence).
+ */
+typedef struct h3a_attn_params {
+  const void* q;          /* bf16, or e4m3 bytes in FP8_QK mode */
+  const void* k;          /* bf16, or e4m3 bytes in FP8_QK mode */
+  const void* v;          /* bf16 */
+  void* o;                /* bf16 out */
+  int64_t q_stride_l, q_stride_h;
+  int64_t k_stride_l, k_stride_h;
+  int64_t v_stride_l, v_stride_h;
+  int64_t o_stride_l, o_stride_h;
+  int32_t Lq, Lk, H, d;   /* d must be 128 */
+  int32_t B;              /* must be 1 */
+  int32_t mode;           /* H3A_MODE_* */
+  float softmax_scale;    /* <= 0 selects 1/sqrt(d) */
+  const float* q_scale;   /* FP8_QK: [H, ceil(Lq/128)] fp32, else NULL */
+  const float* k_scale;   /* FP8_QK: [H, ceil(Lk/128)] fp32, else NULL */
+  const int32_t* row_ptr; /* BLOCK_SPARSE: [ceil(Lq/128)+1] device int32, else NULL */
+  const int32_t* col_idx; /* BLOCK_SPARSE: [nnz] device int32, ascending inside each row */
+  int32_t nnz;            /* BLOCK_SPARSE: number of kept tiles (host value of row_ptr[last]) */
+  float* lse;             /* optional [H, Lq] fp32 natural-log-sum-exp out, or NULL */
+  void* workspace;        /* device scratch of h3a_attn_workspace_bytes() bytes (BLOCK_SPARSE only) */
+  size_t workspace_bytes;
+  int32_t* status_word;   /* optional device int32; a kernel that gives up a bounded wait writes a
+                             non-zero code here and returns; must be 0 on entry */
+  int64_t wait_limit_ns;  /* bound for each device-side wait; <= 0 selects 2 s */
+} h3a_attn_params;
+
+/*
+ * Q/K preparation: per-head RMSNorm over d=128 (fp32 math), then rotation by a (cos,sin) table.
+ * Replaces the norm + rotary step that the reference's DiT applies to to_q/to_k outputs before
+ * attention (in the un-vendored model file; positions come from src/pika_h3/core/packing.py:126-133).
+ * Input  x[l*in_stride_l + h*in_stride_h + c] bf16.
+ * Output bf16 [H, L, 128] head-major contiguous, or with H3A_PREP_FP8 e4m3 [H, L, 128] bytes plus
+ * scales [H, ceil(L/128)] fp32 (scale = absmax/448 of the block, 1 for an all-zero block).
+ */
+typedef struct h3a_prep_params {
+  const void* q_in;  const void* k_in;     /* bf16; either may be NULL to skip that tensor */
+  void* q_out;       void* k_out;
+  float* q_scale;    float* k_scale;       /* H3A_PREP_FP8 only */
+  int64_t q_stride_l, q_stride_h, k_stride_l, k_stride_h; /* elements */
+  int32_t Lq, Lk, H, d;                    /* d must be 128 */
+  const float* q_rope;  const float* k_rope; /* [L, 64, 2] fp32 (cos, sin) per token and pair, or NULL = no rotation */
+  const float* q_weight; const float* k_weight; /* [128] fp32 RMSNorm weights, or NULL = ones */
+  float eps;                               /* <= 0 selects 1e-6 */
+  int32_t rope_mode;                       /* H3A_ROPE_* */
+  uint32_t flags;                          /* H3A_PREP_* */
+} h3a_prep_params;
+
+/* Library version. */
+int32_t h3a_version(int32_t* major, int32_t* minor);
+
+/* Human-readable name of a status code (static storage). */
+const char* h3a_status_string(int32_t status);
+
+/* Bytes of device scratch h3a_attn_fwd needs for these params (0 for the dense modes). */
+int32_t h3a_attn_workspace_bytes(const h3a_attn_params* p, size_t* bytes);
+
+/* Launch the attention forward on `stream` (a cudaStream_t passed as void*). */
+int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream);
+
+/* Launch the Q/K preparation on `stream`. */
+int32_t h3a_qk_prep(const h3a_prep_params* p, void* stream);
+
+/*
+ * Build the (cos, sin) table [L, 64, 2] fp32 on the device from a float position grid pos[L,3]
+ * (device fp32; the reference builds this grid on the host in float64, src/pika_h3/core/packing.py:166,
+ * and moves it to the device each forward, src/pika_h3/core/wrapper.py:164-166).
+ * Head-dim split over (t,h,w) is split[0..2] (sum 128, each even); pair j of axis a turns by
+ * pos[:,a] * theta^(-2j/split[a]).
+ */
+int32_t h3a_rope_table(const float* pos, int32_t L, const int32_t split[3], float theta, float* table, void* stream);
+
+/*
+ * Host-side block-index builder for the spatiotemporal-neighbourhood mask over 128x128 tiles.
+ * Token order: n_audio audio tokens, then a (T,Hg,Wg) video grid frame-major / row-major
+ * (src/pika_h3/core/packing.py:49-54).  A video-video tile is kept when some query token of the row
+ * tile and some key token of the column tile differ by at most (wt,wh,ww) on the three axes; every
+ * tile holding audio keys is kept; row tiles holding audio queries keep every column.
+ * Two-call protocol: with col_idx == NULL only *nnz is written; otherwise row_ptr[nqb+1] and
+ * col_idx[*nnz] (host memory, capacity passed in *nnz) are filled, columns ascending.
+ */
+int32_t h3a_build_block_index(int32_t T, int32_t Hg, int32_t Wg, int32_t n_audio,
+                              int32_t wt, int32_t wh, int32_t ww,
+                              int32_t* row_ptr, int32_t* col_idx, int64_t* nnz);
+
+/* Copy the device status word to the host after synchronising `stream`; maps non-zero to H3A_ERR_TIMEOUT. */
+int32_t h3a_read_device_status(const int32_t* status_word, void* stream, int32_t* raw);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* H3ATTN_H_ */

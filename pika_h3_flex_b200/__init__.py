@@ -1,0 +1,28 @@
+"""B200-native (sm_100a) attention path for the Pika H3 Flex joint video+audio DiT.
+
+Python here is host-side plumbing over ``libh3attn.so`` (hand-written CUDA behind a C ABI, see
+``include/h3attn.h``); there is no CPU or library fallback.
+"""
+from . import _lib
+from ._lib import (
+    MODE_BLOCK_SPARSE,
+    MODE_DENSE_BF16,
+    MODE_FP8_QK,
+    H3AError,
+)
+from .ops import (
+    BlockIndex,
+    attn_fwd,
+    build_block_index,
+    joint_attention,
+    qk_prep,
+    read_status,
+    rope_table,
+    rope_table_from_cos_sin,
+)
+
+__all__ = [
+    "_lib", "H3AError", "MODE_DENSE_BF16", "MODE_FP8_QK", "MODE_BLOCK_SPARSE",
+    "BlockIndex", "attn_fwd", "build_block_index", "joint_attention", "qk_prep",
+    "read_status", "rope_table", "rope_table_from_cos_sin",
+]

@@ -1,0 +1,470 @@
+// Flash-style forward attention for sm_100a: tcgen05 MMAs with S/P/O accumulators in TMEM, K/V tiles
+// staged by TMA through a multi-buffered shared-memory ring, warp-specialised roles.
+//
+// One CTA owns a PAIR of 128-row query tiles of one head (two "streams") and walks the key tiles:
+//   warp 8   producer : TMA loads of Q (once) and of K_j, V_j into a ring of 32 KB stages
+//   warp 9   issuer   : one thread issues  S_t = Q_t K_j^T  (SS MMA) and  O_t += P_t V_j  (TS MMA, P read
+//                       from TMEM); tcgen05.commit signals mbarriers
+//   warps 0-3 / 4-7   : softmax of stream 0 / 1, one query row per thread (TMEM lane == row): online
+//                       max / exp2 / sum, P written back over S as packed bf16, lazy rescale of O
+//                       (only when the running max grows by more than 2^8), final 1/l and store.
+// The two streams ping-pong so that the tensor pipe works on one stream while the other is in softmax.
+// K_j and V_j are fetched once per 256 query rows.
+//
+// TMEM (512 columns x 128 lanes, fp32):  [0,128) S0/P0   [128,256) S1/P1   [256,384) O0   [384,512) O1
+//
+// Every wait on an mbarrier is bounded: when the time limit runs out the CTA records a code in the
+// caller's status word, raises a CTA-wide abort flag, lets copies in flight land, frees TMEM and returns.
+#pragma once
+#include "ptx.cuh"
+
+namespace h3a {
+
+constexpr int kTile = 128;
+constexpr int kHeadDim = 128;
+constexpr int kStages = 5;
+constexpr int kStageBytes = 32768;
+constexpr int kQTileBytes = 32768;
+constexpr int kHalfBytes = 16384;  // one [128 rows][128 bytes] swizzled box
+constexpr int kAttnThreads = 320;
+constexpr int kProducerWarp = 8;
+constexpr int kIssuerWarp = 9;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct AttnBars {
+  uint64_t kv_full[kStages];
+  uint64_t kv_empty[kStages];
+  uint64_t q_full;
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t o_full[2];
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+  uint32_t early_exit;
+};
+
+constexpr int kAttnSmemBytes = 2 * kQTileBytes + kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+static_assert(sizeof(AttnBars) <= 256, "barrier block too large");
+static_assert(kAttnSmemBytes <= 232448, "shared memory budget");
+
+struct AttnArgs {
+  int Lq, Lk, H;
+  int n_kv_tiles;
+  int n_qpairs;
+  float scale_log2;        // softmax_scale * log2(e)
+  const float* q_scale;    // fp8: [H, nqb]
+  const float* k_scale;    // fp8: [H, nkb]
+  int nqb, nkb;
+  const int32_t* row_ptr;  // sparse: CSR row pointers (plan entries of pair p start at row_ptr[2p])
+  const int32_t* plan;     // sparse: (tile << 2) | stream flags
+  const int32_t* plan_cnt; // sparse: entries per pair
+  __nv_bfloat16* o;
+  long long o_stride_l, o_stride_h;
+  float* lse;              // [H, Lq] or null
+  int* status;             // device status word or null
+  long long wait_ns;
+};
+
+// status word layout: bits [0,8) code, bits [8,32) blockIdx.x (truncated)
+enum : int {
+  kWaitQFull = 1, kWaitKvEmpty = 2, kWaitKvFullK = 3, kWaitKvFullV = 4,
+  kWaitSFull = 5, kWaitPFull = 6, kWaitOFull = 7
+};
+
+struct WaitCtx {
+  AttnBars* bars;
+  int* status;
+  long long limit_ns;
+};
+
+__device__ __forceinline__ bool bounded_wait(const WaitCtx& c, uint32_t bar, uint32_t parity, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint32_t polls = 0;
+  uint64_t t0 = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 63u) == 0u) {
+      if (c.bars->abort_flag) return false;
+      uint64_t now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (static_cast<long long>(now - t0) > c.limit_ns) {
+        c.bars->abort_flag = 1u;
+        if (c.status) atomicCAS(c.status, 0, code | (static_cast<int>(blockIdx.x & 0x7FFFFF) << 8));
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// Merge the sorted key-tile lists of query tiles 2p and 2p+1 into one list with stream flags.
+__global__ void build_pair_plan_kernel(const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ col_idx,
+                                       int nqb, int n_qpairs, int32_t* __restrict__ plan, int32_t* __restrict__ plan_cnt) {
+  int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= n_qpairs) return;
+  int r0 = 2 * p, r1 = 2 * p + 1;
+  int a = row_ptr[r0], a_end = row_ptr[r0 + 1];
+  int b = (r1 < nqb) ? row_ptr[r1] : 0, b_end = (r1 < nqb) ? row_ptr[r1 + 1] : 0;
+  int32_t* out = plan + row_ptr[r0];
+  int n = 0;
+  while (a < a_end || b < b_end) {
+    int ca = (a < a_end) ? col_idx[a] : 0x7FFFFFFF;
+    int cb = (b < b_end) ? col_idx[b] : 0x7FFFFFFF;
+    int c = min(ca, cb);
+    int f = 0;
+    if (ca == c) { f |= 1; ++a; }
+    if (cb == c) { f |= 2; ++b; }
+    out[n++] = (c << 2) | f;
+  }
+  plan_cnt[p] = n;
+}
+
+template <bool kFp8, bool kSparse>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const AttnArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;  // 128B-swizzled tiles want 1024-byte alignment
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const uint32_t q_smem = base;
+  const uint32_t ring_smem = base + 2 * kQTileBytes;
+  AttnBars* bars = reinterpret_cast<AttnBars*>(smem + 2 * kQTileBytes + kStages * kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int head = blockIdx.x / args.n_qpairs;
+  const int pair = blockIdx.x % args.n_qpairs;
+  const int q0 = pair * 2 * kTile;
+
+  constexpr uint32_t kQBytes = kFp8 ? kHalfBytes : kQTileBytes;  // bytes per Q tile
+  constexpr uint32_t kKBytes = kFp8 ? kHalfBytes : kStageBytes;  // bytes per K tile
+  constexpr uint32_t kVBytes = kStageBytes;
+
+  // ---- plan: which key tiles, for which streams
+  int n_it;
+  const int32_t* plan = nullptr;
+  int dense_flags = 3;
+  if constexpr (kSparse) {
+    plan = args.plan + args.row_ptr[2 * pair];
+    n_it = args.plan_cnt[pair];
+  } else {
+    n_it = args.n_kv_tiles;
+    dense_flags = (q0 + kTile < args.Lq) ? 3 : 1;
+  }
+  auto entry_at = [&](int it) -> int {
+    if constexpr (kSparse) return plan[it];
+    else return (it << 2) | dense_flags;
+  };
+
+  // ---- set-up
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(smem_u32(&bars->kv_full[i]), 1);
+      mbar_init(smem_u32(&bars->kv_empty[i]), 1);
+    }
+    mbar_init(smem_u32(&bars->q_full), 1);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(smem_u32(&bars->s_full[t]), 1);
+      mbar_init(smem_u32(&bars->p_full[t]), 128);
+      mbar_init(smem_u32(&bars->o_full[t]), 1);
+    }
+    bars->abort_flag = 0;
+    bars->early_exit = (args.status != nullptr && *reinterpret_cast<volatile int*>(args.status) != 0) ? 1u : 0u;
+    fence_mbar_init();
+  }
+  if (warp == kProducerWarp && lane == 0) {
+    prefetch_tmap(&tm_q);
+    prefetch_tmap(&tm_k);
+    prefetch_tmap(&tm_v);
+  }
+  __syncthreads();
+  if (bars->early_exit) return;  // an earlier CTA of this launch already gave up: do nothing
+  if (warp == kIssuerWarp) {
+    tmem_alloc(smem_u32(&bars->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = bars->tmem_base;
+
+  WaitCtx wc{bars, args.status, args.wait_ns};
+
+  if (warp == kProducerWarp) {
+    // =========================================================== producer
+    if (lane == 0) {
+      const uint32_t qbar = smem_u32(&bars->q_full);
+      mbar_arrive_expect_tx(qbar, 2 * kQBytes);
+      for (int t = 0; t < 2; ++t) {
+        if constexpr (kFp8) {
+          tma_load_3d(q_smem + t * kQTileBytes, &tm_q, qbar, 0, q0 + t * kTile, head);
+        } else {
+          tma_load_3d(q_smem + t * kQTileBytes, &tm_q, qbar, 0, q0 + t * kTile, head);
+          tma_load_3d(q_smem + t * kQTileBytes + kHalfBytes, &tm_q, qbar, 64, q0 + t * kTile, head);
+        }
+      }
+      int cnt = 0;
+      for (int it = 0; it < n_it; ++it) {
+        const int tile = entry_at(it) >> 2;
+        {  // K tile
+          const int s = cnt % kStages;
+          const uint32_t ph = (cnt / kStages) & 1;
+          if (!bounded_wait(wc, smem_u32(&bars->kv_empty[s]), ph ^ 1u, kWaitKvEmpty)) break;
+          const uint32_t fb = smem_u32(&bars->kv_full[s]);
+          const uint32_t dst = ring_smem + s * kStageBytes;
+          mbar_arrive_expect_tx(fb, kKBytes);
+          tma_load_3d(dst, &tm_k, fb, 0, tile * kTile, head);
+          if constexpr (!kFp8) tma_load_3d(dst + kHalfBytes, &tm_k, fb, 64, tile * kTile, head);
+          ++cnt;
+        }
+        {  // V tile
+          const int s = cnt % kStages;
+          const uint32_t ph = (cnt / kStages) & 1;
+          if (!bounded_wait(wc, smem_u32(&bars->kv_empty[s]), ph ^ 1u, kWaitKvEmpty)) break;
+          const uint32_t fb = smem_u32(&bars->kv_full[s]);
+          const uint32_t dst = ring_smem + s * kStageBytes;
+          mbar_arrive_expect_tx(fb, kVBytes);
+          tma_load_3d(dst, &tm_v, fb, 0, tile * kTile, head);
+          tma_load_3d(dst + kHalfBytes, &tm_v, fb, 64, tile * kTile, head);
+          ++cnt;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == kIssuerWarp) {
+    // =========================================================== MMA issuer
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idesc_s = kFp8 ? umma_idesc(UMMA_FMT_E4M3, UMMA_FMT_E4M3, 0, 0, 128, 128)
+                                        : umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 0, 128, 128);
+      constexpr uint32_t idesc_pv = umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 1, 128, 128);
+      bool ok = bounded_wait(wc, smem_u32(&bars->q_full), 0, kWaitQFull);
+      tc_fence_after_sync();
+      uint32_t p_cnt[2] = {0, 0};
+      uint32_t pv_cnt[2] = {0, 0};
+
+      // S_t = Q_t K^T for ring stage `sk` (both operands K-major, 128B swizzle, 8-row groups 1024 B apart)
+      auto issue_s = [&](int t, int sk) {
+        const uint32_t qa = q_smem + t * kQTileBytes;
+        const uint32_t ka = ring_smem + sk * kStageBytes;
+        const uint32_t d = tmem + t * kTile;
+        if constexpr (kFp8) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // 32 e4m3 = 32 bytes per step inside the 128-byte swizzle span
+            umma_e4m3_ss(d, umma_desc_sw128(qa + k * 32, 16, 1024), umma_desc_sw128(ka + k * 32, 16, 1024), idesc_s, k > 0);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {  // 16 bf16 = 32 bytes per step; dims 64..127 live in the second box
+            const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+            umma_bf16_ss(d, umma_desc_sw128(qa + off, 16, 1024), umma_desc_sw128(ka + off, 16, 1024), idesc_s, k > 0);
+          }
+        }
+        umma_commit(smem_u32(&bars->s_full[t]));
+      };
+      // O_t += P_t V for ring stage `sv`: A = P from TMEM (two bf16 per column), B = V MN-major
+      // ([token][64 dims] boxes: 8-token groups 1024 B apart, the two 64-dim halves 16 KB apart)
+      auto issue_pv = [&](int t, int sv) {
+        const uint32_t va = ring_smem + sv * kStageBytes;
+        const uint32_t d = tmem + 256 + t * kTile;
+        const uint32_t a = tmem + t * kTile;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // 16 tokens per step = 16 rows of 128 B
+          umma_bf16_ts(d, a + k * 8, umma_desc_sw128(va + k * 2048, kHalfBytes, 1024), idesc_pv, (pv_cnt[t] > 0 || k > 0) ? 1u : 0u);
+        ++pv_cnt[t];
+        umma_commit(smem_u32(&bars->o_full[t]));
+      };
+
+      if (ok) {  // prologue: S for entry 0
+        const int f0 = entry_at(0) & 3;
+        ok = bounded_wait(wc, smem_u32(&bars->kv_full[0]), 0, kWaitKvFullK);
+        if (ok) {
+          tc_fence_after_sync();
+          if (f0 & 1) issue_s(0, 0);
+          if (f0 & 2) issue_s(1, 0);
+          umma_commit(smem_u32(&bars->kv_empty[0]));
+        }
+      }
+      for (int it = 0; ok && it < n_it; ++it) {
+        const int f = entry_at(it) & 3;
+        const bool has_next = (it + 1 < n_it);
+        const int fn = has_next ? (entry_at(it + 1) & 3) : 0;
+        const int cv = 2 * it + 1, ck = 2 * it + 2;
+        const int sv = cv % kStages, sk = ck % kStages;
+        ok = bounded_wait(wc, smem_u32(&bars->kv_full[sv]), (cv / kStages) & 1, kWaitKvFullV);
+        if (!ok) break;
+        bool k_ready = false;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if ((f >> t) & 1) {
+            ok = bounded_wait(wc, smem_u32(&bars->p_full[t]), p_cnt[t] & 1, kWaitPFull);
+            if (!ok) break;
+            ++p_cnt[t];
+            tc_fence_after_sync();
+            issue_pv(t, sv);
+          }
+          if ((fn >> t) & 1) {
+            if (!k_ready) {
+              ok = bounded_wait(wc, smem_u32(&bars->kv_full[sk]), (ck / kStages) & 1, kWaitKvFullK);
+              if (!ok) break;
+              k_ready = true;
+              tc_fence_after_sync();
+            }
+            issue_s(t, sk);
+          }
+        }
+        if (!ok) break;
+        umma_commit(smem_u32(&bars->kv_empty[sv]));
+        if (has_next) umma_commit(smem_u32(&bars->kv_empty[sk]));
+      }
+    }
+    __syncwarp();
+  } else {
+    // =========================================================== softmax / rescale / epilogue
+    const int t = warp >> 2;            // stream
+    const int quarter = warp & 3;       // TMEM lane quarter this warp may touch
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem + lane_base + t * kTile;
+    const uint32_t o_addr = tmem + lane_base + 256 + t * kTile;
+    const int q_row = q0 + t * kTile + row;
+    const int last_tile = args.n_kv_tiles - 1;
+    const int tail = args.Lk - last_tile * kTile;  // valid columns of the last key tile (1..128)
+
+    float qs = 1.0f;
+    if constexpr (kFp8) {
+      const int qb = min(q0 / kTile + t, args.nqb - 1);
+      qs = args.q_scale[head * args.nqb + qb];
+    }
+    float m_ref = 0.0f, l_sum = 0.0f;
+    uint32_t j = 0;
+    bool ok = true;
+    uint32_t s[128];
+
+    for (int it = 0; it < n_it; ++it) {
+      const int e = entry_at(it);
+      if (!((e >> t) & 1)) continue;
+      const int tile = e >> 2;
+      float c = args.scale_log2;
+      if constexpr (kFp8) c *= qs * args.k_scale[head * args.nkb + tile];
+
+      ok = bounded_wait(wc, smem_u32(&bars->s_full[t]), j & 1, kWaitSFull);
+      if (!ok) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) tmem_ld32(s_addr + 32 * i, *reinterpret_cast<uint32_t(*)[32]>(&s[32 * i]));
+      tmem_wait_ld();
+
+      if (tile == last_tile && tail < kTile) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (i >= tail) s[i] = 0xFF800000u;  // -inf
+      }
+      float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]), mx2 = __uint_as_float(s[2]), mx3 = __uint_as_float(s[3]);
+#pragma unroll
+      for (int i = 4; i < 128; i += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(s[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+      }
+      const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;
+
+      if (j == 0) {
+        m_ref = m_tile;
+      } else {
+        const bool grow = (m_tile - m_ref) > kRescaleThreshold;
+        if (__any_sync(0xFFFFFFFFu, grow)) {
+          const float m_new = fmaxf(m_ref, m_tile);
+          const float alpha = ex2_approx(m_ref - m_new);
+          m_ref = m_new;
+          l_sum *= alpha;
+          // O_t must be quiescent: the previous P V of this stream has to be complete
+          ok = bounded_wait(wc, smem_u32(&bars->o_full[t]), (j - 1) & 1, kWaitOFull);
+          if (!ok) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t o[32];
+            tmem_ld32(o_addr + 32 * i, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * alpha);
+            tmem_st32(o_addr + 32 * i, o);
+          }
+        }
+      }
+
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      const float neg_m = -m_ref;
+#pragma unroll
+      for (int i = 0; i < 128; i += 4) {
+        const float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), c, neg_m));
+        const float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), c, neg_m));
+        const float p2 = ex2_approx(fmaf(__uint_as_float(s[i + 2]), c, neg_m));
+        const float p3 = ex2_approx(fmaf(__uint_as_float(s[i + 3]), c, neg_m));
+        l0 += p0; l1 += p1; l2 += p2; l3 += p3;
+        s[i >> 1] = pack_bf16x2(p0, p1);        // slot i/2 <= i: already consumed
+        s[(i >> 1) + 1] = pack_bf16x2(p2, p3);
+      }
+      l_sum += (l0 + l1) + (l2 + l3);
+      tmem_st32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_st32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&bars->p_full[t]));
+      ++j;
+    }
+
+    // ---- epilogue: O / l -> bf16 -> global
+    const bool row_valid = q_row < args.Lq;
+    __nv_bfloat16* orow = args.o + static_cast<long long>(q_row) * args.o_stride_l + static_cast<long long>(head) * args.o_stride_h;
+    if (ok && j > 0) {
+      ok = bounded_wait(wc, smem_u32(&bars->o_full[t]), (j - 1) & 1, kWaitOFull);
+      if (ok) {
+        tc_fence_after_sync();
+        const float inv = 1.0f / l_sum;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + 32 * i, o);
+          tmem_wait_ld();
+          if (row_valid) {
+#pragma unroll
+            for (int x = 0; x < 32; x += 8) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(o[x]) * inv, __uint_as_float(o[x + 1]) * inv);
+              w.y = pack_bf16x2(__uint_as_float(o[x + 2]) * inv, __uint_as_float(o[x + 3]) * inv);
+              w.z = pack_bf16x2(__uint_as_float(o[x + 4]) * inv, __uint_as_float(o[x + 5]) * inv);
+              w.w = pack_bf16x2(__uint_as_float(o[x + 6]) * inv, __uint_as_float(o[x + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + 32 * i + x) = w;
+            }
+          }
+        }
+        if (row_valid && args.lse)
+          args.lse[static_cast<long long>(head) * args.Lq + q_row] = (m_ref + log2f(l_sum)) * 0.6931471805599453f;
+      }
+    } else if (ok && row_valid) {
+      // no key tile listed for this query tile: the output row is zero
+      const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int x = 0; x < 128; x += 8) *reinterpret_cast<uint4*>(orow + x) = z;
+      if (args.lse) args.lse[static_cast<long long>(head) * args.Lq + q_row] = -INFINITY;
+    }
+  }
+
+  // ---- tear-down
+  tc_fence_before_sync();
+  __syncthreads();
+  if (bars->abort_flag) {
+    // a wait gave up: give copies and MMAs in flight a bounded time to land before TMEM and smem go away
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == kIssuerWarp) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace h3a

@@ -1,0 +1,290 @@
+// C-ABI entry points of libh3attn.so: argument validation, TMA tensor maps, kernel launches and the
+// host-side block-index builder.  Declarations and per-function contracts live in include/h3attn.h.
+#include "../../include/h3attn.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "attn_fwd.cuh"
+#include "qk_prep.cuh"
+
+namespace {
+
+using h3a::AttnArgs;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// x[l*stride_l + h*stride_h + c]: dims (128, L, H); box = (box_inner, 128 rows, 1 head), 128-byte swizzle.
+int32_t make_map(CUtensorMap* m, const void* ptr, bool fp8, int64_t L, int64_t H, int64_t stride_l, int64_t stride_h) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return H3A_ERR_DRIVER;
+  const int64_t es = fp8 ? 1 : 2;
+  if (!aligned16(ptr) || (stride_l * es) % 16 != 0 || (stride_h * es) % 16 != 0) return H3A_ERR_ALIGN;
+  if (stride_l <= 0 || stride_h <= 0) return H3A_ERR_ARG;
+  cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(L), static_cast<cuuint64_t>(H)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(stride_l * es), static_cast<cuuint64_t>(stride_h * es)};
+  cuuint32_t box[3] = {fp8 ? 128u : 64u, 128u, 1u};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims,
+                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? H3A_OK : H3A_ERR_LAUNCH;
+}
+
+int32_t check_arch() {
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return H3A_ERR_LAUNCH;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return H3A_ERR_LAUNCH;
+  return major == 10 ? H3A_OK : H3A_ERR_ARCH;
+}
+
+int32_t validate_attn(const h3a_attn_params* p) {
+  if (!p || !p->q || !p->k || !p->v || !p->o) return H3A_ERR_ARG;
+  if (p->d != 128 || p->B != 1) return H3A_ERR_SHAPE;
+  if (p->Lq <= 0 || p->Lk <= 0 || p->H <= 0) return H3A_ERR_SHAPE;
+  if (p->mode < H3A_MODE_DENSE_BF16 || p->mode > H3A_MODE_BLOCK_SPARSE) return H3A_ERR_ARG;
+  if (p->mode == H3A_MODE_FP8_QK && (!p->q_scale || !p->k_scale)) return H3A_ERR_ARG;
+  if (p->mode == H3A_MODE_BLOCK_SPARSE && (!p->row_ptr || !p->col_idx || p->nnz < 0)) return H3A_ERR_ARG;
+  if (!aligned16(p->o) || (p->o_stride_l % 8) != 0 || (p->o_stride_h % 8) != 0) return H3A_ERR_ALIGN;
+  if (p->o_stride_l <= 0 || p->o_stride_h <= 0) return H3A_ERR_ARG;
+  return H3A_OK;
+}
+
+size_t sparse_workspace_bytes(const h3a_attn_params* p) {
+  const size_t n_qpairs = (static_cast<size_t>(p->Lq) + 255) / 256;
+  // plan entries (one per kept tile at most) followed by one count per query-tile pair
+  return (static_cast<size_t>(p->nnz) + n_qpairs) * sizeof(int32_t);
+}
+
+template <bool kFp8, bool kSparse>
+int32_t launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a, cudaStream_t st) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(h3a::attn_fwd_kernel<kFp8, kSparse>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    h3a::kAttnSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return H3A_ERR_LAUNCH;
+  const unsigned grid = static_cast<unsigned>(a.n_qpairs) * static_cast<unsigned>(a.H);
+  h3a::attn_fwd_kernel<kFp8, kSparse><<<grid, h3a::kAttnThreads, h3a::kAttnSmemBytes, st>>>(mq, mk, mv, a);
+  return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t h3a_version(int32_t* major, int32_t* minor) {
+  if (major) *major = H3A_VERSION_MAJOR;
+  if (minor) *minor = H3A_VERSION_MINOR;
+  return H3A_OK;
+}
+
+const char* h3a_status_string(int32_t s) {
+  switch (s) {
+    case H3A_OK: return "ok";
+    case H3A_ERR_ARG: return "invalid argument (null pointer, bad enum or flag)";
+    case H3A_ERR_ALIGN: return "pointer or stride not 16-byte aligned";
+    case H3A_ERR_SHAPE: return "unsupported shape (head dim must be 128, batch 1, extents > 0)";
+    case H3A_ERR_ARCH: return "device is not compute capability 10.x (B200)";
+    case H3A_ERR_LAUNCH: return "CUDA runtime or driver call failed";
+    case H3A_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case H3A_ERR_WORKSPACE: return "workspace missing or too small";
+    case H3A_ERR_DRIVER: return "driver entry point cuTensorMapEncodeTiled not available";
+    default: return "unknown status";
+  }
+}
+
+int32_t h3a_attn_workspace_bytes(const h3a_attn_params* p, size_t* bytes) {
+  if (!p || !bytes) return H3A_ERR_ARG;
+  *bytes = (p->mode == H3A_MODE_BLOCK_SPARSE) ? sparse_workspace_bytes(p) : 0;
+  return H3A_OK;
+}
+
+int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream) {
+  int32_t rc = validate_attn(p);
+  if (rc != H3A_OK) return rc;
+  rc = check_arch();
+  if (rc != H3A_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool fp8 = p->mode == H3A_MODE_FP8_QK;
+  const bool sparse = p->mode == H3A_MODE_BLOCK_SPARSE;
+
+  CUtensorMap mq, mk, mv;
+  if ((rc = make_map(&mq, p->q, fp8, p->Lq, p->H, p->q_stride_l, p->q_stride_h)) != H3A_OK) return rc;
+  if ((rc = make_map(&mk, p->k, fp8, p->Lk, p->H, p->k_stride_l, p->k_stride_h)) != H3A_OK) return rc;
+  if ((rc = make_map(&mv, p->v, false, p->Lk, p->H, p->v_stride_l, p->v_stride_h)) != H3A_OK) return rc;
+
+  AttnArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.Lq = p->Lq; a.Lk = p->Lk; a.H = p->H;
+  a.nqb = (p->Lq + 127) / 128;
+  a.nkb = (p->Lk + 127) / 128;
+  a.n_kv_tiles = a.nkb;
+  a.n_qpairs = (p->Lq + 255) / 256;
+  const float scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->d));
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.q_scale = p->q_scale; a.k_scale = p->k_scale;
+  a.o = static_cast<__nv_bfloat16*>(p->o);
+  a.o_stride_l = p->o_stride_l; a.o_stride_h = p->o_stride_h;
+  a.lse = p->lse;
+  a.status = p->status_word;
+  a.wait_ns = p->wait_limit_ns > 0 ? p->wait_limit_ns : 2000000000ll;
+
+  if (sparse) {
+    const size_t need = sparse_workspace_bytes(p);
+    if (!p->workspace || p->workspace_bytes < need) return H3A_ERR_WORKSPACE;
+    if (!aligned16(p->workspace)) return H3A_ERR_ALIGN;
+    int32_t* plan = static_cast<int32_t*>(p->workspace);
+    int32_t* plan_cnt = plan + p->nnz;
+    const int threads = 128;
+    h3a::build_pair_plan_kernel<<<(a.n_qpairs + threads - 1) / threads, threads, 0, st>>>(p->row_ptr, p->col_idx, a.nqb,
+                                                                                         a.n_qpairs, plan, plan_cnt);
+    if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
+    a.row_ptr = p->row_ptr; a.plan = plan; a.plan_cnt = plan_cnt;
+    return launch_attn<false, true>(mq, mk, mv, a, st);
+  }
+  if (fp8) return launch_attn<true, false>(mq, mk, mv, a, st);
+  return launch_attn<false, false>(mq, mk, mv, a, st);
+}
+
+int32_t h3a_qk_prep(const h3a_prep_params* p, void* stream) {
+  if (!p) return H3A_ERR_ARG;
+  if (p->d != 128 || p->H <= 0) return H3A_ERR_SHAPE;
+  if (p->rope_mode != H3A_ROPE_INTERLEAVED && p->rope_mode != H3A_ROPE_HALF) return H3A_ERR_ARG;
+  if (p->flags & ~H3A_PREP_FP8) return H3A_ERR_ARG;
+  const bool fp8 = (p->flags & H3A_PREP_FP8) != 0;
+  int32_t rc = check_arch();
+  if (rc != H3A_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (int which = 0; which < 2; ++which) {
+    h3a::PrepArgs a;
+    a.in = static_cast<const __nv_bfloat16*>(which ? p->k_in : p->q_in);
+    if (!a.in) continue;
+    a.out = which ? p->k_out : p->q_out;
+    a.scale = which ? p->k_scale : p->q_scale;
+    a.stride_l = which ? p->k_stride_l : p->q_stride_l;
+    a.stride_h = which ? p->k_stride_h : p->q_stride_h;
+    a.L = which ? p->Lk : p->Lq;
+    a.H = p->H;
+    a.rope = which ? p->k_rope : p->q_rope;
+    a.weight = which ? p->k_weight : p->q_weight;
+    a.eps = p->eps > 0.f ? p->eps : 1e-6f;
+    a.rope_half = p->rope_mode == H3A_ROPE_HALF;
+    if (a.L <= 0) return H3A_ERR_SHAPE;
+    if (!a.out || (fp8 && !a.scale)) return H3A_ERR_ARG;
+    if (!aligned16(a.in) || !aligned16(a.out) || (a.stride_l % 8) || (a.stride_h % 8)) return H3A_ERR_ALIGN;
+    if (a.rope && !aligned16(a.rope)) return H3A_ERR_ALIGN;
+    a.nblk = (a.L + 127) / 128;
+    dim3 grid(a.nblk, a.H);
+    if (fp8) h3a::qk_prep_kernel<true><<<grid, h3a::kPrepThreads, 0, st>>>(a);
+    else h3a::qk_prep_kernel<false><<<grid, h3a::kPrepThreads, 0, st>>>(a);
+    if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
+  }
+  return H3A_OK;
+}
+
+int32_t h3a_rope_table(const float* pos, int32_t L, const int32_t split[3], float theta, float* table, void* stream) {
+  if (!pos || !table || !split) return H3A_ERR_ARG;
+  if (L <= 0) return H3A_ERR_SHAPE;
+  if (split[0] + split[1] + split[2] != 128 || (split[0] | split[1] | split[2]) & 1 || split[0] <= 0 || split[1] < 0 || split[2] < 0)
+    return H3A_ERR_SHAPE;
+  if (!aligned16(table)) return H3A_ERR_ALIGN;
+  int32_t rc = check_arch();
+  if (rc != H3A_OK) return rc;
+  const long long n = static_cast<long long>(L) * 64;
+  const int threads = 256;
+  h3a::rope_table_kernel<<<static_cast<unsigned>((n + threads - 1) / threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      pos, L, split[0], split[1], split[2], theta > 0.f ? theta : 10000.0f, table);
+  return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
+}
+
+int32_t h3a_build_block_index(int32_t T, int32_t Hg, int32_t Wg, int32_t n_audio, int32_t wt, int32_t wh, int32_t ww,
+                              int32_t* row_ptr, int32_t* col_idx, int64_t* nnz) {
+  if (!nnz) return H3A_ERR_ARG;
+  if (T <= 0 || Hg <= 0 || Wg <= 0 || n_audio < 0 || wt < 0 || wh < 0 || ww < 0) return H3A_ERR_SHAPE;
+  const int64_t n_video = static_cast<int64_t>(T) * Hg * Wg;
+  const int64_t L = n_audio + n_video;
+  const int64_t nb = (L + 127) / 128;
+  // column tiles that hold at least one audio key are always kept
+  const int64_t n_audio_tiles = (n_audio + 127) / 128;
+  std::vector<uint8_t> mark(static_cast<size_t>(nb));
+  std::vector<int32_t> cols;
+  int64_t total = 0;
+  const bool fill = col_idx != nullptr;
+  if (fill && !row_ptr) return H3A_ERR_ARG;
+  const int64_t cap = fill ? *nnz : 0;
+  if (fill) row_ptr[0] = 0;
+  for (int64_t qb = 0; qb < nb; ++qb) {
+    const int64_t lo = qb * 128, hi = std::min<int64_t>(L, lo + 128);
+    if (lo < n_audio) {
+      std::fill(mark.begin(), mark.end(), 1);  // the tile holds audio queries: dense row
+    } else {
+      std::fill(mark.begin(), mark.end(), 0);
+      for (int64_t b = 0; b < n_audio_tiles; ++b) mark[b] = 1;
+    }
+    if (lo >= n_audio) {
+      // video queries of this tile: each one sees a (2wt+1) x (2wh+1) set of row segments of width 2ww+1
+      for (int64_t tok = lo; tok < hi; ++tok) {
+        const int64_t n = tok - n_audio;
+        const int t = static_cast<int>(n / (static_cast<int64_t>(Hg) * Wg));
+        const int h = static_cast<int>((n / Wg) % Hg);
+        const int w = static_cast<int>(n % Wg);
+        const int w0 = std::max(0, w - ww), w1 = std::min(Wg - 1, w + ww);
+        for (int tt = std::max(0, t - wt); tt <= std::min(T - 1, t + wt); ++tt)
+          for (int hh = std::max(0, h - wh); hh <= std::min(Hg - 1, h + wh); ++hh) {
+            const int64_t base = n_audio + (static_cast<int64_t>(tt) * Hg + hh) * Wg;
+            const int64_t b0 = (base + w0) / 128, b1 = (base + w1) / 128;
+            for (int64_t b = b0; b <= b1; ++b) mark[b] = 1;
+          }
+      }
+    }
+    for (int64_t b = 0; b < nb; ++b)
+      if (mark[b]) {
+        if (fill) {
+          if (total >= cap) return H3A_ERR_WORKSPACE;
+          col_idx[total] = static_cast<int32_t>(b);
+        }
+        ++total;
+      }
+    if (fill) row_ptr[qb + 1] = static_cast<int32_t>(total);
+  }
+  if (total > 0x7FFFFFFF) return H3A_ERR_SHAPE;
+  *nnz = total;
+  return H3A_OK;
+}
+
+int32_t h3a_read_device_status(const int32_t* status_word, void* stream, int32_t* raw) {
+  if (!status_word) return H3A_ERR_ARG;
+  int32_t v = 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(&v, status_word, sizeof(v), cudaMemcpyDeviceToHost, st) != cudaSuccess) return H3A_ERR_LAUNCH;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return H3A_ERR_LAUNCH;
+  if (raw) *raw = v;
+  return v == 0 ? H3A_OK : H3A_ERR_TIMEOUT;
+}
+
+}  // extern "C"

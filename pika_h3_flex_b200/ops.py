@@ -1,0 +1,251 @@
+"""Torch-facing wrappers over the C ABI.  Tensors are device memory handles only: every function hands
+``data_ptr()``, element strides and the current CUDA stream to ``libh3attn.so``.
+
+All sequence tensors have *logical* shape ``[L, H, 128]`` with the last dim contiguous; any L/H strides
+(so ``[H, L, 128]`` storage viewed through ``permute(1, 0, 2)`` is fine and is what ``qk_prep`` returns).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import AttnParams, PrepParams, check
+
+TILE = 128
+HEAD_DIM = 128
+ROPE_SPLIT = (32, 48, 48)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("h3attn runs on CUDA tensors only (there is no CPU path)")
+
+
+def _lhd(t: torch.Tensor, name: str, dtypes) -> Tuple[int, int, int, int]:
+    if t.dim() != 3 or t.shape[2] != HEAD_DIM or t.stride(2) != 1:
+        raise ValueError(f"{name}: expected logical [L, H, 128] with a contiguous last dim, got {tuple(t.shape)} / {t.stride()}")
+    if t.dtype not in dtypes:
+        raise TypeError(f"{name}: dtype {t.dtype} not in {dtypes}")
+    return t.shape[0], t.shape[1], t.stride(0), t.stride(1)
+
+
+@dataclass
+class BlockIndex:
+    """CSR index over 128x128 tiles: ``row_ptr [nQB+1]``, ``col_idx [nnz]`` (int32, columns ascending)."""
+
+    row_ptr: torch.Tensor
+    col_idx: torch.Tensor
+    nnz: int
+    n_q_tiles: int
+    n_k_tiles: int
+
+    @property
+    def density(self) -> float:
+        return self.nnz / float(self.n_q_tiles * self.n_k_tiles)
+
+    def to(self, device) -> "BlockIndex":
+        return BlockIndex(self.row_ptr.to(device), self.col_idx.to(device), self.nnz, self.n_q_tiles, self.n_k_tiles)
+
+    @staticmethod
+    def from_csr(row_ptr, col_idx, n_k_tiles: int) -> "BlockIndex":
+        rp = torch.as_tensor(np.asarray(row_ptr), dtype=torch.int32)
+        ci = torch.as_tensor(np.asarray(col_idx), dtype=torch.int32)
+        return BlockIndex(rp, ci, int(ci.numel()), int(rp.numel() - 1), int(n_k_tiles))
+
+
+def build_block_index(grid: Tuple[int, int, int], n_audio: int, window: Tuple[int, int, int] = (2, 8, 8)) -> BlockIndex:
+    """Spatiotemporal-neighbourhood block index (host memory) via ``h3a_build_block_index``."""
+    lib = _lib.load()
+    T, Hg, Wg = (int(x) for x in grid)
+    L = n_audio + T * Hg * Wg
+    nb = (L + TILE - 1) // TILE
+    nnz = C.c_int64(0)
+    args = [T, Hg, Wg, int(n_audio), int(window[0]), int(window[1]), int(window[2])]
+    check(lib.h3a_build_block_index(*args, None, None, C.byref(nnz)), "h3a_build_block_index(size)")
+    row_ptr = np.zeros(nb + 1, dtype=np.int32)
+    col_idx = np.zeros(max(1, nnz.value), dtype=np.int32)
+    check(
+        lib.h3a_build_block_index(*args, row_ptr.ctypes.data, col_idx.ctypes.data, C.byref(nnz)),
+        "h3a_build_block_index(fill)",
+    )
+    return BlockIndex(torch.from_numpy(row_ptr), torch.from_numpy(col_idx[: nnz.value].copy()), int(nnz.value), nb, nb)
+
+
+def rope_table(pos: torch.Tensor, split=ROPE_SPLIT, theta: float = 10000.0) -> torch.Tensor:
+    """(cos, sin) table ``[L, 64, 2]`` fp32 on the device from a position grid ``[L, 3]``."""
+    _require_cuda(pos)
+    lib = _lib.load()
+    p = pos.to(torch.float32).contiguous()
+    L = p.shape[0]
+    table = torch.empty(L, 64, 2, dtype=torch.float32, device=p.device)
+    sp = (C.c_int32 * 3)(*[int(s) for s in split])
+    check(lib.h3a_rope_table(p.data_ptr(), L, sp, float(theta), table.data_ptr(), _stream()), "h3a_rope_table")
+    return table
+
+
+def rope_table_from_cos_sin(cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Pack caller-supplied ``cos, sin [L, 64]`` into the ``[L, 64, 2]`` fp32 table layout."""
+    return torch.stack([cos.to(torch.float32), sin.to(torch.float32)], dim=-1).contiguous()
+
+
+def qk_prep(
+    q: Optional[torch.Tensor],
+    k: Optional[torch.Tensor],
+    q_rope: Optional[torch.Tensor] = None,
+    k_rope: Optional[torch.Tensor] = None,
+    q_weight: Optional[torch.Tensor] = None,
+    k_weight: Optional[torch.Tensor] = None,
+    eps: float = 1e-6,
+    fp8: bool = False,
+    rope_half: bool = False,
+):
+    """RMSNorm + rotation (+ e4m3 quantisation).  Returns ``(q', k', q_scale, k_scale)``; the prepared
+    tensors are logical ``[L, H, 128]`` views of head-major storage; scales are ``[H, ceil(L/128)]`` or None."""
+    _require_cuda(q, k)
+    lib = _lib.load()
+    p = PrepParams()
+    p.d = HEAD_DIM
+    p.eps = float(eps)
+    p.rope_mode = _lib.ROPE_HALF if rope_half else _lib.ROPE_INTERLEAVED
+    p.flags = _lib.PREP_FP8 if fp8 else 0
+    outs = {}
+    keep = []
+    H = None
+    for name, x, rope, w in (("q", q, q_rope, q_weight), ("k", k, k_rope, k_weight)):
+        if x is None:
+            outs[name] = (None, None)
+            continue
+        L, h, sl, sh = _lhd(x, name, (torch.bfloat16,))
+        if H is not None and h != H:
+            raise ValueError("q and k must have the same number of heads")
+        H = h
+        out = torch.empty(h, L, HEAD_DIM, dtype=torch.uint8 if fp8 else torch.bfloat16, device=x.device)
+        scale = torch.empty(h, (L + TILE - 1) // TILE, dtype=torch.float32, device=x.device) if fp8 else None
+        setattr(p, f"{name}_in", x.data_ptr())
+        setattr(p, f"{name}_out", out.data_ptr())
+        setattr(p, f"{name}_scale", scale.data_ptr() if fp8 else None)
+        setattr(p, f"{name}_stride_l", sl)
+        setattr(p, f"{name}_stride_h", sh)
+        setattr(p, f"L{name}", L)
+        if rope is not None:
+            if rope.shape != (L, 64, 2) or rope.dtype != torch.float32 or not rope.is_contiguous():
+                raise ValueError(f"{name}_rope must be a contiguous fp32 [L, 64, 2] table")
+            setattr(p, f"{name}_rope", rope.data_ptr())
+        if w is not None:
+            w = w.to(torch.float32).contiguous()
+            keep.append(w)
+            setattr(p, f"{name}_weight", w.data_ptr())
+        outs[name] = (out.permute(1, 0, 2), scale)
+    if H is None:
+        raise ValueError("nothing to prepare")
+    p.H = H
+    check(lib.h3a_qk_prep(C.byref(p), _stream()), "h3a_qk_prep")
+    return outs["q"][0], outs["k"][0], outs["q"][1], outs["k"][1]
+
+
+def attn_fwd(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    mode: int = _lib.MODE_DENSE_BF16,
+    q_scale: Optional[torch.Tensor] = None,
+    k_scale: Optional[torch.Tensor] = None,
+    block_index: Optional[BlockIndex] = None,
+    softmax_scale: float = 0.0,
+    out: Optional[torch.Tensor] = None,
+    return_lse: bool = False,
+    status_word: Optional[torch.Tensor] = None,
+    wait_limit_ns: int = 0,
+    workspace: Optional[torch.Tensor] = None,
+):
+    """Forward attention through ``h3a_attn_fwd``.  Returns ``out [Lq, H, 128]`` bf16 (and ``lse [H, Lq]``)."""
+    _require_cuda(q, k, v)
+    lib = _lib.load()
+    fp8 = mode == _lib.MODE_FP8_QK
+    qk_types = (torch.uint8, torch.float8_e4m3fn) if fp8 else (torch.bfloat16,)
+    Lq, H, qsl, qsh = _lhd(q, "q", qk_types)
+    Lk, Hk, ksl, ksh = _lhd(k, "k", qk_types)
+    Lv, Hv, vsl, vsh = _lhd(v, "v", (torch.bfloat16,))
+    if Hk != H or Hv != H or Lv != Lk:
+        raise ValueError("q, k, v disagree on heads or key length")
+    if out is None:
+        out = torch.empty(Lq, H, HEAD_DIM, dtype=torch.bfloat16, device=q.device)
+    _, _, osl, osh = _lhd(out, "out", (torch.bfloat16,))
+    p = AttnParams()
+    p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    p.q_stride_l, p.q_stride_h = qsl, qsh
+    p.k_stride_l, p.k_stride_h = ksl, ksh
+    p.v_stride_l, p.v_stride_h = vsl, vsh
+    p.o_stride_l, p.o_stride_h = osl, osh
+    p.Lq, p.Lk, p.H, p.d, p.B = Lq, Lk, H, HEAD_DIM, 1
+    p.mode = int(mode)
+    p.softmax_scale = float(softmax_scale)
+    if fp8:
+        nqb, nkb = (Lq + TILE - 1) // TILE, (Lk + TILE - 1) // TILE
+        if q_scale is None or k_scale is None:
+            raise ValueError("FP8_QK mode needs q_scale and k_scale")
+        if tuple(q_scale.shape) != (H, nqb) or tuple(k_scale.shape) != (H, nkb):
+            raise ValueError("scale tensors must be [H, ceil(L/128)]")
+        q_scale, k_scale = q_scale.contiguous(), k_scale.contiguous()
+        p.q_scale, p.k_scale = q_scale.data_ptr(), k_scale.data_ptr()
+    if mode == _lib.MODE_BLOCK_SPARSE:
+        if block_index is None:
+            raise ValueError("BLOCK_SPARSE mode needs a block index")
+        if block_index.n_q_tiles != (Lq + TILE - 1) // TILE or block_index.n_k_tiles != (Lk + TILE - 1) // TILE:
+            raise ValueError("block index does not match Lq / Lk")
+        if not block_index.row_ptr.is_cuda:
+            raise ValueError("block index must be on the device (BlockIndex.to(device))")
+        p.row_ptr, p.col_idx, p.nnz = block_index.row_ptr.data_ptr(), block_index.col_idx.data_ptr(), block_index.nnz
+        need = C.c_size_t(0)
+        check(lib.h3a_attn_workspace_bytes(C.byref(p), C.byref(need)), "h3a_attn_workspace_bytes")
+        if workspace is None or workspace.numel() * workspace.element_size() < need.value:
+            workspace = torch.empty(max(16, need.value), dtype=torch.uint8, device=q.device)
+        p.workspace, p.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    lse = None
+    if return_lse:
+        lse = torch.empty(H, Lq, dtype=torch.float32, device=q.device)
+        p.lse = lse.data_ptr()
+    if status_word is not None:
+        p.status_word = status_word.data_ptr()
+    p.wait_limit_ns = int(wait_limit_ns)
+    check(lib.h3a_attn_fwd(C.byref(p), _stream()), "h3a_attn_fwd")
+    return (out, lse) if return_lse else out
+
+
+def read_status(status_word: torch.Tensor) -> int:
+    """Synchronise the current stream and return the raw device status word (0 = no wait gave up)."""
+    raw = C.c_int32(0)
+    rc = _lib.load().h3a_read_device_status(status_word.data_ptr(), _stream(), C.byref(raw))
+    if rc not in (_lib.H3A_OK, _lib.H3A_ERR_TIMEOUT):
+        check(rc, "h3a_read_device_status")
+    return raw.value
+
+
+def joint_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    rope: Optional[torch.Tensor],
+    mode: int = _lib.MODE_DENSE_BF16,
+    block_index: Optional[BlockIndex] = None,
+    q_weight=None,
+    k_weight=None,
+    eps: float = 1e-6,
+    rope_half: bool = False,
+    k_rope: Optional[torch.Tensor] = None,
+    **kw,
+):
+    """The whole hot path on one GPU: prepare Q/K (norm, rotation, optional e4m3) then attention."""
+    fp8 = mode == _lib.MODE_FP8_QK
+    qp, kp, qs, ks = qk_prep(q, k, rope, rope if k_rope is None else k_rope, q_weight, k_weight, eps, fp8, rope_half)
+    return attn_fwd(qp, kp, v, mode, qs, ks, block_index, **kw)
