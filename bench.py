@@ -1,0 +1,382 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path.  One JSON line on stdout (rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+A step is one pass of the hot path over one batch of seeded synthetic input: Q/K preparation (RMSNorm +
+rotation [+ e4m3 quantisation]) followed by the attention forward, on the 480p-like joint sequence
+(49,384 tokens = 1,024 audio + 31x30x52 video, 40 heads, d = 128) unless --workload says otherwise.
+`value` counts 4*Lq*Lk*d*H*density FLOPs per step; inputs are resident in HBM when the timed region
+starts.  `e2e` is the same step driven from pinned HOST buffers (H2D of Q, K, V and D2H of the output
+inside the timed region).  With N > 1 (launched by torchrun, one rank per GPU) the same total work is
+split Ulysses-style: each rank holds L/N tokens, two all-to-all exchanges bracket the local attention.
+`--impl reference` times the CPU oracle (the restatement of the reference's attention, all host threads)
+on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (grid, n_audio, heads, mode, window, seed)
+    "cfg1_dense": ((31, 30, 52), 1024, 40, "dense_bf16", None, 1001),
+    "cfg2_fp8": ((31, 30, 52), 1024, 40, "fp8_qk", None, 1001),
+    "cfg3_sparse": ((31, 48, 84), 1024, 40, "block_sparse", (2, 8, 8), 1003),
+    "cfg3_sparse20": ((31, 48, 84), 1024, 40, "block_sparse", (3, 48, 84), 1003),
+    "cfg0_dense": ((4, 32, 32), 0, 8, "dense_bf16", None, 1000),
+}
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_kernel launch, from the ncu captures summarised
+# under profiles/ (None until a capture of that workload exists)
+NCU_TRAFFIC_BYTES = {}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["bf16_tflops"]), float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "measured"
+    return 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.gpu)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def workload_dims(name):
+    grid, n_audio, H, mode, window, seed = WORKLOADS[name]
+    L = n_audio + grid[0] * grid[1] * grid[2]
+    return grid, n_audio, L, H, mode, window, seed
+
+
+# ------------------------------------------------------------------------------------------------ CPU oracle arm
+def cpu_oracle_sample(name: str, target_seconds: float = 15.0, threads: int | None = None):
+    """Time the CPU oracle (fp32, all host threads) on a bounded sample of query rows of the workload against
+    the full key range.  Returns (tflops, cores, sample description, seconds)."""
+    from oracle import oracle as O
+
+    grid, n_audio, L, H, mode, window, seed = workload_dims(name)
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    Hs = min(H, 4)  # heads in the sample (per-head work is identical)
+    g = torch.Generator().manual_seed(seed)
+    k = torch.randn(L, Hs, 128, generator=g)
+    v = torch.randn(L, Hs, 128, generator=g)
+    pos = O.make_positions(grid, n_audio)
+    cos, sin = O.rope_table(pos)
+    csr = None
+    density = 1.0
+    if mode == "block_sparse":
+        import pika_h3_flex_b200 as h3
+
+        bi = h3.build_block_index(grid, n_audio, window)  # host-only call
+        csr = (bi.row_ptr.numpy(), bi.col_idx.numpy())
+        density = bi.density
+
+    def run(n_rows):
+        rows = torch.linspace(0, L - 1, n_rows).long()
+        q = torch.randn(L, Hs, 128, generator=torch.Generator().manual_seed(seed + 1))
+        t0 = time.perf_counter()
+        # preparation of the sampled rows and of all keys, then exact attention for the sampled rows
+        qn = O.apply_rope(O.rms_norm(q[rows]), cos[rows], sin[rows])
+        kn = O.apply_rope(O.rms_norm(k), cos, sin)
+        if mode == "fp8_qk":
+            kq, sk = O.quantize_e4m3_blocks(kn)
+            kn = O.dequantize_blocks(kq, sk)
+        if csr is None:
+            O.attention(qn, kn, v, chunk=512)
+        else:
+            full_q = torch.zeros(L, Hs, 128)
+            full_q[rows] = qn
+            O.attention(full_q, kn, v, csr=csr, q_rows=rows, chunk=512)
+        dt = time.perf_counter() - t0
+        flops = 4.0 * n_rows * L * 128 * Hs * (1.0 if csr is None else 1.0)
+        return dt, flops
+
+    run(64)  # warm-up (thread pool, allocator)
+    dt, flops = run(256)
+    n_rows = int(max(256, min(L, 256 * target_seconds / max(dt, 1e-3))))
+    dt, flops = run(n_rows)
+    # the masked oracle still evaluates full rows, so its useful FLOPs are scaled by the density
+    tflops = flops * density / dt / 1e12
+    return tflops, threads, f"{n_rows} query rows x {Hs} heads x all {L} keys of {name} (prep + exact softmax attention, fp32)", dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    name = args.workload
+    grid, n_audio, L, H, mode, window, seed = workload_dims(name)
+    per_step = max(2.0, min(20.0, 90.0 / max(1, args.steps + args.warmup)))
+    vals, times = [], []
+    cores = os.cpu_count() or 1
+    sample = ""
+    for i in range(args.warmup + args.steps):
+        tf, cores, sample, dt = cpu_oracle_sample(name, per_step)
+        if i >= args.warmup:
+            vals.append(tf)
+            times.append(dt)
+    value = sum(vals) / len(vals)
+    line = {
+        "impl": "reference", "metric": "attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "L": L, "H": H, "d": 128, "mode": mode,
+                   "note": "CPU restatement of the reference attention (oracle); each step is a bounded sample"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+def run_ours(args):
+    import torch.distributed as dist
+
+    import pika_h3_flex_b200 as h3
+    from pika_h3_flex_b200 import _lib
+    from pika_h3_flex_b200.ulysses import UlyssesAttention
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torchrun (one rank per GPU)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    torch.backends.cuda.matmul.allow_tf32 = False
+
+    name = args.workload
+    grid, n_audio, L, H, mode_name, window, seed = workload_dims(name)
+    mode = {"dense_bf16": _lib.MODE_DENSE_BF16, "fp8_qk": _lib.MODE_FP8_QK, "block_sparse": _lib.MODE_BLOCK_SPARSE}[mode_name]
+    if L % world:
+        raise SystemExit(f"sequence length {L} does not split over {world} ranks")
+    Ls = L // world
+    from pika_h3_flex_b200.layout import position_grid
+
+    pos = position_grid(grid, n_audio)[rank * Ls : (rank + 1) * Ls]
+    g = torch.Generator(device=dev).manual_seed(seed + rank)
+    q = torch.randn(Ls, H, 128, device=dev, generator=g).bfloat16()
+    k = torch.randn(Ls, H, 128, device=dev, generator=g).bfloat16()
+    v = torch.randn(Ls, H, 128, device=dev, generator=g).bfloat16()
+    rope = h3.rope_table(pos.to(dev))
+    bi = None
+    density = 1.0
+    if mode == _lib.MODE_BLOCK_SPARSE:
+        bi_host = h3.build_block_index(grid, n_audio, window)
+        density = bi_host.density
+        bi = bi_host.to(dev)
+    flops = 4.0 * L * L * 128 * H * density
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    attn_events = []
+
+    if world == 1:
+        out = torch.empty(L, H, 128, dtype=torch.bfloat16, device=dev)
+        ws = torch.empty(16, dtype=torch.uint8, device=dev)
+        if bi is not None:
+            ws = torch.empty((bi.nnz + (L + 255) // 256) * 4 + 16, dtype=torch.uint8, device=dev)
+
+        def step(record=False):
+            qp, kp, qs, ks = h3.qk_prep(q, k, rope, rope, fp8=(mode == _lib.MODE_FP8_QK))
+            if record:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            h3.attn_fwd(qp, kp, v, mode, qs, ks, bi, out=out, status_word=status, workspace=ws)
+            if record:
+                e1.record()
+                attn_events.append((e0, e1))
+            return out
+
+        launches_per_step = 3 + (1 if bi is not None else 0)
+    else:
+        ua = UlyssesAttention(None, mode, bi)
+
+        def step(record=False):
+            return ua(q, k, v, rope)
+
+        # prep (2) + V head-major copy (1, torch) + attention (1) [+ plan]; only this library's kernels are counted
+        launches_per_step = 3 + (1 if bi is not None else 0)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    if h3.read_status(status) != 0:
+        raise SystemExit(f"device wait gave up during warm-up: status 0x{h3.read_status(status):x}")
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for _ in range(args.steps):
+        step(record=True)
+    e_stop.record()
+    barrier()
+    elapsed_ms = e_start.elapsed_time(e_stop)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    value = flops / (ms_per_step * 1e-3) / 1e12
+    if h3.read_status(status) != 0:
+        raise SystemExit(f"device wait gave up: status 0x{h3.read_status(status):x}")
+
+    # ---- dominant kernel, timed live with CUDA events on the launching stream
+    roofline = None
+    if attn_events:
+        attn_ms = sum(a.elapsed_time(b) for a, b in attn_events) / len(attn_events)
+        burst, sustained, src = measured_peaks()
+        achieved = flops / (attn_ms * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": "attn_fwd_kernel", "achieved": achieved, "peak": burst, "unit": "TFLOP/s",
+                    "frac": achieved / burst, "peak_source": f"bf16 burst, of {src}", "frac_of_sustained": achieved / sustained,
+                    "frac_of_spec_2250": achieved / 2250.0, "kernel_ms": attn_ms, "traffic": NCU_TRAFFIC_BYTES.get(name)}
+
+    # ---- end to end from host buffers through the public call
+    e2e = None
+    if world == 1:
+        hq, hk, hv = (torch.empty(L, H, 128, dtype=torch.bfloat16).pin_memory() for _ in range(3))
+        for dst, src_t in ((hq, q), (hk, k), (hv, v)):
+            dst.copy_(src_t)
+        ho = torch.empty(L, H, 128, dtype=torch.bfloat16).pin_memory()
+        dq, dk, dv = (torch.empty_like(q) for _ in range(3))
+        torch.cuda.synchronize()
+
+        def e2e_step():
+            dq.copy_(hq, non_blocking=True)
+            dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True)
+            o = h3.joint_attention(dq, dk, dv, rope, mode, bi)
+            ho.copy_(o, non_blocking=True)
+
+        n_e2e = max(2, min(args.steps, 5))
+        e2e_step()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        b.record()
+        torch.cuda.synchronize()
+        e2e_ms = a.elapsed_time(b) / n_e2e
+        nbytes = L * H * 128 * 2
+        e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": 3 * nbytes,
+               "d2h_bytes_per_step": nbytes, "ms_per_step": e2e_ms, "steps": n_e2e}
+    else:
+        e2e = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+               "note": "host-buffer end-to-end is measured at N=1 only"}
+
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        cpu_baseline = None
+        if world == 1 and not args.no_cpu_baseline:
+            tf, cores, sample, _ = cpu_oracle_sample(name, args.cpu_seconds)
+            cpu_baseline = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample}
+        line = {
+            "metric": "attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16" if mode != _lib.MODE_FP8_QK else "e4m3(QK)+bf16(PV)", "data": "synthetic",
+            "config": {"workload": name, "L": L, "H": H, "d": 128, "mode": mode_name, "density": density,
+                       "flops_per_step": flops, "step": "qk_prep(RMSNorm+RoPE) + attention forward",
+                       "parallelism": "single GPU" if world == 1 else f"ulysses{world} (seq<->head all-to-all, NCCL)",
+                       "l2": "inputs (Q,K,V = %.0f MB per rank) exceed the 126 MB L2; no flush" % (3 * Ls * H * 256 / 1e6)},
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
+            "gpu_launches": launches_per_step * args.steps,
+            "attn_ms_per_dit_step_per_layer": ms_per_step,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg1_dense")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the cpu_baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -10,6 +10,7 @@ from ._lib import (
     MODE_FP8_QK,
     H3AError,
 )
+from .layout import position_grid
 from .ops import (
     BlockIndex,
     attn_fwd,
@@ -24,5 +25,5 @@ from .ops import (
 __all__ = [
     "_lib", "H3AError", "MODE_DENSE_BF16", "MODE_FP8_QK", "MODE_BLOCK_SPARSE",
     "BlockIndex", "attn_fwd", "build_block_index", "joint_attention", "qk_prep",
-    "read_status", "rope_table", "rope_table_from_cos_sin",
+    "read_status", "rope_table", "rope_table_from_cos_sin", "position_grid",
 ]

@@ -1,0 +1,148 @@
+"""Ulysses sequence parallelism around the attention path: sequence shards -> head shards -> attention
+-> sequence shards, one process per GPU, exchanges over NCCL (NVLink / NVSwitch).
+
+The reference runs one request on one GPU ("Multi-GPU inference within one request is not implemented",
+reference ``README.md:115``); this wrapper is what lets the same processor call run with the packed
+sequence split across ranks.  Rank r holds tokens ``[r*L/P, (r+1)*L/P)`` of every head.  Normalisation,
+rotation and (in FP8 mode) quantisation are token-local, so they run BEFORE the exchange and the wire
+carries final operands in head-major layout ``[H, L/P, 128]``: the block that goes to rank p (its
+``H/P`` heads) is contiguous, and each received ``[L/P, 128]`` block lands directly at its final place in
+``[H/P, L, 128]``, so neither side needs a pack or unpack pass.
+
+Exchanges are batched point-to-point operations (``torch.distributed.batch_isend_irecv``: grouped
+ncclSend/ncclRecv on NCCL, plain send/recv on gloo for the CPU tests).  Peers' data always lands in local
+memory through the collective before a kernel reads it.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib, ops
+
+
+def padded_heads(n_heads: int, world: int) -> int:
+    """Heads padded up to a multiple of the world size."""
+    return (n_heads + world - 1) // world * world
+
+
+def _exchange(send_blocks: List[Optional[torch.Tensor]], recv_blocks: List[Optional[torch.Tensor]], group, async_op: bool):
+    """Send ``send_blocks[p]`` to rank p and receive ``recv_blocks[p]`` from rank p (lists of lists of
+    contiguous tensors); the local block is copied.  Returns the list of outstanding requests."""
+    rank = dist.get_rank(group)
+    world = dist.get_world_size(group)
+    ops_list = []
+    for off in range(1, world):
+        dst = (rank + off) % world
+        src = (rank - off) % world
+        for t in send_blocks[dst]:
+            ops_list.append(dist.P2POp(dist.isend, t, dist.get_global_rank(group, dst) if group is not None else dst, group))
+        for t in recv_blocks[src]:
+            ops_list.append(dist.P2POp(dist.irecv, t, dist.get_global_rank(group, src) if group is not None else src, group))
+    for s, r in zip(send_blocks[rank], recv_blocks[rank]):
+        r.copy_(s)
+    reqs = dist.batch_isend_irecv(ops_list) if ops_list else []
+    if not async_op:
+        for r in reqs:
+            r.wait()
+        return []
+    return reqs
+
+
+def seq_to_head(x_hm: torch.Tensor, group=None, async_op: bool = False):
+    """``x_hm [Hp, Ls, C]`` head-major local shard (all padded heads, local tokens) ->
+    ``[Hp/P, P*Ls, C]`` (local heads, every token).  Returns ``(out, requests)``."""
+    world = dist.get_world_size(group)
+    Hp, Ls, Cc = x_hm.shape
+    if Hp % world:
+        raise ValueError(f"heads {Hp} not a multiple of world size {world}; pad first")
+    hp = Hp // world
+    out = torch.empty(hp, world * Ls, Cc, dtype=x_hm.dtype, device=x_hm.device)
+    send = [[x_hm[p * hp + j] for j in range(hp)] for p in range(world)]
+    recv = [[out[j, p * Ls : (p + 1) * Ls] for j in range(hp)] for p in range(world)]
+    return out, _exchange(send, recv, group, async_op)
+
+
+def head_to_seq(o_hm: torch.Tensor, group=None, async_op: bool = False):
+    """Inverse of :func:`seq_to_head`: ``o_hm [Hp/P, P*Ls, C]`` -> ``[Hp, Ls, C]``."""
+    world = dist.get_world_size(group)
+    hp, L, Cc = o_hm.shape
+    if L % world:
+        raise ValueError("sequence length not a multiple of world size")
+    Ls = L // world
+    out = torch.empty(hp * world, Ls, Cc, dtype=o_hm.dtype, device=o_hm.device)
+    send = [[o_hm[j, p * Ls : (p + 1) * Ls] for j in range(hp)] for p in range(world)]
+    recv = [[out[p * hp + j] for j in range(hp)] for p in range(world)]
+    return out, _exchange(send, recv, group, async_op)
+
+
+def scales_seq_to_head(s: torch.Tensor, group=None) -> torch.Tensor:
+    """FP8 block scales ``[Hp, nb_local]`` -> ``[Hp/P, P*nb_local]`` (needs Ls % 128 == 0 so that blocks do
+    not straddle ranks)."""
+    out, _ = seq_to_head(s[:, :, None].contiguous(), group)
+    return out[:, :, 0].contiguous()
+
+
+def _pad_heads_hm(x_hm: torch.Tensor, Hp: int) -> torch.Tensor:
+    if x_hm.shape[0] == Hp:
+        return x_hm
+    pad = x_hm.new_zeros(Hp - x_hm.shape[0], *x_hm.shape[1:])
+    return torch.cat([x_hm, pad], dim=0)
+
+
+class UlyssesAttention:
+    """Sequence-parallel joint attention.  ``__call__(q, k, v, rope)`` takes this rank's ``[L/P, H, 128]``
+    bf16 projections and rotary table rows and returns this rank's ``[L/P, H, 128]`` output.
+
+    ``prep_fn(q, k, q_rope, k_rope, fp8) -> (q', k', q_scale, k_scale)`` and
+    ``attn_fn(q, k, v, mode, q_scale, k_scale, block_index)`` default to the CUDA library; the CPU tests
+    inject host stand-ins to exercise the reshard logic with gloo ranks.
+    """
+
+    def __init__(self, group=None, mode: int = _lib.MODE_DENSE_BF16, block_index: Optional[ops.BlockIndex] = None,
+                 prep_fn: Optional[Callable] = None, attn_fn: Optional[Callable] = None,
+                 to_head_major: Optional[Callable] = None):
+        self.group = group
+        self.mode = mode
+        self.block_index = block_index
+        self.prep_fn = prep_fn or self._cuda_prep
+        self.attn_fn = attn_fn or self._cuda_attn
+        self.to_head_major = to_head_major or (lambda v: v.permute(1, 0, 2).contiguous())
+
+    @staticmethod
+    def _cuda_prep(q, k, q_rope, k_rope, fp8):
+        return ops.qk_prep(q, k, q_rope, k_rope, fp8=fp8)
+
+    @staticmethod
+    def _cuda_attn(q, k, v, mode, q_scale, k_scale, block_index):
+        # head-major output so that the return exchange sends contiguous [L/P, 128] blocks without a copy
+        out = torch.empty(q.shape[1], q.shape[0], ops.HEAD_DIM, dtype=torch.bfloat16, device=q.device).permute(1, 0, 2)
+        return ops.attn_fwd(q, k, v, mode, q_scale, k_scale, block_index, out=out)
+
+    def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rope: Optional[torch.Tensor]) -> torch.Tensor:
+        world = dist.get_world_size(self.group)
+        Ls, H, _ = q.shape
+        fp8 = self.mode == _lib.MODE_FP8_QK
+        if fp8 and Ls % ops.TILE:
+            raise ValueError("FP8 mode under Ulysses needs the local sequence length to be a multiple of 128")
+        Hp = padded_heads(H, world)
+        # token-local work first: the wire then carries final operands
+        qp, kp, qs, ks = self.prep_fn(q, k, rope, rope, fp8)
+        # prepared tensors are logical [Ls, H, C] views of head-major storage
+        q_hm = _pad_heads_hm(qp.permute(1, 0, 2).contiguous(), Hp)
+        k_hm = _pad_heads_hm(kp.permute(1, 0, 2).contiguous(), Hp)
+        qh, rq = seq_to_head(q_hm, self.group, async_op=True)
+        kh, rk = seq_to_head(k_hm, self.group, async_op=True)
+        v_hm = _pad_heads_hm(self.to_head_major(v), Hp)  # overlaps the Q/K exchanges
+        vh, rv = seq_to_head(v_hm, self.group, async_op=True)
+        qsh = ksh = None
+        if fp8:
+            qsh = scales_seq_to_head(_pad_heads_hm(qs, Hp), self.group)
+            ksh = scales_seq_to_head(_pad_heads_hm(ks, Hp), self.group)
+        for r in rq + rk + rv:
+            r.wait()
+        oh = self.attn_fn(qh.permute(1, 0, 2), kh.permute(1, 0, 2), vh.permute(1, 0, 2), self.mode, qsh, ksh, self.block_index)
+        o_hm, _ = head_to_seq(oh.permute(1, 0, 2).contiguous(), self.group)
+        return o_hm[:H].permute(1, 0, 2)

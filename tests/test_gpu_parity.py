@@ -1,0 +1,314 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU oracle on the same seeded inputs.
+
+Tolerances (bf16 modes, vs the fp32 oracle on the same bf16-rounded inputs): max-abs <= 2e-2,
+mean-abs <= 2e-3, and additionally rel-L2 <= 1e-2.  FP8-QK vs the fp32 dense result: max-abs <= 3e-2,
+mean-abs <= 3e-3, rel-L2 <= 6e-2 at L >= 4096; vs the oracle run on the SAME quantised operands the bf16
+bounds apply.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+BF16_MAX, BF16_MEAN, BF16_REL = 2e-2, 2e-3, 1e-2
+FP8_MAX, FP8_MEAN, FP8_REL = 3e-2, 3e-3, 6e-2
+
+
+@pytest.fixture(scope="module")
+def h(lib):
+    import pika_h3_flex_b200 as pkg
+
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return pkg
+
+
+def dev(x):
+    return x.to("cuda")
+
+
+def check(out, ref, mx=BF16_MAX, mean=BF16_MEAN, rel=BF16_REL):
+    st = O.error_stats(out.float().cpu(), ref)
+    assert st["max_abs"] <= mx and st["mean_abs"] <= mean and st["rel_l2"] <= rel, st
+    return st
+
+
+def bf16_inputs(L, H, seed, Lk=None):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(L, H, 128, generator=g).bfloat16()
+    k = torch.randn(Lk or L, H, 128, generator=g).bfloat16()
+    v = torch.randn(Lk or L, H, 128, generator=g).bfloat16()
+    return q, k, v
+
+
+# ------------------------------------------------------------------------------------------ preparation
+def test_rope_table_matches_oracle(h):
+    pos = O.make_positions((5, 6, 7), 300)
+    tab = h.rope_table(dev(pos)).cpu().double()
+    cos, sin = O.rope_table(pos)
+    assert float((tab[..., 0] - cos).abs().max()) < 2e-7 and float((tab[..., 1] - sin).abs().max()) < 2e-7
+
+
+@pytest.mark.parametrize("L,H,half,weights", [(70, 2, False, False), (300, 3, False, True), (300, 3, True, False), (129, 1, True, True)])
+def test_qk_prep_bf16(h, L, H, half, weights):
+    q, k, _ = bf16_inputs(L, H, 21)
+    pos = O.make_positions((L // 35, 5, 7), L - (L // 35) * 35)
+    cos, sin = O.rope_table(pos)
+    g = torch.Generator().manual_seed(5)
+    qw = (1 + 0.1 * torch.randn(128, generator=g)) if weights else None
+    kw = (1 + 0.1 * torch.randn(128, generator=g)) if weights else None
+    qo, ko = O.qk_prep(q.float(), k.float(), cos, sin, qw, kw, interleaved=not half)
+    tab = h.rope_table(dev(pos))
+    qp, kp, qs, ks = h.qk_prep(dev(q), dev(k), tab, tab, None if qw is None else dev(qw), None if kw is None else dev(kw), rope_half=half)
+    assert qs is None and ks is None and qp.shape == q.shape
+    # outputs are the bf16 rounding of the fp32 oracle (values up to ~4: half an ulp is 0.0078)
+    for got, want in ((qp, qo), (kp, ko)):
+        d = (got.float().cpu() - want).abs()
+        assert float(d.max()) <= 1.6e-2 and float(d.mean()) <= 2e-3
+        assert float((got.float().cpu() != want.bfloat16().float()).float().mean()) < 0.02  # rounding ties only
+
+
+def test_qk_prep_strided_input_and_no_rope(h):
+    L, H = 200, 4
+    q, k, _ = bf16_inputs(L, H, 22)
+    qkv = torch.randn(L, 3, H, 128).bfloat16()
+    qkv[:, 0], qkv[:, 1] = q, k
+    qkv_d = dev(qkv)
+    qp, kp, _, _ = h.qk_prep(qkv_d[:, 0], qkv_d[:, 1])  # views into a fused QKV buffer, no rotation
+    assert float((qp.float().cpu() - O.rms_norm(q.float())).abs().max()) <= 1.6e-2
+    assert float((kp.float().cpu() - O.rms_norm(k.float())).abs().max()) <= 1.6e-2
+
+
+def test_qk_prep_fp8(h):
+    L, H = 300, 3
+    q, k, _ = bf16_inputs(L, H, 23)
+    pos = O.make_positions((8, 5, 7), 20)
+    cos, sin = O.rope_table(pos)
+    qo, ko = O.qk_prep(q.float(), k.float(), cos, sin)
+    tab = h.rope_table(dev(pos))
+    qp, kp, qs, ks = h.qk_prep(dev(q), dev(k), tab, tab, fp8=True)
+    for got, sc, want in ((qp, qs, qo), (kp, ks, ko)):
+        wq, ws = O.quantize_e4m3_blocks(want)
+        assert float((sc.cpu() - ws).abs().max() / ws.max()) < 1e-5
+        codes = got.view(torch.float8_e4m3fn).float().cpu()
+        assert float((codes != wq).float().mean()) < 5e-3  # fp32 rounding of the pre-quantisation value
+        assert float((codes - wq).abs().max()) <= 32.0      # never more than one code step
+
+
+# ------------------------------------------------------------------------------------------ attention
+@pytest.mark.parametrize(
+    "L,Lk,H",
+    [(128, 128, 1), (1, 1, 1), (100, 37, 2), (256, 256, 1), (300, 300, 2), (512, 512, 2), (1000, 1500, 3), (385, 129, 2), (257, 1024, 1)],
+)
+def test_dense_attention_shapes(h, L, Lk, H):
+    q, k, v = bf16_inputs(L, H, 100 + L + Lk, Lk)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out, lse = h.attn_fwd(dev(q), dev(k), dev(v), return_lse=True, status_word=status)
+    ref, ref_lse = O.attention(q.float(), k.float(), v.float(), return_lse=True)
+    assert h.read_status(status) == 0
+    check(out, ref, mx=3e-2 if Lk < 256 else BF16_MAX, mean=4e-3 if Lk < 256 else BF16_MEAN)
+    assert float((lse.cpu().t() - ref_lse).abs().max()) < 2e-3
+
+
+def test_dense_attention_head_major_views_and_out_buffer(h):
+    L, H = 640, 3
+    q, k, v = bf16_inputs(L, H, 31)
+    qd = dev(q.permute(1, 0, 2).contiguous()).permute(1, 0, 2)
+    kd = dev(k.permute(1, 0, 2).contiguous()).permute(1, 0, 2)
+    out = torch.full((H, L + 2, 128), 7.0, dtype=torch.bfloat16, device="cuda")  # canary rows around the output
+    h.attn_fwd(qd, kd, dev(v), out=out[:, 1 : L + 1].permute(1, 0, 2))
+    check(out[:, 1 : L + 1].permute(1, 0, 2), O.attention(q.float(), k.float(), v.float()))
+    assert float((out[:, 0].float() - 7).abs().max()) == 0 and float((out[:, L + 1].float() - 7).abs().max()) == 0
+
+
+def test_dense_attention_large_logits_trigger_rescale(h):
+    # keys ordered so that the running maximum keeps growing tile after tile
+    L, H = 1024, 1
+    q, k, v = bf16_inputs(L, H, 33)
+    k = (k.float() * torch.linspace(0.2, 6.0, L)[:, None, None]).bfloat16()
+    out = h.attn_fwd(dev(q), dev(k), dev(v))
+    check(out, O.attention(q.float(), k.float(), v.float()), mx=6e-2, mean=6e-3, rel=2e-2)
+
+
+def test_softmax_scale_argument(h):
+    q, k, v = bf16_inputs(256, 2, 34)
+    out = h.attn_fwd(dev(q), dev(k), dev(v), softmax_scale=0.05)
+    check(out, O.attention(q.float(), k.float(), v.float(), scale=0.05))
+
+
+@pytest.mark.parametrize("L,H", [(512, 2), (1000, 2), (130, 1)])
+def test_fp8_attention_on_quantised_operands(h, L, H):
+    q, k, v = bf16_inputs(L, H, 40 + L)
+    qq, sq = O.quantize_e4m3_blocks(q.float())
+    kq, sk = O.quantize_e4m3_blocks(k.float())
+    ref = O.attention(O.dequantize_blocks(qq, sq), O.dequantize_blocks(kq, sk), v.float())
+    qd = dev(qq.to(torch.float8_e4m3fn).view(torch.uint8).permute(1, 0, 2).contiguous()).permute(1, 0, 2)
+    kd = dev(kq.to(torch.float8_e4m3fn).view(torch.uint8).permute(1, 0, 2).contiguous()).permute(1, 0, 2)
+    out = h.attn_fwd(qd, kd, dev(v), h.MODE_FP8_QK, dev(sq), dev(sk))
+    check(out, ref)
+
+
+def sparse_case(grid, n_audio, window, H, seed):
+    keep = O.neighbourhood_block_mask(grid, n_audio, window)
+    csr = O.mask_to_csr(keep)
+    L = n_audio + grid[0] * grid[1] * grid[2]
+    q, k, v = bf16_inputs(L, H, seed)
+    return q, k, v, csr, keep
+
+
+@pytest.mark.parametrize("grid,n_audio,window", [((4, 10, 20), 128, (1, 2, 3)), ((6, 8, 16), 256, (1, 1, 2)), ((5, 9, 14), 100, (0, 2, 2))])
+def test_block_sparse_attention(h, grid, n_audio, window):
+    q, k, v, csr, keep = sparse_case(grid, n_audio, window, 2, 50)
+    bi = h.BlockIndex.from_csr(csr[0], csr[1], keep.shape[1]).to("cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = h.attn_fwd(dev(q), dev(k), dev(v), h.MODE_BLOCK_SPARSE, block_index=bi, status_word=status)
+    assert h.read_status(status) == 0
+    check(out, O.attention(q.float(), k.float(), v.float(), csr=csr))
+    # the library's own builder gives the same index
+    bi2 = h.build_block_index(grid, n_audio, window)
+    assert torch.equal(bi2.row_ptr, bi.row_ptr.cpu()) and torch.equal(bi2.col_idx, bi.col_idx.cpu())
+
+
+def test_block_sparse_rows_with_disjoint_lists_and_empty_row(h):
+    # hand-made index: neighbouring query tiles with different key lists, one query tile with none
+    L = 5 * 128
+    q, k, v = bf16_inputs(L, 1, 51)
+    rows = [[0, 1, 2, 3, 4], [1], [], [0, 4], [2, 3]]
+    rp = np.cumsum([0] + [len(r) for r in rows]).astype(np.int32)
+    ci = np.array([c for r in rows for c in r], dtype=np.int32)
+    bi = h.BlockIndex.from_csr(rp, ci, 5).to("cuda")
+    out = h.attn_fwd(dev(q), dev(k), dev(v), h.MODE_BLOCK_SPARSE, block_index=bi).float().cpu()
+    ref = O.attention(q.float(), k.float(), v.float(), csr=(rp, ci))
+    assert float(out[256:384].abs().max()) == 0.0  # no key tile listed -> zero rows
+    keep_rows = torch.cat([torch.arange(0, 256), torch.arange(384, L)])
+    check(out[keep_rows], ref[keep_rows])
+
+
+# ------------------------------------------------------------------------------------------ whole path
+def test_joint_path_on_golden_fixture(h, golden_dir):
+    g = dict(np.load(os.path.join(golden_dir, "small_joint.npz")))
+    q, k, v = (torch.from_numpy(g[n]).bfloat16() for n in "qkv")
+    tab = h.rope_table(dev(torch.from_numpy(g["pos"])))
+    for tag, half in (("inter", False), ("half", True)):
+        out = h.joint_attention(dev(q), dev(k), dev(v), tab, rope_half=half)
+        check(out, torch.from_numpy(g[f"dense_{tag}"]), mx=4e-2, mean=5e-3, rel=1.5e-2)  # 96 keys: outputs ~10x larger
+    out8 = h.joint_attention(dev(q), dev(k), dev(v), tab, h.MODE_FP8_QK)
+    st = O.error_stats(out8.float().cpu(), torch.from_numpy(g["dense_inter"]))
+    assert st["rel_l2"] <= FP8_REL
+
+
+@pytest.fixture(scope="module")
+def cfg0():
+    grid, n_audio, H, seed = O.CONFIGS["cfg0"]
+    L = n_audio + grid[0] * grid[1] * grid[2]
+    q, k, v = O.seeded_qkv(L, H, seed=seed)
+    q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    pos = O.make_positions(grid, n_audio)
+    ref = O.joint_attention(q.float(), k.float(), v.float(), pos, "dense")
+    return q, k, v, pos, ref
+
+
+def test_config0_dense(h, cfg0):
+    q, k, v, pos, ref = cfg0
+    out = h.joint_attention(dev(q), dev(k), dev(v), h.rope_table(dev(pos)))
+    st = check(out, ref)
+    assert st["rel_l2"] < 5e-3
+
+
+def test_config0_fp8_within_stated_bounds(h, cfg0):
+    q, k, v, pos, ref = cfg0
+    out = h.joint_attention(dev(q), dev(k), dev(v), h.rope_table(dev(pos)), h.MODE_FP8_QK)
+    check(out, ref, FP8_MAX, FP8_MEAN, FP8_REL)
+    ref8 = O.joint_attention(q.float(), k.float(), v.float(), pos, "fp8_qk")
+    check(out, ref8)  # against the oracle on quantised operands: bf16 bounds
+
+
+def test_config0_block_sparse(h, cfg0):
+    q, k, v, pos, _ = cfg0
+    grid = O.CONFIGS["cfg0"][0]
+    bi = h.build_block_index(grid, 0, (1, 8, 8))
+    csr = (bi.row_ptr.numpy(), bi.col_idx.numpy())
+    assert 0.3 < bi.density < 1.0
+    out = h.joint_attention(dev(q), dev(k), dev(v), h.rope_table(dev(pos)), h.MODE_BLOCK_SPARSE, bi.to("cuda"))
+    check(out, O.joint_attention(q.float(), k.float(), v.float(), pos, "block_sparse", csr=csr))
+
+
+# ------------------------------------------------------------------------------------------ full-size properties
+def _full_inputs(name, H):
+    grid, n_audio, _, seed = O.CONFIGS[name]
+    L = n_audio + grid[0] * grid[1] * grid[2]
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q = torch.randn(L, H, 128, device="cuda", generator=g).bfloat16()
+    k = torch.randn(L, H, 128, device="cuda", generator=g).bfloat16()
+    v = torch.randn(L, H, 128, device="cuda", generator=g).bfloat16()
+    return grid, n_audio, L, q, k, v
+
+
+def test_config1_full_length_properties(h):
+    """480p-like length (49,384 tokens, tail tile of 104), 8 of the 40 heads to bound host time."""
+    H = 8
+    grid, n_audio, L, q, k, v = _full_inputs("cfg1", H)
+    pos = O.make_positions(grid, n_audio)
+    tab = h.rope_table(dev(pos))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    qp, kp, _, _ = h.qk_prep(q, k, tab, tab)
+    out, lse = h.attn_fwd(qp, kp, v, return_lse=True, status_word=status)
+    assert h.read_status(status) == 0
+    # (1) sampled query rows against the fp64 oracle
+    rows = torch.cat([torch.arange(0, L, 997), torch.tensor([L - 1, L - 104, L - 105, 1023, 1024])])
+    hs = [0, H - 1]
+    qo, ko = O.qk_prep(q[:, hs].cpu().double(), k[:, hs].cpu().double(), *O.rope_table(pos))
+    ref = O.attention(qo, ko, v[:, hs].cpu().double(), q_rows=rows)
+    check(out[rows][:, hs], ref.float())
+    # (2) softmax rows sum to one: with V = 1 every output element is 1
+    ones = torch.ones_like(v)
+    o1 = h.attn_fwd(qp, kp, ones)
+    assert float((o1.float() - 1).abs().max()) <= 8e-3
+    # (3) key order does not matter: permute K and V rows together
+    perm = torch.randperm(L, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    kperm = kp.permute(1, 0, 2)[:, perm].contiguous().permute(1, 0, 2)
+    o2, lse2 = h.attn_fwd(qp, kperm, v[perm].contiguous(), return_lse=True)
+    assert float((o2.float() - out.float()).abs().max()) <= 4e-3
+    assert float((lse2 - lse).abs().max()) <= 1e-3
+    # (4) linear in V
+    o3 = h.attn_fwd(qp, kp, (2 * v).contiguous())
+    assert float((o3.float() - 2 * out.float()).abs().max()) <= 8e-3
+
+
+def test_config3_full_length_block_sparse_properties(h):
+    """768p-like length (126,016 tokens), literal neighbourhood rule (7.2 % of tiles), 2 heads."""
+    H = 2
+    grid, n_audio, L, q, k, v = _full_inputs("cfg3", H)
+    bi = h.build_block_index(grid, n_audio, (2, 8, 8))
+    bid = bi.to("cuda")
+    pos = O.make_positions(grid, n_audio)
+    tab = h.rope_table(dev(pos))
+    qp, kp, _, _ = h.qk_prep(q, k, tab, tab)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = h.attn_fwd(qp, kp, v, h.MODE_BLOCK_SPARSE, block_index=bid, status_word=status)
+    assert h.read_status(status) == 0
+    rows = torch.cat([torch.arange(0, L, 4099), torch.tensor([L - 1, 1023, 1024, 1151, 1152])])
+    qo, ko = O.qk_prep(q.cpu().double(), k.cpu().double(), *O.rope_table(pos))
+    ref = O.attention(qo, ko, v.cpu().double(), csr=(bi.row_ptr.numpy(), bi.col_idx.numpy()), q_rows=rows)
+    check(out[rows], ref.float(), mx=3e-2, mean=3e-3)
+    o1 = h.attn_fwd(qp, kp, torch.ones_like(v), h.MODE_BLOCK_SPARSE, block_index=bid)
+    assert float((o1.float() - 1).abs().max()) <= 8e-3
+
+
+# ------------------------------------------------------------------------------------------ errors
+def test_errors_are_reported_not_swallowed(h):
+    q, k, v = (dev(x) for x in bf16_inputs(256, 2, 60))
+    with pytest.raises(ValueError):
+        h.attn_fwd(q, k[:, :1], v)
+    with pytest.raises(h.H3AError) as e:
+        h.attn_fwd(q[:, :, :128][:, :, :].as_strided((256, 2, 128), (260, 130, 1)), k, v)
+    assert e.value.status == h._lib.H3A_ERR_ALIGN
+    with pytest.raises(ValueError):
+        h.attn_fwd(q, k, v, h.MODE_BLOCK_SPARSE)
+    with pytest.raises(ValueError):
+        h.attn_fwd(q, k, v, h.MODE_FP8_QK)

@@ -1,0 +1,133 @@
+"""GPU: the processor call shape on a stand-in attention module (LoRA-wrapped projections named as the
+reference's DEFAULT_LORA_TARGETS, src/pika_h3/core/loader.py:9) against the oracle."""
+import pytest
+import torch
+import torch.nn as nn
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+class LoraLinear(nn.Module):
+    """base Linear + (alpha/r) B A, the structure PEFT gives to_q/to_k/to_v/to_out.0 (rank = alpha = 128 in
+    the reference, src/pika_h3/pipeline.py:34; smaller here)."""
+
+    def __init__(self, din, dout, r=8):
+        super().__init__()
+        self.base = nn.Linear(din, dout, bias=True)
+        self.A = nn.Linear(din, r, bias=False)
+        self.B = nn.Linear(r, dout, bias=False)
+
+    def forward(self, x):
+        return self.base(x) + self.B(self.A(x))
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, d, eps=1e-6):
+        super().__init__()
+        self.weight = nn.Parameter(1 + 0.1 * torch.randn(d))
+        self.eps = eps
+
+
+class StubAttention(nn.Module):
+    def __init__(self, dim, heads, ctx_dim=None):
+        super().__init__()
+        self.heads = heads
+        inner = heads * 128
+        self.to_q = LoraLinear(dim, inner)
+        self.to_k = LoraLinear(ctx_dim or dim, inner)
+        self.to_v = LoraLinear(ctx_dim or dim, inner)
+        self.to_out = nn.ModuleList([LoraLinear(inner, dim), nn.Dropout(0.0)])
+        self.norm_q = RMSNorm(128)
+        self.norm_k = RMSNorm(128)
+
+
+def oracle_forward(attn, x, ctx, pos, mode="dense", csr=None):
+    H = attn.heads
+    src = x if ctx is None else ctx
+    q = attn.to_q(x).view(-1, H, 128).float().cpu()
+    k = attn.to_k(src).view(-1, H, 128).float().cpu()
+    v = attn.to_v(src).view(-1, H, 128).float().cpu()
+    qw, kw = attn.norm_q.weight.float().cpu(), attn.norm_k.weight.float().cpu()
+    if ctx is None:
+        o = O.joint_attention(q, k, v, pos, mode, csr=csr, q_weight=qw, k_weight=kw)
+    else:
+        o = O.attention(O.rms_norm(q, qw), O.rms_norm(k, kw), v)
+    o = o.reshape(1, x.shape[1], -1).to(x)
+    return attn.to_out[0](o)
+
+
+@pytest.fixture(scope="module")
+def setup(lib):
+    assert torch.cuda.is_available()
+    torch.manual_seed(3)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    attn = StubAttention(256, 2).cuda().bfloat16()
+    grid, n_audio = (4, 8, 8), 64
+    pos = O.make_positions(grid, n_audio)
+    x = torch.randn(1, pos.shape[0], 256, device="cuda").bfloat16()
+    return attn, x, pos, grid, n_audio
+
+
+@torch.no_grad()
+def test_self_attention_with_position_ids(setup):
+    from pika_h3_flex_b200.processor import B200AttnProcessor
+
+    attn, x, pos, _, _ = setup
+    proc = B200AttnProcessor()
+    y = proc(attn, x, position_ids=pos.cuda(), token_tags=None, timestep_indices=None)  # extra kwargs pass through
+    ref = oracle_forward(attn, x, None, pos)
+    assert y.shape == x.shape and y.dtype == x.dtype
+    assert float((y.float() - ref.float()).abs().max()) < 3e-2
+    # the table is cached per position tensor
+    assert len(proc._rope_cache._d) == 1
+    proc(attn, x, position_ids=pos.cuda())
+    assert len(proc._rope_cache._d) == 2  # a new tensor object is a new key
+
+
+@torch.no_grad()
+def test_self_attention_with_cos_sin_tuple_and_modes(setup):
+    from pika_h3_flex_b200 import build_block_index
+    from pika_h3_flex_b200.processor import B200AttnProcessor
+
+    attn, x, pos, grid, n_audio = setup
+    cos, sin = O.rope_table(pos)
+    full = (cos.float().repeat_interleave(2, dim=1).cuda(), sin.float().repeat_interleave(2, dim=1).cuda())
+    ref = oracle_forward(attn, x, None, pos)
+    y = B200AttnProcessor()(attn, x, image_rotary_emb=full)
+    assert float((y.float() - ref.float()).abs().max()) < 3e-2
+    y8 = B200AttnProcessor("fp8_qk")(attn, x, image_rotary_emb=(cos.float().cuda(), sin.float().cuda()))
+    assert float(((y8.float() - ref.float()).norm() / ref.float().norm())) < 8e-2
+    bi = build_block_index(grid, n_audio, (1, 2, 2))
+    ys = B200AttnProcessor("block_sparse", bi.to("cuda"))(attn, x, position_ids=pos.cuda())
+    refs = oracle_forward(attn, x, None, pos, "block_sparse", (bi.row_ptr.numpy(), bi.col_idx.numpy()))
+    assert float((ys.float() - refs.float()).abs().max()) < 3e-2
+
+
+@torch.no_grad()
+def test_cross_attention_to_text_tokens(setup):
+    from pika_h3_flex_b200.processor import B200AttnProcessor
+
+    _, x, _, _, _ = setup
+    torch.manual_seed(4)
+    attn = StubAttention(256, 2, ctx_dim=512).cuda().bfloat16()
+    text = torch.randn(1, 77, 512, device="cuda").bfloat16()
+    y = B200AttnProcessor()(attn, x, encoder_hidden_states=text)
+    ref = oracle_forward(attn, x, text, None)
+    assert float((y.float() - ref.float()).abs().max()) < 3e-2
+
+
+def test_processor_rejects_what_it_cannot_do(setup):
+    from pika_h3_flex_b200.processor import B200AttnProcessor
+
+    attn, x, pos, _, _ = setup
+    proc = B200AttnProcessor()
+    with pytest.raises(NotImplementedError):
+        proc(attn, x, attention_mask=torch.ones(1, 1, device="cuda"))
+    with pytest.raises(ValueError):
+        proc(attn, torch.cat([x, x]), position_ids=pos.cuda())
+    with pytest.raises(RuntimeError):
+        proc(attn, x.cpu(), position_ids=pos)
+    with pytest.raises(ValueError):
+        B200AttnProcessor("block_sparse")

@@ -1,0 +1,111 @@
+"""CPU ranks (gloo): the Ulysses reshard logic — head padding, seq->head and head->seq exchanges, FP8
+scale resharding — against the single-process oracle.  The CUDA prep/attention calls are replaced by
+oracle stand-ins here; the GPU tests cover the real kernels."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import oracle as O
+from pika_h3_flex_b200 import _lib
+from pika_h3_flex_b200.ulysses import UlyssesAttention, head_to_seq, padded_heads, seq_to_head
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _cpu_prep(q, k, q_rope, k_rope, fp8):
+    cos, sin = (q_rope[..., 0].double(), q_rope[..., 1].double()) if q_rope is not None else (None, None)
+    qp, kp = (O.qk_prep(q, k, cos, sin) if cos is not None else (O.rms_norm(q), O.rms_norm(k)))
+    if not fp8:
+        return qp, kp, None, None
+    qq, sq = O.quantize_e4m3_blocks(qp)
+    kq, sk = O.quantize_e4m3_blocks(kp)
+    return qq, kq, sq, sk
+
+
+def _cpu_attn(q, k, v, mode, q_scale, k_scale, block_index):
+    if mode == _lib.MODE_FP8_QK:
+        q, k = O.dequantize_blocks(q, q_scale), O.dequantize_blocks(k, k_scale)
+    csr = None
+    if mode == _lib.MODE_BLOCK_SPARSE:
+        csr = (block_index.row_ptr.numpy(), block_index.col_idx.numpy())
+    return O.attention(q, k, v, csr=csr)
+
+
+def _worker(rank, world, port, H, L, mode, result_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)
+        q, k, v = O.seeded_qkv(L, H, seed=77)
+        pos = O.make_positions((L // 16, 4, 4), L - (L // 16) * 16)
+        cos, sin = O.rope_table(pos)
+        rope = torch.stack([cos, sin], dim=-1).float()
+        Ls = L // world
+        sl = slice(rank * Ls, (rank + 1) * Ls)
+        bi = None
+        if mode == _lib.MODE_BLOCK_SPARSE:
+            from pika_h3_flex_b200.ops import BlockIndex
+
+            keep = O.neighbourhood_block_mask((L // 16, 4, 4), L - (L // 16) * 16, (1, 1, 1))
+            bi = BlockIndex.from_csr(*O.mask_to_csr(keep), n_k_tiles=keep.shape[1])
+        ua = UlyssesAttention(None, mode, bi, prep_fn=_cpu_prep, attn_fn=_cpu_attn)
+        out = ua(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), rope[sl].contiguous())
+        # raw exchange round trip
+        x = torch.arange(padded_heads(H, world) * Ls * 4, dtype=torch.float32).view(-1, Ls, 4) + 1000 * rank
+        y, _ = seq_to_head(x)
+        z, _ = head_to_seq(y)
+        torch.save({"out": out.clone(), "roundtrip": bool(torch.equal(x, z)), "y": y}, os.path.join(result_dir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(world, H, L, mode, tmp_path):
+    mp.spawn(_worker, args=(world, _free_port(), H, L, mode, str(tmp_path)), nprocs=world, join=True)
+    res = [torch.load(os.path.join(tmp_path, f"r{r}.pt")) for r in range(world)]
+    q, k, v = O.seeded_qkv(L, H, seed=77)
+    pos = O.make_positions((L // 16, 4, 4), L - (L // 16) * 16)
+    csr = None
+    if mode == _lib.MODE_BLOCK_SPARSE:
+        csr = O.mask_to_csr(O.neighbourhood_block_mask((L // 16, 4, 4), L - (L // 16) * 16, (1, 1, 1)))
+    ref = O.joint_attention(q, k, v, pos, {0: "dense", 1: "fp8_qk", 2: "block_sparse"}[mode], csr=csr)
+    out = torch.cat([r["out"] for r in res], dim=0)
+    assert out.shape == ref.shape
+    assert all(r["roundtrip"] for r in res)
+    return out, ref, res
+
+
+@pytest.mark.parametrize("world,H", [(2, 4), (2, 3), (4, 6)])
+def test_ulysses_dense_matches_single_rank(world, H, tmp_path):
+    out, ref, res = _run(world, H, 256, _lib.MODE_DENSE_BF16, tmp_path)
+    assert float((out - ref).abs().max()) < 1e-5
+    # after seq->head rank r holds heads [r*hp, (r+1)*hp) of every source rank's tokens, in rank order
+    hp = padded_heads(H, world) // world
+    Ls = 256 // world
+    y1 = res[1]["y"]
+    assert y1.shape == (hp, world * Ls, 4)
+    for src in range(world):
+        assert float(y1[0, src * Ls, 0]) == 1000 * src + (1 * hp) * Ls * 4
+
+
+def test_ulysses_fp8_scales_follow_their_blocks(tmp_path):
+    out, ref, _ = _run(2, 4, 512, _lib.MODE_FP8_QK, tmp_path)
+    assert float((out - ref).abs().max()) < 1e-5
+
+
+def test_ulysses_block_sparse(tmp_path):
+    out, ref, _ = _run(2, 2, 512, _lib.MODE_BLOCK_SPARSE, tmp_path)
+    assert float((out - ref).abs().max()) < 1e-5
+
+
+def test_ulysses_rejects_bad_shapes():
+    assert padded_heads(40, 8) == 40 and padded_heads(6, 4) == 8 and padded_heads(1, 8) == 8
