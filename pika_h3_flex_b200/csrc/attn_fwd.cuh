@@ -2,16 +2,20 @@
 // staged by TMA through a multi-buffered shared-memory ring, warp-specialised roles.
 //
 // One CTA owns a PAIR of 128-row query tiles of one head (two "streams") and walks the key tiles:
-//   warp 8   producer : TMA loads of Q (once) and of K_j, V_j into a ring of 32 KB stages
-//   warp 9   issuer   : one thread issues  S_t = Q_t K_j^T  (SS MMA) and  O_t += P_t V_j  (TS MMA, P read
-//                       from TMEM); tcgen05.commit signals mbarriers
+//   warp 8   producer : TMA loads of Q (once) and of K_j, V_j (128 keys each) into a ring of 32 KB stages
+//   warp 9   issuer   : one thread issues  S = Q_t K^T  (SS MMA, N = 64 keys) and  O_t += P V  (TS MMA, P
+//                       read from TMEM, K = 64 keys); tcgen05.commit signals mbarriers
 //   warps 0-3 / 4-7   : softmax of stream 0 / 1, one query row per thread (TMEM lane == row): online
 //                       max / exp2 / sum, P written back over S as packed bf16, lazy rescale of O
 //                       (only when the running max grows by more than 2^8), final 1/l and store.
-// The two streams ping-pong so that the tensor pipe works on one stream while the other is in softmax.
+// Each 128-key tile is processed as two 64-key halves with their own S buffer, so each stream has two
+// S/P buffers in flight: while the softmax warps work on one half, the tensor pipe already produces the
+// next S into the other buffer (after the P V that frees it), and the two streams interleave on top.
 // K_j and V_j are fetched once per 256 query rows.
 //
-// TMEM (512 columns x 128 lanes, fp32):  [0,128) S0/P0   [128,256) S1/P1   [256,384) O0   [384,512) O1
+// TMEM (512 columns x 128 lanes, fp32):
+//   stream t: S/P buffer h at columns [128 t + 64 h, +64) (P = packed bf16 in its first 32 columns)
+//   O_t at columns [256 + 128 t, +128)
 //
 // Every wait on an mbarrier is bounded: when the time limit runs out the CTA records a code in the
 // caller's status word, raises a CTA-wide abort flag, lets copies in flight land, frees TMEM and returns.
@@ -35,8 +39,8 @@ struct AttnBars {
   uint64_t kv_full[kStages];
   uint64_t kv_empty[kStages];
   uint64_t q_full;
-  uint64_t s_full[2];
-  uint64_t p_full[2];
+  uint64_t s_full[2][2];  // [stream][half]
+  uint64_t p_full[2][2];
   uint64_t o_full[2];
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
@@ -165,8 +169,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     mbar_init(smem_u32(&bars->q_full), 1);
     for (int t = 0; t < 2; ++t) {
-      mbar_init(smem_u32(&bars->s_full[t]), 1);
-      mbar_init(smem_u32(&bars->p_full[t]), 128);
+      for (int hf = 0; hf < 2; ++hf) {
+        mbar_init(smem_u32(&bars->s_full[t][hf]), 1);
+        mbar_init(smem_u32(&bars->p_full[t][hf]), 128);
+      }
       mbar_init(smem_u32(&bars->o_full[t]), 1);
     }
     bars->abort_flag = 0;
@@ -235,19 +241,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   } else if (warp == kIssuerWarp) {
     // =========================================================== MMA issuer
     if (lane == 0 && n_it > 0) {
-      constexpr uint32_t idesc_s = kFp8 ? umma_idesc(UMMA_FMT_E4M3, UMMA_FMT_E4M3, 0, 0, 128, 128)
-                                        : umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 0, 128, 128);
+      constexpr uint32_t idesc_s = kFp8 ? umma_idesc(UMMA_FMT_E4M3, UMMA_FMT_E4M3, 0, 0, 128, 64)
+                                        : umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 0, 128, 64);
       constexpr uint32_t idesc_pv = umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 1, 128, 128);
       bool ok = bounded_wait(wc, smem_u32(&bars->q_full), 0, kWaitQFull);
       tc_fence_after_sync();
-      uint32_t p_cnt[2] = {0, 0};
+      uint32_t p_cnt[2][2] = {{0, 0}, {0, 0}};
       uint32_t pv_cnt[2] = {0, 0};
 
-      // S_t = Q_t K^T for ring stage `sk` (both operands K-major, 128B swizzle, 8-row groups 1024 B apart)
-      auto issue_s = [&](int t, int sk) {
+      // S[t][hf] = Q_t K[hf]^T for keys [64 hf, 64 hf + 64) of ring stage `sk` (both operands K-major,
+      // 128B swizzle, 8-row groups 1024 B apart; 64 key rows = 8192 B into each box)
+      auto issue_s = [&](int t, int hf, int sk) {
         const uint32_t qa = q_smem + t * kQTileBytes;
-        const uint32_t ka = ring_smem + sk * kStageBytes;
-        const uint32_t d = tmem + t * kTile;
+        const uint32_t ka = ring_smem + sk * kStageBytes + hf * 8192;
+        const uint32_t d = tmem + t * kTile + hf * 64;
         if constexpr (kFp8) {
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // 32 e4m3 = 32 bytes per step inside the 128-byte swizzle span
@@ -259,28 +266,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             umma_bf16_ss(d, umma_desc_sw128(qa + off, 16, 1024), umma_desc_sw128(ka + off, 16, 1024), idesc_s, k > 0);
           }
         }
-        umma_commit(smem_u32(&bars->s_full[t]));
+        umma_commit(smem_u32(&bars->s_full[t][hf]));
       };
-      // O_t += P_t V for ring stage `sv`: A = P from TMEM (two bf16 per column), B = V MN-major
-      // ([token][64 dims] boxes: 8-token groups 1024 B apart, the two 64-dim halves 16 KB apart)
-      auto issue_pv = [&](int t, int sv) {
-        const uint32_t va = ring_smem + sv * kStageBytes;
+      // O_t += P[t][hf] V[hf] for keys [64 hf, +64) of ring stage `sv`: A = P from TMEM (two bf16 per
+      // column), B = V MN-major ([key][64 dims] boxes: 8-key groups 1024 B apart, the two 64-dim halves 16 KB apart)
+      auto issue_pv = [&](int t, int hf, int sv) {
+        const uint32_t va = ring_smem + sv * kStageBytes + hf * 8192;
         const uint32_t d = tmem + 256 + t * kTile;
-        const uint32_t a = tmem + t * kTile;
+        const uint32_t a = tmem + t * kTile + hf * 64;
 #pragma unroll
-        for (int k = 0; k < 8; ++k)  // 16 tokens per step = 16 rows of 128 B
+        for (int k = 0; k < 4; ++k)  // 16 keys per step = 16 rows of 128 B
           umma_bf16_ts(d, a + k * 8, umma_desc_sw128(va + k * 2048, kHalfBytes, 1024), idesc_pv, (pv_cnt[t] > 0 || k > 0) ? 1u : 0u);
         ++pv_cnt[t];
         umma_commit(smem_u32(&bars->o_full[t]));
       };
 
-      if (ok) {  // prologue: S for entry 0
+      if (ok) {  // prologue: both S halves of entry 0
         const int f0 = entry_at(0) & 3;
         ok = bounded_wait(wc, smem_u32(&bars->kv_full[0]), 0, kWaitKvFullK);
         if (ok) {
           tc_fence_after_sync();
-          if (f0 & 1) issue_s(0, 0);
-          if (f0 & 2) issue_s(1, 0);
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            if (f0 & 1) issue_s(0, hf, 0);
+            if (f0 & 2) issue_s(1, hf, 0);
+          }
           umma_commit(smem_u32(&bars->kv_empty[0]));
         }
       }
@@ -294,22 +304,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (!ok) break;
         bool k_ready = false;
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          if ((f >> t) & 1) {
-            ok = bounded_wait(wc, smem_u32(&bars->p_full[t]), p_cnt[t] & 1, kWaitPFull);
-            if (!ok) break;
-            ++p_cnt[t];
-            tc_fence_after_sync();
-            issue_pv(t, sv);
-          }
-          if ((fn >> t) & 1) {
-            if (!k_ready) {
-              ok = bounded_wait(wc, smem_u32(&bars->kv_full[sk]), (ck / kStages) & 1, kWaitKvFullK);
-              if (!ok) break;
-              k_ready = true;
-              tc_fence_after_sync();
+        for (int hf = 0; hf < 2; ++hf) {
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (ok && ((f >> t) & 1)) {
+              ok = bounded_wait(wc, smem_u32(&bars->p_full[t][hf]), p_cnt[t][hf] & 1, kWaitPFull);
+              if (ok) {
+                ++p_cnt[t][hf];
+                tc_fence_after_sync();
+                issue_pv(t, hf, sv);
+              }
             }
-            issue_s(t, sk);
+            if (ok && ((fn >> t) & 1)) {
+              if (!k_ready) {
+                ok = bounded_wait(wc, smem_u32(&bars->kv_full[sk]), (ck / kStages) & 1, kWaitKvFullK);
+                if (ok) {
+                  k_ready = true;
+                  tc_fence_after_sync();
+                }
+              }
+              if (ok) issue_s(t, hf, sk);
+            }
           }
         }
         if (!ok) break;
@@ -336,82 +351,86 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       qs = args.q_scale[head * args.nqb + qb];
     }
     float m_ref = 0.0f, l_sum = 0.0f;
-    uint32_t j = 0;
+    uint32_t j = 0;  // key tiles this stream has processed
     bool ok = true;
-    uint32_t s[128];
+    uint32_t s[64];
 
-    for (int it = 0; it < n_it; ++it) {
+    for (int it = 0; ok && it < n_it; ++it) {
       const int e = entry_at(it);
       if (!((e >> t) & 1)) continue;
       const int tile = e >> 2;
       float c = args.scale_log2;
       if constexpr (kFp8) c *= qs * args.k_scale[head * args.nkb + tile];
 
-      ok = bounded_wait(wc, smem_u32(&bars->s_full[t]), j & 1, kWaitSFull);
-      if (!ok) break;
-      tc_fence_after_sync();
 #pragma unroll
-      for (int i = 0; i < 4; ++i) tmem_ld32(s_addr + 32 * i, *reinterpret_cast<uint32_t(*)[32]>(&s[32 * i]));
-      tmem_wait_ld();
+      for (int hf = 0; hf < 2; ++hf) {
+        const uint32_t n = 2 * j + hf;  // half-step index of this stream == index of its P V
+        const uint32_t sb = s_addr + hf * 64;
+        ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->s_full[t][hf]), j & 1, kWaitSFull));
+        if (!ok) break;
+        tc_fence_after_sync();
+        tmem_ld32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tmem_ld32(sb + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+        tmem_wait_ld();
 
-      if (tile == last_tile && tail < kTile) {
+        if (tile == last_tile && tail < kTile) {
+          const int valid = tail - hf * 64;
 #pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (i >= tail) s[i] = 0xFF800000u;  // -inf
-      }
-      float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]), mx2 = __uint_as_float(s[2]), mx3 = __uint_as_float(s[3]);
+          for (int i = 0; i < 64; ++i)
+            if (i >= valid) s[i] = 0xFF800000u;  // -inf
+        }
+        float mx0 = fmax3(__uint_as_float(s[0]), __uint_as_float(s[1]), __uint_as_float(s[2]));
+        float mx1 = fmax3(__uint_as_float(s[3]), __uint_as_float(s[4]), __uint_as_float(s[5]));
 #pragma unroll
-      for (int i = 4; i < 128; i += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(s[i]));
-        mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
-      }
-      const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;
+        for (int i = 6; i < 62; i += 4) {
+          mx0 = fmax3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+        }
+        const float m_tile = fmax3(mx0, mx1, fmaxf(__uint_as_float(s[62]), __uint_as_float(s[63]))) * c;
 
-      if (j == 0) {
-        m_ref = m_tile;
-      } else {
-        const bool grow = (m_tile - m_ref) > kRescaleThreshold;
-        if (__any_sync(0xFFFFFFFFu, grow)) {
-          const float m_new = fmaxf(m_ref, m_tile);
-          const float alpha = ex2_approx(m_ref - m_new);
-          m_ref = m_new;
-          l_sum *= alpha;
-          // O_t must be quiescent: the previous P V of this stream has to be complete
-          ok = bounded_wait(wc, smem_u32(&bars->o_full[t]), (j - 1) & 1, kWaitOFull);
-          if (!ok) break;
-          tc_fence_after_sync();
+        if (n == 0) {
+          m_ref = m_tile;
+        } else {
+          const bool grow = (m_tile - m_ref) > kRescaleThreshold;
+          if (__any_sync(0xFFFFFFFFu, grow)) {
+            const float m_new = fmaxf(m_ref, m_tile);
+            const float alpha = ex2_approx(m_ref - m_new);
+            m_ref = m_new;
+            l_sum *= alpha;
+            // O_t must be quiescent: the previous P V of this stream has to be complete
+            ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->o_full[t]), (n - 1) & 1, kWaitOFull));
+            if (!ok) break;
+            tc_fence_after_sync();
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t o[32];
-            tmem_ld32(o_addr + 32 * i, o);
-            tmem_wait_ld();
+            for (int i = 0; i < 4; ++i) {
+              uint32_t o[32];
+              tmem_ld32(o_addr + 32 * i, o);
+              tmem_wait_ld();
 #pragma unroll
-            for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * alpha);
-            tmem_st32(o_addr + 32 * i, o);
+              for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * alpha);
+              tmem_st32(o_addr + 32 * i, o);
+            }
           }
         }
-      }
 
-      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-      const float neg_m = -m_ref;
+        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+        const float neg_m = -m_ref;
 #pragma unroll
-      for (int i = 0; i < 128; i += 4) {
-        const float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), c, neg_m));
-        const float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), c, neg_m));
-        const float p2 = ex2_approx(fmaf(__uint_as_float(s[i + 2]), c, neg_m));
-        const float p3 = ex2_approx(fmaf(__uint_as_float(s[i + 3]), c, neg_m));
-        l0 += p0; l1 += p1; l2 += p2; l3 += p3;
-        s[i >> 1] = pack_bf16x2(p0, p1);        // slot i/2 <= i: already consumed
-        s[(i >> 1) + 1] = pack_bf16x2(p2, p3);
+        for (int i = 0; i < 64; i += 4) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), c, neg_m));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), c, neg_m));
+          const float p2 = ex2_approx(fmaf(__uint_as_float(s[i + 2]), c, neg_m));
+          const float p3 = ex2_approx(fmaf(__uint_as_float(s[i + 3]), c, neg_m));
+          l0 += p0; l1 += p1; l2 += p2; l3 += p3;
+          s[i >> 1] = pack_bf16x2(p0, p1);        // slot i/2 <= i: already consumed
+          s[(i >> 1) + 1] = pack_bf16x2(p2, p3);
+        }
+        l_sum += (l0 + l1) + (l2 + l3);
+        tmem_st32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&bars->p_full[t][hf]));
       }
-      l_sum += (l0 + l1) + (l2 + l3);
-      tmem_st32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-      tmem_st32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(smem_u32(&bars->p_full[t]));
       ++j;
     }
 
@@ -419,7 +438,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const bool row_valid = q_row < args.Lq;
     __nv_bfloat16* orow = args.o + static_cast<long long>(q_row) * args.o_stride_l + static_cast<long long>(head) * args.o_stride_h;
     if (ok && j > 0) {
-      ok = bounded_wait(wc, smem_u32(&bars->o_full[t]), (j - 1) & 1, kWaitOFull);
+      ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->o_full[t]), (2 * j - 1) & 1, kWaitOFull));
       if (ok) {
         tc_fence_after_sync();
         const float inv = 1.0f / l_sum;

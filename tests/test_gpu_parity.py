@@ -306,7 +306,8 @@ def test_errors_are_reported_not_swallowed(h):
     with pytest.raises(ValueError):
         h.attn_fwd(q, k[:, :1], v)
     with pytest.raises(h.H3AError) as e:
-        h.attn_fwd(q[:, :, :128][:, :, :].as_strided((256, 2, 128), (260, 130, 1)), k, v)
+        big = torch.zeros(256 * 260 + 512, dtype=torch.bfloat16, device="cuda")
+        h.attn_fwd(big.as_strided((256, 2, 128), (260, 130, 1)), k, v)  # strides not multiples of 16 bytes
     assert e.value.status == h._lib.H3A_ERR_ALIGN
     with pytest.raises(ValueError):
         h.attn_fwd(q, k, v, h.MODE_BLOCK_SPARSE)
