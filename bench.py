@@ -36,6 +36,10 @@ WORKLOADS = {
     "cfg3_sparse": ((31, 48, 84), 1024, 40, "block_sparse", (2, 8, 8), 1003),
     "cfg3_sparse20": ((31, 48, 84), 1024, 40, "block_sparse", (3, 48, 84), 1003),
     "cfg0_dense": ((4, 32, 32), 0, 8, "dense_bf16", None, 1000),
+    # small cases for profiler captures: inputs above the L2 size, a few ms per launch
+    "prof_dense": ((15, 32, 32), 1024, 16, "dense_bf16", None, 2001),
+    "prof_fp8": ((15, 32, 32), 1024, 16, "fp8_qk", None, 2001),
+    "prof_sparse": ((31, 32, 32), 1024, 16, "block_sparse", (3, 32, 32), 2003),
 }
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_kernel launch, from the ncu captures summarised
 # under profiles/ (None until a capture of that workload exists)

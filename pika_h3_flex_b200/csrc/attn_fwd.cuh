@@ -41,7 +41,7 @@ struct AttnBars {
   uint64_t q_full;
   uint64_t s_full[2][2];  // [stream][half]
   uint64_t p_full[2][2];
-  uint64_t o_full[2];
+  uint64_t o_full[2][2];  // completion of the P V of (stream, half): one phase per key tile
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
   uint32_t early_exit;
@@ -172,8 +172,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int hf = 0; hf < 2; ++hf) {
         mbar_init(smem_u32(&bars->s_full[t][hf]), 1);
         mbar_init(smem_u32(&bars->p_full[t][hf]), 128);
+        mbar_init(smem_u32(&bars->o_full[t][hf]), 1);
       }
-      mbar_init(smem_u32(&bars->o_full[t]), 1);
     }
     bars->abort_flag = 0;
     bars->early_exit = (args.status != nullptr && *reinterpret_cast<volatile int*>(args.status) != 0) ? 1u : 0u;
@@ -278,7 +278,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int k = 0; k < 4; ++k)  // 16 keys per step = 16 rows of 128 B
           umma_bf16_ts(d, a + k * 8, umma_desc_sw128(va + k * 2048, kHalfBytes, 1024), idesc_pv, (pv_cnt[t] > 0 || k > 0) ? 1u : 0u);
         ++pv_cnt[t];
-        umma_commit(smem_u32(&bars->o_full[t]));
+        umma_commit(smem_u32(&bars->o_full[t][hf]));
       };
 
       if (ok) {  // prologue: both S halves of entry 0
@@ -397,8 +397,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const float alpha = ex2_approx(m_ref - m_new);
             m_ref = m_new;
             l_sum *= alpha;
-            // O_t must be quiescent: the previous P V of this stream has to be complete
-            ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->o_full[t]), (n - 1) & 1, kWaitOFull));
+            // O_t must be quiescent: the previous P V of this stream has to be complete (MMAs complete
+            // in issue order, so it is the only one that can still be running).  Each (stream, half)
+            // barrier advances one phase per key tile, so a parity wait is never two phases behind.
+            ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->o_full[t][hf ^ 1]), (hf ? j : j - 1) & 1, kWaitOFull));
             if (!ok) break;
             tc_fence_after_sync();
 #pragma unroll
@@ -438,7 +440,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const bool row_valid = q_row < args.Lq;
     __nv_bfloat16* orow = args.o + static_cast<long long>(q_row) * args.o_stride_l + static_cast<long long>(head) * args.o_stride_h;
     if (ok && j > 0) {
-      ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->o_full[t]), (2 * j - 1) & 1, kWaitOFull));
+      ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->o_full[t][1]), (j - 1) & 1, kWaitOFull));
       if (ok) {
         tc_fence_after_sync();
         const float inv = 1.0f / l_sum;
