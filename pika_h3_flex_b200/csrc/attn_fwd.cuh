@@ -75,6 +75,17 @@ enum : int {
   kWaitSFull = 5, kWaitPFull = 6, kWaitOFull = 7
 };
 
+// Optional timeline trace (debug builds only, -DH3A_TRACE): CTA 0 stamps clock64() at phase boundaries.
+#ifdef H3A_TRACE
+__device__ unsigned long long* g_trace = nullptr;
+#define H3A_STAMP(role, idx, k)                                                                   \
+  do {                                                                                            \
+    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && g_trace != nullptr && (idx) < 64) g_trace[((role) * 64 + (idx)) * 8 + (k)] = clock64(); \
+  } while (0)
+#else
+#define H3A_STAMP(role, idx, k) do {} while (0)
+#endif
+
 struct WaitCtx {
   AttnBars* bars;
   int* status;
@@ -199,91 +210,95 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   if (warp == kProducerWarp) {
     // =========================================================== producer
-    if (lane == 0) {
+    // The whole warp walks the loop (uniform control flow, uniform operands); one elected lane issues.
+    const uint32_t leader = elect_one();
+    {
       const uint32_t qbar = smem_u32(&bars->q_full);
-      mbar_arrive_expect_tx(qbar, 2 * kQBytes);
+      mbar_arrive_expect_tx_if(leader, qbar, 2 * kQBytes);
+#pragma unroll
       for (int t = 0; t < 2; ++t) {
-        if constexpr (kFp8) {
-          tma_load_3d(q_smem + t * kQTileBytes, &tm_q, qbar, 0, q0 + t * kTile, head);
-        } else {
-          tma_load_3d(q_smem + t * kQTileBytes, &tm_q, qbar, 0, q0 + t * kTile, head);
-          tma_load_3d(q_smem + t * kQTileBytes + kHalfBytes, &tm_q, qbar, 64, q0 + t * kTile, head);
-        }
+        tma_load_3d_if(leader, q_smem + t * kQTileBytes, &tm_q, qbar, 0, q0 + t * kTile, head);
+        if constexpr (!kFp8) tma_load_3d_if(leader, q_smem + t * kQTileBytes + kHalfBytes, &tm_q, qbar, 64, q0 + t * kTile, head);
       }
-      int cnt = 0;
-      for (int it = 0; it < n_it; ++it) {
-        const int tile = entry_at(it) >> 2;
-        {  // K tile
-          const int s = cnt % kStages;
-          const uint32_t ph = (cnt / kStages) & 1;
-          if (!bounded_wait(wc, smem_u32(&bars->kv_empty[s]), ph ^ 1u, kWaitKvEmpty)) break;
-          const uint32_t fb = smem_u32(&bars->kv_full[s]);
-          const uint32_t dst = ring_smem + s * kStageBytes;
-          mbar_arrive_expect_tx(fb, kKBytes);
-          tma_load_3d(dst, &tm_k, fb, 0, tile * kTile, head);
-          if constexpr (!kFp8) tma_load_3d(dst + kHalfBytes, &tm_k, fb, 64, tile * kTile, head);
-          ++cnt;
+    }
+    int cnt = 0;
+    bool ok = true;
+    for (int it = 0; ok && it < n_it; ++it) {
+      const int tile = entry_at(it) >> 2;
+#pragma unroll
+      for (int kv = 0; kv < 2; ++kv) {  // K tile, then V tile
+        const int s = cnt % kStages;
+        const uint32_t ph = (cnt / kStages) & 1;
+        ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->kv_empty[s]), ph ^ 1u, kWaitKvEmpty));
+        if (!ok) break;
+        const uint32_t fb = smem_u32(&bars->kv_full[s]);
+        const uint32_t dst = ring_smem + s * kStageBytes;
+        if (kv == 0) {
+          mbar_arrive_expect_tx_if(leader, fb, kKBytes);
+          tma_load_3d_if(leader, dst, &tm_k, fb, 0, tile * kTile, head);
+          if constexpr (!kFp8) tma_load_3d_if(leader, dst + kHalfBytes, &tm_k, fb, 64, tile * kTile, head);
+        } else {
+          mbar_arrive_expect_tx_if(leader, fb, kVBytes);
+          tma_load_3d_if(leader, dst, &tm_v, fb, 0, tile * kTile, head);
+          tma_load_3d_if(leader, dst + kHalfBytes, &tm_v, fb, 64, tile * kTile, head);
         }
-        {  // V tile
-          const int s = cnt % kStages;
-          const uint32_t ph = (cnt / kStages) & 1;
-          if (!bounded_wait(wc, smem_u32(&bars->kv_empty[s]), ph ^ 1u, kWaitKvEmpty)) break;
-          const uint32_t fb = smem_u32(&bars->kv_full[s]);
-          const uint32_t dst = ring_smem + s * kStageBytes;
-          mbar_arrive_expect_tx(fb, kVBytes);
-          tma_load_3d(dst, &tm_v, fb, 0, tile * kTile, head);
-          tma_load_3d(dst + kHalfBytes, &tm_v, fb, 64, tile * kTile, head);
-          ++cnt;
-        }
+        ++cnt;
       }
     }
     __syncwarp();
   } else if (warp == kIssuerWarp) {
     // =========================================================== MMA issuer
-    if (lane == 0 && n_it > 0) {
+    // Uniform control flow for the whole warp; the elected lane issues every MMA and commit (a commit
+    // tracks the MMAs of the thread that executes it, and the election is the same lane every time).
+    if (n_it > 0) {
+      const uint32_t leader = elect_one();
       constexpr uint32_t idesc_s = kFp8 ? umma_idesc(UMMA_FMT_E4M3, UMMA_FMT_E4M3, 0, 0, 128, 64)
                                         : umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 0, 128, 64);
       constexpr uint32_t idesc_pv = umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 1, 128, 128);
-      bool ok = bounded_wait(wc, smem_u32(&bars->q_full), 0, kWaitQFull);
+      bool ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->q_full), 0, kWaitQFull));
       tc_fence_after_sync();
       uint32_t p_cnt[2][2] = {{0, 0}, {0, 0}};
       uint32_t pv_cnt[2] = {0, 0};
+      // descriptors of the Q tiles never change; K/V descriptors are a per-stage base plus constants
+      const uint64_t q_desc[2] = {umma_desc_sw128(q_smem, 16, 1024), umma_desc_sw128(q_smem + kQTileBytes, 16, 1024)};
+      const uint64_t k_desc0 = umma_desc_sw128(ring_smem, 16, 1024);
+      const uint64_t v_desc0 = umma_desc_sw128(ring_smem, kHalfBytes, 1024);
 
       // S[t][hf] = Q_t K[hf]^T for keys [64 hf, 64 hf + 64) of ring stage `sk` (both operands K-major,
       // 128B swizzle, 8-row groups 1024 B apart; 64 key rows = 8192 B into each box)
       auto issue_s = [&](int t, int hf, int sk) {
-        const uint32_t qa = q_smem + t * kQTileBytes;
-        const uint32_t ka = ring_smem + sk * kStageBytes + hf * 8192;
+        const uint64_t qd = q_desc[t];
+        const uint64_t kd = k_desc0 + static_cast<uint64_t>((sk * kStageBytes + hf * 8192) >> 4);
         const uint32_t d = tmem + t * kTile + hf * 64;
         if constexpr (kFp8) {
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // 32 e4m3 = 32 bytes per step inside the 128-byte swizzle span
-            umma_e4m3_ss(d, umma_desc_sw128(qa + k * 32, 16, 1024), umma_desc_sw128(ka + k * 32, 16, 1024), idesc_s, k > 0);
+            umma_e4m3_ss_if(leader, d, qd + (k * 32 >> 4), kd + (k * 32 >> 4), idesc_s, k > 0);
         } else {
 #pragma unroll
           for (int k = 0; k < 8; ++k) {  // 16 bf16 = 32 bytes per step; dims 64..127 live in the second box
-            const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-            umma_bf16_ss(d, umma_desc_sw128(qa + off, 16, 1024), umma_desc_sw128(ka + off, 16, 1024), idesc_s, k > 0);
+            const uint32_t off = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
+            umma_bf16_ss_if(leader, d, qd + off, kd + off, idesc_s, k > 0);
           }
         }
-        umma_commit(smem_u32(&bars->s_full[t][hf]));
+        umma_commit_if(leader, smem_u32(&bars->s_full[t][hf]));
       };
       // O_t += P[t][hf] V[hf] for keys [64 hf, +64) of ring stage `sv`: A = P from TMEM (two bf16 per
       // column), B = V MN-major ([key][64 dims] boxes: 8-key groups 1024 B apart, the two 64-dim halves 16 KB apart)
       auto issue_pv = [&](int t, int hf, int sv) {
-        const uint32_t va = ring_smem + sv * kStageBytes + hf * 8192;
+        const uint64_t vd = v_desc0 + static_cast<uint64_t>((sv * kStageBytes + hf * 8192) >> 4);
         const uint32_t d = tmem + 256 + t * kTile;
         const uint32_t a = tmem + t * kTile + hf * 64;
 #pragma unroll
         for (int k = 0; k < 4; ++k)  // 16 keys per step = 16 rows of 128 B
-          umma_bf16_ts(d, a + k * 8, umma_desc_sw128(va + k * 2048, kHalfBytes, 1024), idesc_pv, (pv_cnt[t] > 0 || k > 0) ? 1u : 0u);
+          umma_bf16_ts_if(leader, d, a + k * 8, vd + (k * 2048 >> 4), idesc_pv, (pv_cnt[t] > 0 || k > 0) ? 1u : 0u);
         ++pv_cnt[t];
-        umma_commit(smem_u32(&bars->o_full[t][hf]));
+        umma_commit_if(leader, smem_u32(&bars->o_full[t][hf]));
       };
 
       if (ok) {  // prologue: both S halves of entry 0
         const int f0 = entry_at(0) & 3;
-        ok = bounded_wait(wc, smem_u32(&bars->kv_full[0]), 0, kWaitKvFullK);
+        ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->kv_full[0]), 0, kWaitKvFullK));
         if (ok) {
           tc_fence_after_sync();
 #pragma unroll
@@ -291,7 +306,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (f0 & 1) issue_s(0, hf, 0);
             if (f0 & 2) issue_s(1, hf, 0);
           }
-          umma_commit(smem_u32(&bars->kv_empty[0]));
+          umma_commit_if(leader, smem_u32(&bars->kv_empty[0]));
         }
       }
       for (int it = 0; ok && it < n_it; ++it) {
@@ -300,7 +315,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int fn = has_next ? (entry_at(it + 1) & 3) : 0;
         const int cv = 2 * it + 1, ck = 2 * it + 2;
         const int sv = cv % kStages, sk = ck % kStages;
-        ok = bounded_wait(wc, smem_u32(&bars->kv_full[sv]), (cv / kStages) & 1, kWaitKvFullV);
+        ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->kv_full[sv]), (cv / kStages) & 1, kWaitKvFullV));
         if (!ok) break;
         bool k_ready = false;
 #pragma unroll
@@ -308,28 +323,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             if (ok && ((f >> t) & 1)) {
-              ok = bounded_wait(wc, smem_u32(&bars->p_full[t][hf]), p_cnt[t][hf] & 1, kWaitPFull);
+              H3A_STAMP(2 + t, 2 * it + hf, 0);
+              ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->p_full[t][hf]), p_cnt[t][hf] & 1, kWaitPFull));
               if (ok) {
                 ++p_cnt[t][hf];
                 tc_fence_after_sync();
+                H3A_STAMP(2 + t, 2 * it + hf, 1);
                 issue_pv(t, hf, sv);
+                H3A_STAMP(2 + t, 2 * it + hf, 2);
               }
             }
             if (ok && ((fn >> t) & 1)) {
               if (!k_ready) {
-                ok = bounded_wait(wc, smem_u32(&bars->kv_full[sk]), (ck / kStages) & 1, kWaitKvFullK);
+                ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->kv_full[sk]), (ck / kStages) & 1, kWaitKvFullK));
                 if (ok) {
                   k_ready = true;
                   tc_fence_after_sync();
                 }
               }
               if (ok) issue_s(t, hf, sk);
+              H3A_STAMP(2 + t, 2 * it + hf, 3);
             }
           }
         }
         if (!ok) break;
-        umma_commit(smem_u32(&bars->kv_empty[sv]));
-        if (has_next) umma_commit(smem_u32(&bars->kv_empty[sk]));
+        umma_commit_if(leader, smem_u32(&bars->kv_empty[sv]));
+        if (has_next) umma_commit_if(leader, smem_u32(&bars->kv_empty[sk]));
       }
     }
     __syncwarp();
@@ -366,12 +385,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int hf = 0; hf < 2; ++hf) {
         const uint32_t n = 2 * j + hf;  // half-step index of this stream == index of its P V
         const uint32_t sb = s_addr + hf * 64;
+        if (row == 0) H3A_STAMP(t, n, 0);
         ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->s_full[t][hf]), j & 1, kWaitSFull));
         if (!ok) break;
         tc_fence_after_sync();
+        if (row == 0) H3A_STAMP(t, n, 1);
         tmem_ld32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
         tmem_ld32(sb + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
         tmem_wait_ld();
+        if (row == 0) H3A_STAMP(t, n, 2);
 
         if (tile == last_tile && tail < kTile) {
           const int valid = tail - hf * 64;
@@ -387,6 +409,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
         }
         const float m_tile = fmax3(mx0, mx1, fmaxf(__uint_as_float(s[62]), __uint_as_float(s[63]))) * c;
+        if (row == 0) H3A_STAMP(t, n, 3);
 
         if (n == 0) {
           m_ref = m_tile;
@@ -428,10 +451,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           s[(i >> 1) + 1] = pack_bf16x2(p2, p3);
         }
         l_sum += (l0 + l1) + (l2 + l3);
+        if (row == 0) H3A_STAMP(t, n, 4);
         tmem_st32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(smem_u32(&bars->p_full[t][hf]));
+        if (row == 0) H3A_STAMP(t, n, 5);
       }
       ++j;
     }

@@ -277,6 +277,13 @@ int32_t h3a_build_block_index(int32_t T, int32_t Hg, int32_t Wg, int32_t n_audio
   return H3A_OK;
 }
 
+#ifdef H3A_TRACE
+// debug builds only: point the timeline trace at a device buffer of 4*64*8 uint64
+int32_t h3a_debug_set_trace(void* dev_buffer) {
+  return cudaMemcpyToSymbol(h3a::g_trace, &dev_buffer, sizeof(void*)) == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
+}
+#endif
+
 int32_t h3a_read_device_status(const int32_t* status_word, void* stream, int32_t* raw) {
   if (!status_word) return H3A_ERR_ARG;
   int32_t v = 0;

@@ -28,24 +28,25 @@ MODES = {"dense_bf16": _lib.MODE_DENSE_BF16, "fp8_qk": _lib.MODE_FP8_QK, "block_
 
 
 class RopeCache:
-    """Small LRU of (cos, sin) tables keyed by the identity of the position tensor, like the reference's
-    per-geometry layout cache (``src/pika_h3/core/wrapper.py:71-78``)."""
+    """Small LRU of (cos, sin) tables keyed by the storage and version of the position tensor, like the
+    reference's per-geometry layout cache (``src/pika_h3/core/wrapper.py:71-78``).  Each entry keeps its
+    position tensor alive, so a freed buffer whose address is reused can never alias a cached key."""
 
     def __init__(self, size: int = 8):
         self.size = size
-        self._d: "OrderedDict[tuple, torch.Tensor]" = OrderedDict()
+        self._d: "OrderedDict[tuple, tuple]" = OrderedDict()
 
     def get(self, pos: torch.Tensor, split, theta) -> torch.Tensor:
         key = (pos.data_ptr(), tuple(pos.shape), pos.dtype, pos._version, str(pos.device), tuple(split), float(theta))
-        tab = self._d.get(key)
-        if tab is None:
+        hit = self._d.get(key)
+        if hit is None:
             tab = ops.rope_table(pos.to(device=_cuda_device(pos)), split, theta)
             if len(self._d) >= self.size:
                 self._d.popitem(last=False)
-            self._d[key] = tab
-        else:
-            self._d.move_to_end(key)
-        return tab
+            self._d[key] = (tab, pos)
+            return tab
+        self._d.move_to_end(key)
+        return hit[0]
 
 
 def _cuda_device(t: torch.Tensor):
