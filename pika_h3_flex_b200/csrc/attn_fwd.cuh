@@ -3,8 +3,9 @@
 //
 // One CTA owns a PAIR of 128-row query tiles of one head (two "streams") and walks the key tiles:
 //   warp 8   producer : TMA loads of Q (once) and of K_j, V_j (128 keys each) into a ring of 32 KB stages
-//   warp 9   issuer   : one thread issues  S = Q_t K^T  (SS MMA, N = 64 keys) and  O_t += P V  (TS MMA, P
-//                       read from TMEM, K = 64 keys); tcgen05.commit signals mbarriers
+//   warps 9,10 issuers: one warp per stream; its elected lane issues  S = Q_t K^T  (SS MMA, N = 64 keys)
+//                       and  O_t += P V  (TS MMA, P read from TMEM, K = 64 keys); tcgen05.commit signals
+//                       mbarriers.  Two issuers keep the tensor pipe fed while one of them polls a barrier.
 //   warps 0-3 / 4-7   : softmax of stream 0 / 1, one query row per thread (TMEM lane == row): online
 //                       max / exp2 / sum, P written back over S as packed bf16, lazy rescale of O
 //                       (only when the running max grows by more than 2^8), final 1/l and store.
@@ -30,10 +31,21 @@ constexpr int kStages = 5;
 constexpr int kStageBytes = 32768;
 constexpr int kQTileBytes = 32768;
 constexpr int kHalfBytes = 16384;  // one [128 rows][128 bytes] swizzled box
-constexpr int kAttnThreads = 320;
+constexpr int kAttnThreads = 384;  // warpgroups 0,1: softmax; warpgroup 2: producer, issuer, two idle warps
+// Register re-allocation: setmaxnreg.inc BLOCKS until the registers exist, and they can only come from what
+// the CTA owns at launch (registers per thread reported by the compiler x 384) minus what the helper
+// warpgroup gives back.  kLaunchRegs is checked against the real kernel attribute before every first launch.
+constexpr int kLaunchRegs = 168;
+constexpr int kSoftmaxRegs = 208;
+constexpr int kHelperRegs = 88;
+static_assert(2 * 128 * kSoftmaxRegs + 128 * kHelperRegs <= kLaunchRegs * kAttnThreads, "setmaxnreg budget exceeds the launch allocation");
 constexpr int kProducerWarp = 8;
 constexpr int kIssuerWarp = 9;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+#ifndef H3A_POLY_PAIRS
+#define H3A_POLY_PAIRS 1
+#endif
+constexpr int kPolyPairs = H3A_POLY_PAIRS;  // of every 4 element pairs, how many use the polynomial exp2 (0..4)
 
 struct AttnBars {
   uint64_t kv_full[kStages];
@@ -176,7 +188,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       mbar_init(smem_u32(&bars->kv_full[i]), 1);
-      mbar_init(smem_u32(&bars->kv_empty[i]), 1);
+      mbar_init(smem_u32(&bars->kv_empty[i]), 2);  // released by both issuer warps
     }
     mbar_init(smem_u32(&bars->q_full), 1);
     for (int t = 0; t < 2; ++t) {
@@ -208,7 +220,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   WaitCtx wc{bars, args.status, args.wait_ns};
 
-  if (warp == kProducerWarp) {
+  if (warp >= 8) {
+   setmaxnreg_dec<kHelperRegs>();
+   if (warp == kProducerWarp) {
     // =========================================================== producer
     // The whole warp walks the loop (uniform control flow, uniform operands); one elected lane issues.
     const uint32_t leader = elect_one();
@@ -246,53 +260,56 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
     __syncwarp();
-  } else if (warp == kIssuerWarp) {
-    // =========================================================== MMA issuer
+  } else if (warp == kIssuerWarp || warp == kIssuerWarp + 1) {
+    // =========================================================== MMA issuers, one warp per stream
     // Uniform control flow for the whole warp; the elected lane issues every MMA and commit (a commit
     // tracks the MMAs of the thread that executes it, and the election is the same lane every time).
+    // Each issuer walks every plan entry, also those that do not list its stream: a K/V stage is released
+    // by one commit from each issuer, and waiting for the stage first keeps the two in step.
     if (n_it > 0) {
+      const int t = warp - kIssuerWarp;
       const uint32_t leader = elect_one();
       constexpr uint32_t idesc_s = kFp8 ? umma_idesc(UMMA_FMT_E4M3, UMMA_FMT_E4M3, 0, 0, 128, 64)
                                         : umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 0, 128, 64);
       constexpr uint32_t idesc_pv = umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 1, 128, 128);
       bool ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->q_full), 0, kWaitQFull));
       tc_fence_after_sync();
-      uint32_t p_cnt[2][2] = {{0, 0}, {0, 0}};
-      uint32_t pv_cnt[2] = {0, 0};
-      // descriptors of the Q tiles never change; K/V descriptors are a per-stage base plus constants
-      const uint64_t q_desc[2] = {umma_desc_sw128(q_smem, 16, 1024), umma_desc_sw128(q_smem + kQTileBytes, 16, 1024)};
+      uint32_t p_cnt[2] = {0, 0};
+      uint32_t pv_cnt = 0;
+      // the descriptor of the Q tile never changes; K/V descriptors are a per-stage base plus constants
+      const uint64_t q_desc = umma_desc_sw128(q_smem + t * kQTileBytes, 16, 1024);
       const uint64_t k_desc0 = umma_desc_sw128(ring_smem, 16, 1024);
       const uint64_t v_desc0 = umma_desc_sw128(ring_smem, kHalfBytes, 1024);
+      const uint32_t s_tmem = tmem + t * kTile;
+      const uint32_t o_tmem = tmem + 256 + t * kTile;
 
       // S[t][hf] = Q_t K[hf]^T for keys [64 hf, 64 hf + 64) of ring stage `sk` (both operands K-major,
       // 128B swizzle, 8-row groups 1024 B apart; 64 key rows = 8192 B into each box)
-      auto issue_s = [&](int t, int hf, int sk) {
-        const uint64_t qd = q_desc[t];
+      auto issue_s = [&](int hf, int sk) {
         const uint64_t kd = k_desc0 + static_cast<uint64_t>((sk * kStageBytes + hf * 8192) >> 4);
-        const uint32_t d = tmem + t * kTile + hf * 64;
+        const uint32_t d = s_tmem + hf * 64;
         if constexpr (kFp8) {
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // 32 e4m3 = 32 bytes per step inside the 128-byte swizzle span
-            umma_e4m3_ss_if(leader, d, qd + (k * 32 >> 4), kd + (k * 32 >> 4), idesc_s, k > 0);
+            umma_e4m3_ss_if(leader, d, q_desc + (k * 32 >> 4), kd + (k * 32 >> 4), idesc_s, k > 0);
         } else {
 #pragma unroll
           for (int k = 0; k < 8; ++k) {  // 16 bf16 = 32 bytes per step; dims 64..127 live in the second box
             const uint32_t off = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
-            umma_bf16_ss_if(leader, d, qd + off, kd + off, idesc_s, k > 0);
+            umma_bf16_ss_if(leader, d, q_desc + off, kd + off, idesc_s, k > 0);
           }
         }
         umma_commit_if(leader, smem_u32(&bars->s_full[t][hf]));
       };
       // O_t += P[t][hf] V[hf] for keys [64 hf, +64) of ring stage `sv`: A = P from TMEM (two bf16 per
       // column), B = V MN-major ([key][64 dims] boxes: 8-key groups 1024 B apart, the two 64-dim halves 16 KB apart)
-      auto issue_pv = [&](int t, int hf, int sv) {
+      auto issue_pv = [&](int hf, int sv) {
         const uint64_t vd = v_desc0 + static_cast<uint64_t>((sv * kStageBytes + hf * 8192) >> 4);
-        const uint32_t d = tmem + 256 + t * kTile;
-        const uint32_t a = tmem + t * kTile + hf * 64;
+        const uint32_t a = s_tmem + hf * 64;
 #pragma unroll
         for (int k = 0; k < 4; ++k)  // 16 keys per step = 16 rows of 128 B
-          umma_bf16_ts_if(leader, d, a + k * 8, vd + (k * 2048 >> 4), idesc_pv, (pv_cnt[t] > 0 || k > 0) ? 1u : 0u);
-        ++pv_cnt[t];
+          umma_bf16_ts_if(leader, o_tmem, a + k * 8, vd + (k * 2048 >> 4), idesc_pv, (pv_cnt > 0 || k > 0) ? 1u : 0u);
+        ++pv_cnt;
         umma_commit_if(leader, smem_u32(&bars->o_full[t][hf]));
       };
 
@@ -301,10 +318,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->kv_full[0]), 0, kWaitKvFullK));
         if (ok) {
           tc_fence_after_sync();
-#pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
-            if (f0 & 1) issue_s(0, hf, 0);
-            if (f0 & 2) issue_s(1, hf, 0);
+          if ((f0 >> t) & 1) {
+            issue_s(0, 0);
+            issue_s(1, 0);
           }
           umma_commit_if(leader, smem_u32(&bars->kv_empty[0]));
         }
@@ -315,35 +331,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int fn = has_next ? (entry_at(it + 1) & 3) : 0;
         const int cv = 2 * it + 1, ck = 2 * it + 2;
         const int sv = cv % kStages, sk = ck % kStages;
+        const bool mine = (f >> t) & 1, mine_next = (fn >> t) & 1;
         ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->kv_full[sv]), (cv / kStages) & 1, kWaitKvFullV));
         if (!ok) break;
         bool k_ready = false;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            if (ok && ((f >> t) & 1)) {
-              H3A_STAMP(2 + t, 2 * it + hf, 0);
-              ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->p_full[t][hf]), p_cnt[t][hf] & 1, kWaitPFull));
-              if (ok) {
-                ++p_cnt[t][hf];
-                tc_fence_after_sync();
-                H3A_STAMP(2 + t, 2 * it + hf, 1);
-                issue_pv(t, hf, sv);
-                H3A_STAMP(2 + t, 2 * it + hf, 2);
-              }
+          if (ok && mine) {
+            H3A_STAMP(2 + t, 2 * it + hf, 0);
+            ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->p_full[t][hf]), p_cnt[hf] & 1, kWaitPFull));
+            if (ok) {
+              ++p_cnt[hf];
+              tc_fence_after_sync();
+              H3A_STAMP(2 + t, 2 * it + hf, 1);
+              issue_pv(hf, sv);
+              H3A_STAMP(2 + t, 2 * it + hf, 2);
             }
-            if (ok && ((fn >> t) & 1)) {
-              if (!k_ready) {
-                ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->kv_full[sk]), (ck / kStages) & 1, kWaitKvFullK));
-                if (ok) {
-                  k_ready = true;
-                  tc_fence_after_sync();
-                }
-              }
-              if (ok) issue_s(t, hf, sk);
-              H3A_STAMP(2 + t, 2 * it + hf, 3);
+          }
+          if (ok && has_next && !k_ready) {
+            ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->kv_full[sk]), (ck / kStages) & 1, kWaitKvFullK));
+            if (ok) {
+              k_ready = true;
+              tc_fence_after_sync();
             }
+          }
+          if (ok && mine_next) {
+            issue_s(hf, sk);
+            H3A_STAMP(2 + t, 2 * it + hf, 3);
           }
         }
         if (!ok) break;
@@ -352,7 +366,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
     __syncwarp();
+   }
   } else {
+    setmaxnreg_inc<kSoftmaxRegs>();
     // =========================================================== softmax / rescale / epilogue
     const int t = warp >> 2;            // stream
     const int quarter = warp & 3;       // TMEM lane quarter this warp may touch
@@ -372,93 +388,160 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     float m_ref = 0.0f, l_sum = 0.0f;
     uint32_t j = 0;  // key tiles this stream has processed
     bool ok = true;
-    uint32_t s[64];
+    uint32_t ra[64], rb[64];  // two register images of an S half: one being processed, one being prefetched
 
-    for (int it = 0; ok && it < n_it; ++it) {
-      const int e = entry_at(it);
-      if (!((e >> t) & 1)) continue;
-      const int tile = e >> 2;
+    auto next_entry = [&](int from) -> int {  // next plan entry that lists this stream, or n_it
+      int x = from;
+      while (x < n_it && !((entry_at(x) >> t) & 1)) ++x;
+      return x;
+    };
+    // start the TMEM load of S[t][hf] into r (not waited for)
+    auto load_s = [&](uint32_t (&r)[64], int hf) {
+      tc_fence_after_sync();
+      tmem_ld32(s_addr + hf * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+      tmem_ld32(s_addr + hf * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+    };
+    // wait for S[t][hf] of the stream's tile number `jt`, then start its load
+    auto fetch_s = [&](uint32_t (&r)[64], int hf, uint32_t jt) -> bool {
+      const bool got = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->s_full[t][hf]), jt & 1, kWaitSFull));
+      if (got) load_s(r, hf);
+      return got;
+    };
+    // if S[t][hf] of tile `jt` is already complete start its load now (its latency then hides behind the
+    // P store); never block here: P of the current half must not be held back waiting for the tensor pipe
+    auto try_fetch_s = [&](uint32_t (&r)[64], int hf, uint32_t jt) -> bool {
+      const bool ready = __all_sync(0xFFFFFFFFu, mbar_test_wait(smem_u32(&bars->s_full[t][hf]), jt & 1));
+      if (ready) load_s(r, hf);
+      return ready;
+    };
+    // one half-step on the S image in s[]: online max, lazy rescale of O, P = 2^(s c - m) packed into s[0..31]
+    auto softmax_half = [&](uint32_t (&s)[64], int hf, int tile, float c) -> bool {
+      if (tile == last_tile && tail < kTile) {
+        const int valid = tail - hf * 64;
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (i >= valid) s[i] = 0xFF800000u;  // -inf
+      }
+      float mx0 = fmax3(__uint_as_float(s[0]), __uint_as_float(s[1]), __uint_as_float(s[2]));
+      float mx1 = fmax3(__uint_as_float(s[3]), __uint_as_float(s[4]), __uint_as_float(s[5]));
+      float mx2 = fmax3(__uint_as_float(s[6]), __uint_as_float(s[7]), __uint_as_float(s[8]));
+      float mx3 = fmax3(__uint_as_float(s[9]), __uint_as_float(s[10]), __uint_as_float(s[11]));
+#pragma unroll
+      for (int i = 12; i < 60; i += 8) {
+        mx0 = fmax3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+        mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+        mx2 = fmax3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+        mx3 = fmax3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+      }
+      mx0 = fmax3(mx0, __uint_as_float(s[60]), __uint_as_float(s[61]));
+      mx1 = fmax3(mx1, __uint_as_float(s[62]), __uint_as_float(s[63]));
+      const float m_tile = fmax3(fmaxf(mx0, mx1), mx2, mx3) * c;
+
+      if (j == 0 && hf == 0) {
+        m_ref = m_tile;
+      } else {
+        const bool grow = (m_tile - m_ref) > kRescaleThreshold;
+        if (__any_sync(0xFFFFFFFFu, grow)) {
+          const float m_new = fmaxf(m_ref, m_tile);
+          const float alpha = ex2_approx(m_ref - m_new);
+          m_ref = m_new;
+          l_sum *= alpha;
+          // O_t must be quiescent: the previous P V of this stream has to be complete (MMAs complete
+          // in issue order, so it is the only one that can still be running).  Each (stream, half)
+          // barrier advances one phase per key tile, so a parity wait is never two phases behind.
+          if (!__all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->o_full[t][hf ^ 1]), (hf ? j : j - 1) & 1, kWaitOFull)))
+            return false;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t o[32];
+            tmem_ld32(o_addr + 32 * i, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * alpha);
+            tmem_st32(o_addr + 32 * i, o);
+          }
+        }
+      }
+      // p = 2^(s c - m): scale-and-subtract as packed FFMA2; of every 4 pairs, kPolyPairs take the
+      // FMA-pipe polynomial and the rest the MUFU, so neither unit carries the whole tile
+      uint64_t acc0 = 0, acc1 = 0;  // two packed accumulators = four partial row sums (bit pattern 0 == 0.0f)
+      const uint64_t c2 = pack2(c, c), nm2 = pack2(-m_ref, -m_ref);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const uint64_t x = fma2(pack2u(s[2 * i], s[2 * i + 1]), c2, nm2);
+        uint64_t pp;
+        if ((i & 3) < kPolyPairs) {
+          pp = exp2_poly2(x);
+        } else {
+          float x0, x1;
+          unpack2(x, x0, x1);
+          pp = pack2(ex2_approx(x0), ex2_approx(x1));
+        }
+        if (i & 1) acc1 = add2(acc1, pp);
+        else acc0 = add2(acc0, pp);
+        float p0, p1;
+        unpack2(pp, p0, p1);
+        s[i] = pack_bf16x2(p0, p1);  // slot i <= 2i: already consumed
+      }
+      float a0, a1, a2, a3;
+      unpack2(acc0, a0, a1);
+      unpack2(acc1, a2, a3);
+      l_sum += (a0 + a1) + (a2 + a3);
+      return true;
+    };
+    // publish P[t][hf] (packed in s[0..31]) to TMEM and tell the issuer
+    auto publish_p = [&](uint32_t (&s)[64], int hf) {
+      tmem_st32(s_addr + hf * 64, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&bars->p_full[t][hf]));
+    };
+
+    int it = next_entry(0);
+    if (it < n_it) ok = fetch_s(ra, 0, 0);
+    while (ok && it < n_it) {
+      const int tile = entry_at(it) >> 2;
+      const int it_next = next_entry(it + 1);
       float c = args.scale_log2;
       if constexpr (kFp8) c *= qs * args.k_scale[head * args.nkb + tile];
 
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        const uint32_t n = 2 * j + hf;  // half-step index of this stream == index of its P V
-        const uint32_t sb = s_addr + hf * 64;
-        if (row == 0) H3A_STAMP(t, n, 0);
-        ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->s_full[t][hf]), j & 1, kWaitSFull));
+      // ---- half 0 from image A; the load of half 1 (image B) is started just before P is published when
+      //      that S is already complete, so its latency overlaps the TMEM store and the barrier round trip
+      if (row == 0) H3A_STAMP(t, 2 * j, 0);
+      tmem_wait_ld();
+      reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&ra[0]));
+      reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&ra[32]));
+      if (row == 0) H3A_STAMP(t, 2 * j, 2);
+      ok = softmax_half(ra, 0, tile, c);
+      if (!ok) break;
+      if (row == 0) H3A_STAMP(t, 2 * j, 4);
+      {
+        const bool early = try_fetch_s(rb, 1, j);
+        publish_p(ra, 0);
+        if (!early) ok = fetch_s(rb, 1, j);
         if (!ok) break;
-        tc_fence_after_sync();
-        if (row == 0) H3A_STAMP(t, n, 1);
-        tmem_ld32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-        tmem_ld32(sb + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-        tmem_wait_ld();
-        if (row == 0) H3A_STAMP(t, n, 2);
-
-        if (tile == last_tile && tail < kTile) {
-          const int valid = tail - hf * 64;
-#pragma unroll
-          for (int i = 0; i < 64; ++i)
-            if (i >= valid) s[i] = 0xFF800000u;  // -inf
-        }
-        float mx0 = fmax3(__uint_as_float(s[0]), __uint_as_float(s[1]), __uint_as_float(s[2]));
-        float mx1 = fmax3(__uint_as_float(s[3]), __uint_as_float(s[4]), __uint_as_float(s[5]));
-#pragma unroll
-        for (int i = 6; i < 62; i += 4) {
-          mx0 = fmax3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-          mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-        }
-        const float m_tile = fmax3(mx0, mx1, fmaxf(__uint_as_float(s[62]), __uint_as_float(s[63]))) * c;
-        if (row == 0) H3A_STAMP(t, n, 3);
-
-        if (n == 0) {
-          m_ref = m_tile;
-        } else {
-          const bool grow = (m_tile - m_ref) > kRescaleThreshold;
-          if (__any_sync(0xFFFFFFFFu, grow)) {
-            const float m_new = fmaxf(m_ref, m_tile);
-            const float alpha = ex2_approx(m_ref - m_new);
-            m_ref = m_new;
-            l_sum *= alpha;
-            // O_t must be quiescent: the previous P V of this stream has to be complete (MMAs complete
-            // in issue order, so it is the only one that can still be running).  Each (stream, half)
-            // barrier advances one phase per key tile, so a parity wait is never two phases behind.
-            ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->o_full[t][hf ^ 1]), (hf ? j : j - 1) & 1, kWaitOFull));
-            if (!ok) break;
-            tc_fence_after_sync();
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint32_t o[32];
-              tmem_ld32(o_addr + 32 * i, o);
-              tmem_wait_ld();
-#pragma unroll
-              for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * alpha);
-              tmem_st32(o_addr + 32 * i, o);
-            }
-          }
-        }
-
-        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-        const float neg_m = -m_ref;
-#pragma unroll
-        for (int i = 0; i < 64; i += 4) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), c, neg_m));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), c, neg_m));
-          const float p2 = ex2_approx(fmaf(__uint_as_float(s[i + 2]), c, neg_m));
-          const float p3 = ex2_approx(fmaf(__uint_as_float(s[i + 3]), c, neg_m));
-          l0 += p0; l1 += p1; l2 += p2; l3 += p3;
-          s[i >> 1] = pack_bf16x2(p0, p1);        // slot i/2 <= i: already consumed
-          s[(i >> 1) + 1] = pack_bf16x2(p2, p3);
-        }
-        l_sum += (l0 + l1) + (l2 + l3);
-        if (row == 0) H3A_STAMP(t, n, 4);
-        tmem_st32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-        tmem_wait_st();
-        tc_fence_before_sync();
-        mbar_arrive(smem_u32(&bars->p_full[t][hf]));
-        if (row == 0) H3A_STAMP(t, n, 5);
       }
+      if (row == 0) H3A_STAMP(t, 2 * j, 5);
+
+      // ---- half 1 from image B; prefetch half 0 of the stream's next tile into image A
+      if (row == 0) H3A_STAMP(t, 2 * j + 1, 0);
+      tmem_wait_ld();
+      reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&rb[0]));
+      reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&rb[32]));
+      if (row == 0) H3A_STAMP(t, 2 * j + 1, 2);
+      ok = softmax_half(rb, 1, tile, c);
+      if (!ok) break;
+      if (row == 0) H3A_STAMP(t, 2 * j + 1, 4);
+      {
+        const bool early = (it_next < n_it) && try_fetch_s(ra, 0, j + 1);
+        publish_p(rb, 1);
+        if (!early && it_next < n_it) ok = fetch_s(ra, 0, j + 1);
+        if (!ok) break;
+      }
+      if (row == 0) H3A_STAMP(t, 2 * j + 1, 5);
       ++j;
+      it = it_next;
     }
 
     // ---- epilogue: O / l -> bf16 -> global

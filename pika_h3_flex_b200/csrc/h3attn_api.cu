@@ -86,6 +86,10 @@ int32_t launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
   std::call_once(once, [] {
     attr_err = cudaFuncSetAttribute(h3a::attn_fwd_kernel<kFp8, kSparse>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     h3a::kAttnSmemBytes);
+    // the in-kernel register re-allocation would block forever if the launch allocation were smaller
+    cudaFuncAttributes fa;
+    if (attr_err == cudaSuccess) attr_err = cudaFuncGetAttributes(&fa, h3a::attn_fwd_kernel<kFp8, kSparse>);
+    if (attr_err == cudaSuccess && fa.numRegs < h3a::kLaunchRegs) attr_err = cudaErrorLaunchOutOfResources;
   });
   if (attr_err != cudaSuccess) return H3A_ERR_LAUNCH;
   const unsigned grid = static_cast<unsigned>(a.n_qpairs) * static_cast<unsigned>(a.H);
