@@ -38,7 +38,8 @@ enum {
   H3A_ERR_LAUNCH = -5,  /* CUDA runtime / driver call failed */
   H3A_ERR_TIMEOUT = -6, /* a bounded device-side wait ran out (read back from the status word) */
   H3A_ERR_WORKSPACE = -7, /* workspace missing or too small */
-  H3A_ERR_DRIVER = -8   /* driver entry point for tensor-map encoding not found */
+  H3A_ERR_DRIVER = -8,  /* driver entry point for tensor-map encoding not found */
+  H3A_ERR_STATIC_SCRATCH = -9 /* h3a_attn_fwd_sparse_static: block index larger than the built-in scratch */
 };
 
 /* attention modes */
@@ -147,6 +148,33 @@ int32_t h3a_rope_table(const float* pos, int32_t L, const int32_t split[3], floa
 int32_t h3a_build_block_index(int32_t T, int32_t Hg, int32_t Wg, int32_t n_audio,
                               int32_t wt, int32_t wh, int32_t ww,
                               int32_t* row_ptr, int32_t* col_idx, int64_t* nnz);
+
+/*
+ * Block-sparse attention for callers that must not allocate device memory.  (No counterpart in the
+ * reference project; it exists for hosts built around this library.)
+ *
+ * Who needs it: an embedding runtime that reserves the whole GPU for its own arena at start-up and forbids
+ * cudaMalloc afterwards -- a serving process with a fixed memory plan, where a late allocation can fail,
+ * fragment the arena or stall every stream while the driver synchronises the device -- has no buffer to pass
+ * as `workspace`.  Here the scratch for the merged tile plan is a fixed array inside the library:
+ * 262144 int32 (1 MiB) of device memory, held by every GPU that loads the library until the process exits.
+ *
+ * Same arguments and results as h3a_attn_fwd with mode == H3A_MODE_BLOCK_SPARSE (any other mode returns
+ * H3A_ERR_ARG); `workspace` and `workspace_bytes` are ignored.  The caller still owns q, k, v, o, the block
+ * index, lse and the status word.
+ *   - Limit: nnz + ceil(Lq/256) must be <= 262144 (h3a_static_scratch_capacity reports it), otherwise
+ *     H3A_ERR_STATIC_SCRATCH and nothing is launched.
+ *   - It calls no cudaMalloc, cudaFree or other allocating routine.
+ *   - The first call on each device looks up the array's device address (once per device, with that device
+ *     current); make that first call before starting any stream capture on the device.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.  Nothing in it has
+ *     to start at zero: each call rewrites every entry it later reads.  Two calls whose kernels can overlap on
+ *     the GPU (different streams, no ordering between them) race on it: serialise them.
+ */
+int32_t h3a_attn_fwd_sparse_static(const h3a_attn_params* p, void* stream);
+
+/* Capacity of that built-in scratch in plan entries (int32). */
+int32_t h3a_static_scratch_capacity(size_t* plan_entries);
 
 /* Copy the device status word to the host after synchronising `stream`; maps non-zero to H3A_ERR_TIMEOUT. */
 int32_t h3a_read_device_status(const int32_t* status_word, void* stream, int32_t* raw);

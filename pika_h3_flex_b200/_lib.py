@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libh3attn.so")
 H3A_OK = 0
 H3A_ERR_ARG, H3A_ERR_ALIGN, H3A_ERR_SHAPE, H3A_ERR_ARCH = -1, -2, -3, -4
 H3A_ERR_LAUNCH, H3A_ERR_TIMEOUT, H3A_ERR_WORKSPACE, H3A_ERR_DRIVER = -5, -6, -7, -8
+H3A_ERR_STATIC_SCRATCH = -9
 MODE_DENSE_BF16, MODE_FP8_QK, MODE_BLOCK_SPARSE = 0, 1, 2
 ROPE_INTERLEAVED, ROPE_HALF = 0, 1
 PREP_FP8 = 1
@@ -29,6 +30,8 @@ EXPORTS = (
     "h3a_rope_table",
     "h3a_build_block_index",
     "h3a_read_device_status",
+    "h3a_attn_fwd_sparse_static",
+    "h3a_static_scratch_capacity",
 )
 
 
@@ -95,6 +98,10 @@ def load() -> C.CDLL:
     lib.h3a_build_block_index.restype = C.c_int32
     lib.h3a_read_device_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
     lib.h3a_read_device_status.restype = C.c_int32
+    lib.h3a_attn_fwd_sparse_static.argtypes = [C.POINTER(AttnParams), C.c_void_p]
+    lib.h3a_attn_fwd_sparse_static.restype = C.c_int32
+    lib.h3a_static_scratch_capacity.argtypes = [C.POINTER(C.c_size_t)]
+    lib.h3a_static_scratch_capacity.restype = C.c_int32
     _lib = lib
     return lib
 

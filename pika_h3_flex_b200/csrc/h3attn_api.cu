@@ -97,6 +97,32 @@ int32_t launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
   return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
 }
 
+// ---- static scratch for h3a_attn_fwd_sparse_static -------------------------------------------------------
+// One plan entry per kept tile plus one count per query-tile pair, all int32.  1 MiB covers the 768p-like
+// sequence (985 x 985 tiles) up to about 27 % density.  Every GPU that loads this library holds the array
+// until the process exits.
+constexpr size_t kStaticScratchInts = 262144;
+static __device__ __align__(256) int32_t g_static_scratch[kStaticScratchInts];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+int32_t* g_scratch_addr[kMaxDevices] = {};  // device address of g_static_scratch, per device ordinal
+
+// In host code the name g_static_scratch is only a handle for the runtime, not a device pointer: the address
+// a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
+int32_t static_scratch_for_current_device(int32_t** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return H3A_ERR_LAUNCH;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return H3A_ERR_LAUNCH;
+    g_scratch_addr[dev] = static_cast<int32_t*>(ptr);
+  }
+  *out = g_scratch_addr[dev];
+  return H3A_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -118,6 +144,7 @@ const char* h3a_status_string(int32_t s) {
     case H3A_ERR_TIMEOUT: return "a bounded device-side wait ran out";
     case H3A_ERR_WORKSPACE: return "workspace missing or too small";
     case H3A_ERR_DRIVER: return "driver entry point cuTensorMapEncodeTiled not available";
+    case H3A_ERR_STATIC_SCRATCH: return "block index too large for the static scratch array (kept tiles + query-tile pairs > 262144)";
     default: return "unknown status";
   }
 }
@@ -279,6 +306,56 @@ int32_t h3a_build_block_index(int32_t T, int32_t Hg, int32_t Wg, int32_t n_audio
   if (total > 0x7FFFFFFF) return H3A_ERR_SHAPE;
   *nnz = total;
   return H3A_OK;
+}
+
+int32_t h3a_static_scratch_capacity(size_t* plan_entries) {
+  if (!plan_entries) return H3A_ERR_ARG;
+  *plan_entries = kStaticScratchInts;
+  return H3A_OK;
+}
+
+int32_t h3a_attn_fwd_sparse_static(const h3a_attn_params* p, void* stream) {
+  int32_t rc = validate_attn(p);
+  if (rc != H3A_OK) return rc;
+  if (p->mode != H3A_MODE_BLOCK_SPARSE) return H3A_ERR_ARG;
+  const size_t n_qpairs = (static_cast<size_t>(p->Lq) + 255) / 256;
+  if (static_cast<size_t>(p->nnz) + n_qpairs > kStaticScratchInts) return H3A_ERR_STATIC_SCRATCH;
+  rc = check_arch();
+  if (rc != H3A_OK) return rc;
+  int32_t* scratch = nullptr;
+  if ((rc = static_scratch_for_current_device(&scratch)) != H3A_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  CUtensorMap mq, mk, mv;
+  if ((rc = make_map(&mq, p->q, false, p->Lq, p->H, p->q_stride_l, p->q_stride_h)) != H3A_OK) return rc;
+  if ((rc = make_map(&mk, p->k, false, p->Lk, p->H, p->k_stride_l, p->k_stride_h)) != H3A_OK) return rc;
+  if ((rc = make_map(&mv, p->v, false, p->Lk, p->H, p->v_stride_l, p->v_stride_h)) != H3A_OK) return rc;
+
+  AttnArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.Lq = p->Lq; a.Lk = p->Lk; a.H = p->H;
+  a.nqb = (p->Lq + 127) / 128;
+  a.nkb = (p->Lk + 127) / 128;
+  a.n_kv_tiles = a.nkb;
+  a.n_qpairs = static_cast<int>(n_qpairs);
+  const float scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->d));
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.o = static_cast<__nv_bfloat16*>(p->o);
+  a.o_stride_l = p->o_stride_l; a.o_stride_h = p->o_stride_h;
+  a.lse = p->lse;
+  a.status = p->status_word;
+  a.wait_ns = p->wait_limit_ns > 0 ? p->wait_limit_ns : 2000000000ll;
+
+  // The plan kernel writes every count and every plan entry the attention kernel will read, so nothing in
+  // the array has to start at zero and whatever the previous call left there is never looked at.
+  int32_t* plan = scratch;
+  int32_t* plan_cnt = scratch + p->nnz;
+  const int threads = 128;
+  h3a::build_pair_plan_kernel<<<(a.n_qpairs + threads - 1) / threads, threads, 0, st>>>(p->row_ptr, p->col_idx, a.nqb,
+                                                                                       a.n_qpairs, plan, plan_cnt);
+  if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
+  a.row_ptr = p->row_ptr; a.plan = plan; a.plan_cnt = plan_cnt;
+  return launch_attn<false, true>(mq, mk, mv, a, st);
 }
 
 #ifdef H3A_TRACE

@@ -222,6 +222,48 @@ def attn_fwd(
     return (out, lse) if return_lse else out
 
 
+def static_scratch_capacity() -> int:
+    """Plan entries (int32) the library's built-in scratch holds: the limit on ``nnz + ceil(Lq/256)`` for
+    :func:`attn_fwd_sparse_static`."""
+    n = C.c_size_t(0)
+    check(_lib.load().h3a_static_scratch_capacity(C.byref(n)), "h3a_static_scratch_capacity")
+    return int(n.value)
+
+
+def attn_fwd_sparse_static(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_index: BlockIndex,
+                           out: torch.Tensor, softmax_scale: float = 0.0, status_word: Optional[torch.Tensor] = None):
+    """Block-sparse attention through ``h3a_attn_fwd_sparse_static``: for hosts that may not allocate device
+    memory once they are running, so the tile-plan scratch is the 1 MiB array inside the library and ``out``
+    must be supplied.  This wrapper itself creates no tensor.  Calls on one device share that scratch: do not
+    let two of them overlap on the GPU; make the first call on a device before any stream capture there."""
+    _require_cuda(q, k, v, out)
+    lib = _lib.load()
+    Lq, H, qsl, qsh = _lhd(q, "q", (torch.bfloat16,))
+    Lk, Hk, ksl, ksh = _lhd(k, "k", (torch.bfloat16,))
+    Lv, Hv, vsl, vsh = _lhd(v, "v", (torch.bfloat16,))
+    Lo, Ho, osl, osh = _lhd(out, "out", (torch.bfloat16,))
+    if Hk != H or Hv != H or Ho != H or Lv != Lk or Lo != Lq:
+        raise ValueError("q, k, v, out disagree on heads or lengths")
+    if block_index.n_q_tiles != (Lq + TILE - 1) // TILE or block_index.n_k_tiles != (Lk + TILE - 1) // TILE:
+        raise ValueError("block index does not match Lq / Lk")
+    if not block_index.row_ptr.is_cuda:
+        raise ValueError("block index must be on the device (BlockIndex.to(device))")
+    p = AttnParams()
+    p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    p.q_stride_l, p.q_stride_h = qsl, qsh
+    p.k_stride_l, p.k_stride_h = ksl, ksh
+    p.v_stride_l, p.v_stride_h = vsl, vsh
+    p.o_stride_l, p.o_stride_h = osl, osh
+    p.Lq, p.Lk, p.H, p.d, p.B = Lq, Lk, H, HEAD_DIM, 1
+    p.mode = _lib.MODE_BLOCK_SPARSE
+    p.softmax_scale = float(softmax_scale)
+    p.row_ptr, p.col_idx, p.nnz = block_index.row_ptr.data_ptr(), block_index.col_idx.data_ptr(), block_index.nnz
+    if status_word is not None:
+        p.status_word = status_word.data_ptr()
+    check(lib.h3a_attn_fwd_sparse_static(C.byref(p), _stream()), "h3a_attn_fwd_sparse_static")
+    return out
+
+
 def read_status(status_word: torch.Tensor) -> int:
     """Synchronise the current stream and return the raw device status word (0 = no wait gave up)."""
     raw = C.c_int32(0)
