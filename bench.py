@@ -43,7 +43,10 @@ WORKLOADS = {
 }
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_kernel launch, from the ncu captures summarised
 # under profiles/ (None until a capture of that workload exists)
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    "prof_dense": 251.6e6,           # measured (profiles/attn_fwd_dense_bf16_prof_dense.md)
+    "cfg1_dense": 251.6e6 * 7.535,   # the same capture scaled by the units per launch (L*H: 49,384*40 / 16,384*16)
+}
 
 
 def measured_peaks():
