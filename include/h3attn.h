@@ -150,6 +150,16 @@ int32_t h3a_build_block_index(int32_t T, int32_t Hg, int32_t Wg, int32_t n_audio
                               int32_t* row_ptr, int32_t* col_idx, int64_t* nnz);
 
 /*
+ * Strided copy between pinned host memory and the device (to_host = 0: host -> device, 1: device -> host):
+ * `rows` rows of `width_bytes`, row pitches in bytes.  Used by the host-buffer path to move the slice of a
+ * group of heads of a token-major [L, H, 128] tensor (width = heads * 256 bytes, pitch = H * 256 bytes) while
+ * another group is being computed; the reference moves whole tensors with `.to(device)` before the forward
+ * (src/pika_h3/core/wrapper.py:164-166, src/pika_h3/pipeline.py:115,128).
+ */
+int32_t h3a_memcpy2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows,
+                           int32_t to_host, void* stream);
+
+/*
  * Block-sparse attention for callers that must not allocate device memory.  (No counterpart in the
  * reference project; it exists for hosts built around this library.)
  *

@@ -32,6 +32,7 @@ EXPORTS = (
     "h3a_read_device_status",
     "h3a_attn_fwd_sparse_static",
     "h3a_static_scratch_capacity",
+    "h3a_memcpy2d_async",
 )
 
 
@@ -102,6 +103,8 @@ def load() -> C.CDLL:
     lib.h3a_attn_fwd_sparse_static.restype = C.c_int32
     lib.h3a_static_scratch_capacity.argtypes = [C.POINTER(C.c_size_t)]
     lib.h3a_static_scratch_capacity.restype = C.c_int32
+    lib.h3a_memcpy2d_async.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int32, C.c_void_p]
+    lib.h3a_memcpy2d_async.restype = C.c_int32
     _lib = lib
     return lib
 

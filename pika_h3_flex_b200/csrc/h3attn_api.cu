@@ -308,6 +308,15 @@ int32_t h3a_build_block_index(int32_t T, int32_t Hg, int32_t Wg, int32_t n_audio
   return H3A_OK;
 }
 
+int32_t h3a_memcpy2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows,
+                           int32_t to_host, void* stream) {
+  if (!dst || !src || width_bytes == 0 || rows == 0 || width_bytes > dst_pitch || width_bytes > src_pitch) return H3A_ERR_ARG;
+  const cudaError_t e = cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows,
+                                          to_host ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice,
+                                          static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
+}
+
 int32_t h3a_static_scratch_capacity(size_t* plan_entries) {
   if (!plan_entries) return H3A_ERR_ARG;
   *plan_entries = kStaticScratchInts;

@@ -134,3 +134,11 @@ def test_block_index_rejects_bad_arguments(lib):
     ci = np.zeros(1, dtype=np.int32)
     n = C.c_int64(0)
     assert lib.h3a_build_block_index(2, 8, 16, 0, 1, 1, 1, rp.ctypes.data, ci.ctypes.data, C.byref(n)) == _lib.H3A_ERR_WORKSPACE
+
+
+def test_memcpy2d_argument_validation(lib):
+    buf = (C.c_char * 64)()
+    a = C.addressof(buf)
+    assert lib.h3a_memcpy2d_async(None, 16, a, 16, 16, 1, 0, None) == _lib.H3A_ERR_ARG
+    assert lib.h3a_memcpy2d_async(a, 8, a, 16, 16, 1, 0, None) == _lib.H3A_ERR_ARG  # width beyond the pitch
+    assert lib.h3a_memcpy2d_async(a, 16, a, 16, 0, 1, 0, None) == _lib.H3A_ERR_ARG

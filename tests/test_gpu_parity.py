@@ -313,3 +313,33 @@ def test_errors_are_reported_not_swallowed(h):
         h.attn_fwd(q, k, v, h.MODE_BLOCK_SPARSE)
     with pytest.raises((TypeError, ValueError)):
         h.attn_fwd(q, k, v, h.MODE_FP8_QK)  # bf16 operands and no scales
+
+
+# ------------------------------------------------------------------------------------------ host-buffer path
+@pytest.mark.parametrize("mode_name,groups", [("dense", None), ("dense", [1, 2, 2]), ("fp8_qk", [5]), ("block_sparse", [2, 3])])
+def test_host_buffer_path_pipelined_over_head_groups(h, mode_name, groups):
+    grid, n_audio, H = (4, 8, 12), 100, 5
+    pos = O.make_positions(grid, n_audio)
+    L = pos.shape[0]
+    q, k, v = bf16_inputs(L, H, 90)
+    csr, bi, mode = None, None, h.MODE_DENSE_BF16
+    if mode_name == "block_sparse":
+        bih = h.build_block_index(grid, n_audio, (1, 2, 2))
+        csr, bi, mode = (bih.row_ptr.numpy(), bih.col_idx.numpy()), bih.to("cuda"), h.MODE_BLOCK_SPARSE
+    elif mode_name == "fp8_qk":
+        mode = h.MODE_FP8_QK
+    ref = O.joint_attention(q.float(), k.float(), v.float(), pos, mode_name, csr=csr)
+    host = h.HostJointAttention(L, H, mode, bi, head_groups=groups)
+    hq, hk, hv = (t.contiguous().pin_memory() for t in (q, k, v))
+    ho = torch.full((L, H, 128), 9.0, dtype=torch.bfloat16).pin_memory()
+    tab = h.rope_table(dev(pos))
+    for _ in range(2):  # second call reuses the staging buffers and streams
+        ho.fill_(9.0)
+        host(hq, hk, hv, tab, ho)
+        torch.cuda.current_stream().synchronize()
+        if mode_name == "fp8_qk":
+            assert O.error_stats(ho.float(), ref)["rel_l2"] <= FP8_REL
+        else:
+            check(ho, ref, mx=3e-2, mean=3e-3)
+    with pytest.raises(ValueError):
+        host(q, hk, hv, tab, ho)  # not pinned
