@@ -242,6 +242,9 @@ def run_ours(args):
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     attn_events = []
 
+    from pika_h3_flex_b200.ops import normed_logit_bound
+
+    bound = 0.0 if args.online_max else normed_logit_bound(fp8=(mode == _lib.MODE_FP8_QK))  # unit-weight QK-RMSNorm
     if world == 1:
         out = torch.empty(L, H, 128, dtype=torch.bfloat16, device=dev)
         ws = torch.empty(16, dtype=torch.uint8, device=dev)
@@ -253,7 +256,7 @@ def run_ours(args):
             if record:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-            h3.attn_fwd(qp, kp, v, mode, qs, ks, bi, out=out, status_word=status, workspace=ws)
+            h3.attn_fwd(qp, kp, v, mode, qs, ks, bi, out=out, status_word=status, workspace=ws, logit_bound=bound)
             if record:
                 e1.record()
                 attn_events.append((e0, e1))
@@ -355,6 +358,7 @@ def run_ours(args):
             "vs_baseline": None, "dtype": "bf16" if mode != _lib.MODE_FP8_QK else "e4m3(QK)+bf16(PV)", "data": "synthetic",
             "config": {"workload": name, "L": L, "H": H, "d": 128, "mode": mode_name, "density": density,
                        "flops_per_step": flops, "step": "qk_prep(RMSNorm+RoPE) + attention forward",
+                       "softmax_reference": "running row maximum" if bound == 0.0 else "fixed logit bound %.2f from QK-RMSNorm" % bound,
                        "parallelism": "single GPU" if world == 1 else f"ulysses{world} (seq<->head all-to-all, NCCL)",
                        "l2": "inputs (Q,K,V = %.0f MB per rank) exceed the 126 MB L2; no flush" % (3 * Ls * H * 256 / 1e6)},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
@@ -375,6 +379,7 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg1_dense")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the cpu_baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--online-max", action="store_true", help="use the running-maximum kernel instead of the fixed logit bound")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

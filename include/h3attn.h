@@ -89,6 +89,12 @@ typedef struct h3a_attn_params {
   int32_t* status_word;   /* optional device int32; a kernel that gives up a bounded wait writes a
                              non-zero code here and returns; must be 0 on entry */
   int64_t wait_limit_ns;  /* bound for each device-side wait; <= 0 selects 2 s */
+  float logit_bound;      /* optional: a value B with |q.k| * softmax_scale <= B for every query/key pair (with
+                             QK-RMSNorm: 128 * max|w_q| * max|w_k| * softmax_scale).  When 0 < B <= 30 the kernel
+                             uses B as the fixed softmax reference instead of a running row maximum: the result is
+                             the same softmax (any reference is exact), without the max pass and without rescaling.
+                             A bound that is too small only costs range, not correctness, up to a factor 2^40.
+                             0 = unknown: running maximum. */
 } h3a_attn_params;
 
 /*

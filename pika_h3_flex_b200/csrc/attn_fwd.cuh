@@ -42,6 +42,13 @@ static_assert(2 * 128 * kSoftmaxRegs + 128 * kHelperRegs <= kLaunchRegs * kAttnT
 constexpr int kProducerWarp = 8;
 constexpr int kIssuerWarp = 9;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+// S production: 0 = one N=64 MMA group per half (each half's S is produced while softmax works on the other
+// half, but these MMAs are shared-memory-bandwidth bound); 1 = one full-rate N=128 MMA group per key tile into
+// both halves' buffers, issued after the P V of the previous tile's second half.
+#ifndef H3A_FULL_S
+#define H3A_FULL_S 0
+#endif
+constexpr bool kFullS = H3A_FULL_S != 0;
 #ifndef H3A_POLY_PAIRS
 #define H3A_POLY_PAIRS 1
 #endif
@@ -80,6 +87,7 @@ struct AttnArgs {
   float* lse;              // [H, Lq] or null
   int* status;             // device status word or null
   long long wait_ns;
+  float fixed_m;           // fixed softmax reference in log2 units (kFixed kernels)
 };
 
 // status word layout: bits [0,8) code, bits [8,32) blockIdx.x (truncated)
@@ -147,7 +155,9 @@ __global__ void build_pair_plan_kernel(const int32_t* __restrict__ row_ptr, cons
   plan_cnt[p] = n;
 }
 
-template <bool kFp8, bool kSparse>
+// kFixed: the caller supplied an upper bound of the logits; it is used as the softmax reference for every row, so
+// there is no running maximum, no rescaling of O and no per-row state besides the row sum.
+template <bool kFp8, bool kSparse, bool kFixed>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnArgs args) {
@@ -270,8 +280,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (n_it > 0) {
       const int t = warp - kIssuerWarp;
       const uint32_t leader = elect_one();
-      constexpr uint32_t idesc_s = kFp8 ? umma_idesc(UMMA_FMT_E4M3, UMMA_FMT_E4M3, 0, 0, 128, 64)
-                                        : umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 0, 128, 64);
+      constexpr uint32_t kSN = kFullS ? 128 : 64;
+      constexpr uint32_t idesc_s = kFp8 ? umma_idesc(UMMA_FMT_E4M3, UMMA_FMT_E4M3, 0, 0, 128, kSN)
+                                        : umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 0, 128, kSN);
       constexpr uint32_t idesc_pv = umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 1, 128, 128);
       bool ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->q_full), 0, kWaitQFull));
       tc_fence_after_sync();
@@ -321,7 +332,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tc_fence_after_sync();
           if ((f0 >> t) & 1) {
             issue_s(0, 0);
-            issue_s(1, 0);
+            if constexpr (!kFullS) issue_s(1, 0);
           }
           umma_commit_if(leader, smem_u32(&bars->kv_empty[0]));
         }
@@ -356,8 +367,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               tc_fence_after_sync();
             }
           }
-          if (ok && mine_next) {
-            issue_s(hf, sk);
+          if (ok && mine_next && (!kFullS || hf == 1)) {
+            issue_s(kFullS ? 0 : hf, sk);  // with kFullS: both halves at once (hf offset 0, N = 128)
             H3A_STAMP(2 + t, 2 * it + hf, 3);
           }
         }
@@ -386,7 +397,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int qb = min(q0 / kTile + t, args.nqb - 1);
       qs = args.q_scale[head * args.nqb + qb];
     }
-    float m_ref = 0.0f, l_sum = 0.0f;
+    float m_ref = kFixed ? args.fixed_m : 0.0f, l_sum = 0.0f;
     uint32_t j = 0;  // key tiles this stream has processed
     bool ok = true;
     uint32_t ra[64], rb[64];  // two register images of an S half: one being processed, one being prefetched
@@ -423,6 +434,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int i = 0; i < 64; ++i)
           if (i >= valid) s[i] = 0xFF800000u;  // -inf
       }
+      if constexpr (!kFixed) {
       float mx0 = fmax3(__uint_as_float(s[0]), __uint_as_float(s[1]), __uint_as_float(s[2]));
       float mx1 = fmax3(__uint_as_float(s[3]), __uint_as_float(s[4]), __uint_as_float(s[5]));
       float mx2 = fmax3(__uint_as_float(s[6]), __uint_as_float(s[7]), __uint_as_float(s[8]));
@@ -464,6 +476,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
       }
+      }
       // p = 2^(s c - m): scale-and-subtract as packed FFMA2; of every 4 pairs, kPolyPairs take the
       // FMA-pipe polynomial and the rest the MUFU, so neither unit carries the whole tile
       uint64_t acc0 = 0, acc1 = 0;  // two packed accumulators = four partial row sums (bit pattern 0 == 0.0f)
@@ -500,7 +513,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     };
 
     int it = next_entry(0);
-    if (it < n_it) ok = fetch_s(ra, 0, 0);
+    if (it < n_it) {
+      ok = fetch_s(ra, 0, 0);
+      if (kFullS && ok) load_s(rb, 1);  // one barrier covers both halves
+    }
     while (ok && it < n_it) {
       const int tile = entry_at(it) >> 2;
       const int it_next = next_entry(it + 1);
@@ -517,7 +533,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       ok = softmax_half(ra, 0, tile, c);
       if (!ok) break;
       if (row == 0) H3A_STAMP(t, 2 * j, 4);
-      {
+      if constexpr (kFullS) {
+        publish_p(ra, 0);
+      } else {
         const bool early = try_fetch_s(rb, 1, j);
         publish_p(ra, 0);
         if (!early) ok = fetch_s(rb, 1, j);
@@ -534,7 +552,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       ok = softmax_half(rb, 1, tile, c);
       if (!ok) break;
       if (row == 0) H3A_STAMP(t, 2 * j + 1, 4);
-      {
+      if constexpr (kFullS) {
+        publish_p(rb, 1);
+        if (it_next < n_it) {
+          ok = fetch_s(ra, 0, j + 1);
+          if (!ok) break;
+          load_s(rb, 1);
+        }
+      } else {
         const bool early = (it_next < n_it) && try_fetch_s(ra, 0, j + 1);
         publish_p(rb, 1);
         if (!early && it_next < n_it) ok = fetch_s(ra, 0, j + 1);

@@ -79,21 +79,21 @@ size_t sparse_workspace_bytes(const h3a_attn_params* p) {
   return (static_cast<size_t>(p->nnz) + n_qpairs) * sizeof(int32_t);
 }
 
-template <bool kFp8, bool kSparse>
+template <bool kFp8, bool kSparse, bool kFixed = false>
 int32_t launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a, cudaStream_t st) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(h3a::attn_fwd_kernel<kFp8, kSparse>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    attr_err = cudaFuncSetAttribute(h3a::attn_fwd_kernel<kFp8, kSparse, kFixed>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     h3a::kAttnSmemBytes);
     // the in-kernel register re-allocation would block forever if the launch allocation were smaller
     cudaFuncAttributes fa;
-    if (attr_err == cudaSuccess) attr_err = cudaFuncGetAttributes(&fa, h3a::attn_fwd_kernel<kFp8, kSparse>);
+    if (attr_err == cudaSuccess) attr_err = cudaFuncGetAttributes(&fa, h3a::attn_fwd_kernel<kFp8, kSparse, kFixed>);
     if (attr_err == cudaSuccess && fa.numRegs < h3a::kLaunchRegs) attr_err = cudaErrorLaunchOutOfResources;
   });
   if (attr_err != cudaSuccess) return H3A_ERR_LAUNCH;
   const unsigned grid = static_cast<unsigned>(a.n_qpairs) * static_cast<unsigned>(a.H);
-  h3a::attn_fwd_kernel<kFp8, kSparse><<<grid, h3a::kAttnThreads, h3a::kAttnSmemBytes, st>>>(mq, mk, mv, a);
+  h3a::attn_fwd_kernel<kFp8, kSparse, kFixed><<<grid, h3a::kAttnThreads, h3a::kAttnSmemBytes, st>>>(mq, mk, mv, a);
   return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
 }
 
@@ -184,6 +184,10 @@ int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream) {
   a.lse = p->lse;
   a.status = p->status_word;
   a.wait_ns = p->wait_limit_ns > 0 ? p->wait_limit_ns : 2000000000ll;
+  // fixed softmax reference: the bound rescaled like the logits (x softmax_scale is already in it), in log2 units.
+  // Above 30 (2^-87 for a logit at minus the bound) the running-maximum kernel is used instead.
+  const bool fixed = p->logit_bound > 0.f && p->logit_bound <= 30.f;
+  a.fixed_m = fixed ? p->logit_bound * 1.4426950408889634f : 0.f;
 
   if (sparse) {
     const size_t need = sparse_workspace_bytes(p);
@@ -196,10 +200,10 @@ int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream) {
                                                                                          a.n_qpairs, plan, plan_cnt);
     if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
     a.row_ptr = p->row_ptr; a.plan = plan; a.plan_cnt = plan_cnt;
-    return launch_attn<false, true>(mq, mk, mv, a, st);
+    return fixed ? launch_attn<false, true, true>(mq, mk, mv, a, st) : launch_attn<false, true, false>(mq, mk, mv, a, st);
   }
-  if (fp8) return launch_attn<true, false>(mq, mk, mv, a, st);
-  return launch_attn<false, false>(mq, mk, mv, a, st);
+  if (fp8) return fixed ? launch_attn<true, false, true>(mq, mk, mv, a, st) : launch_attn<true, false, false>(mq, mk, mv, a, st);
+  return fixed ? launch_attn<false, false, true>(mq, mk, mv, a, st) : launch_attn<false, false, false>(mq, mk, mv, a, st);
 }
 
 int32_t h3a_qk_prep(const h3a_prep_params* p, void* stream) {

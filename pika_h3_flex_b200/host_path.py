@@ -64,7 +64,8 @@ class HostJointAttention:
             ev_in.record(self.s_in)
             cur.wait_event(ev_in)
             qp, kp, qs, ks = ops.qk_prep(self.dq[:, h0:h1], self.dk[:, h0:h1], rope, rope, fp8=fp8)
-            ops.attn_fwd(qp, kp, self.dv[:, h0:h1], self.mode, qs, ks, self.block_index, out=self.do[:, h0:h1])
+            ops.attn_fwd(qp, kp, self.dv[:, h0:h1], self.mode, qs, ks, self.block_index, out=self.do[:, h0:h1],
+                         logit_bound=ops.normed_logit_bound(fp8=fp8))
             ev_c = torch.cuda.Event()
             ev_c.record(cur)
             self.s_out.wait_event(ev_c)

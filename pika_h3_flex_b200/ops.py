@@ -167,6 +167,7 @@ def attn_fwd(
     status_word: Optional[torch.Tensor] = None,
     wait_limit_ns: int = 0,
     workspace: Optional[torch.Tensor] = None,
+    logit_bound: float = 0.0,
 ):
     """Forward attention through ``h3a_attn_fwd``.  Returns ``out [Lq, H, 128]`` bf16 (and ``lse [H, Lq]``)."""
     _require_cuda(q, k, v)
@@ -218,6 +219,7 @@ def attn_fwd(
     if status_word is not None:
         p.status_word = status_word.data_ptr()
     p.wait_limit_ns = int(wait_limit_ns)
+    p.logit_bound = float(logit_bound)
     check(lib.h3a_attn_fwd(C.byref(p), _stream()), "h3a_attn_fwd")
     return (out, lse) if return_lse else out
 
@@ -273,6 +275,17 @@ def read_status(status_word: torch.Tensor) -> int:
     return raw.value
 
 
+def normed_logit_bound(q_weight=None, k_weight=None, softmax_scale: float = 0.0, fp8: bool = False) -> float:
+    """Upper bound of ``|q.k| * scale`` after per-head RMSNorm: each prepared row has norm at most
+    ``sqrt(128) * max|w|`` (Cauchy-Schwarz), so ``|q.k| <= 128 * max|w_q| * max|w_k|``.  A 2 % margin covers the
+    bf16 rounding of the prepared rows, 13 % more the e4m3 rounding in FP8 mode.  Reads the weights once (a device
+    synchronisation): cache the result per module."""
+    wq = 1.0 if q_weight is None else float(q_weight.detach().abs().max())
+    wk = 1.0 if k_weight is None else float(k_weight.detach().abs().max())
+    scale = softmax_scale if softmax_scale > 0 else HEAD_DIM ** -0.5
+    return HEAD_DIM * wq * wk * scale * (1.15 if fp8 else 1.02)
+
+
 def joint_attention(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -285,9 +298,14 @@ def joint_attention(
     eps: float = 1e-6,
     rope_half: bool = False,
     k_rope: Optional[torch.Tensor] = None,
+    logit_bound: Optional[float] = None,
     **kw,
 ):
-    """The whole hot path on one GPU: prepare Q/K (norm, rotation, optional e4m3) then attention."""
+    """The whole hot path on one GPU: prepare Q/K (norm, rotation, optional e4m3) then attention.
+    ``logit_bound`` None derives the bound from the RMSNorm weights (unit weights need no device read); pass a
+    cached value to avoid the read, or 0 to force the running-maximum kernel."""
     fp8 = mode == _lib.MODE_FP8_QK
+    if logit_bound is None:
+        logit_bound = normed_logit_bound(q_weight, k_weight, kw.get("softmax_scale", 0.0), fp8)
     qp, kp, qs, ks = qk_prep(q, k, rope, rope if k_rope is None else k_rope, q_weight, k_weight, eps, fp8, rope_half)
-    return attn_fwd(qp, kp, v, mode, qs, ks, block_index, **kw)
+    return attn_fwd(qp, kp, v, mode, qs, ks, block_index, logit_bound=logit_bound, **kw)

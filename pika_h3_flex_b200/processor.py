@@ -87,6 +87,7 @@ class B200AttnProcessor:
         self.qk_norm = qk_norm
         self.eps = eps
         self._rope_cache = RopeCache()
+        self._bounds = {}
 
     # ---- rotary information from whatever the caller passes
     def _rope(self, S: int, image_rotary_emb, kwargs) -> Optional[torch.Tensor]:
@@ -130,7 +131,12 @@ class B200AttnProcessor:
         bi = self.block_index
         if cross and mode == _lib.MODE_BLOCK_SPARSE:
             mode, bi = _lib.MODE_DENSE_BF16, None  # the block index describes the joint self-attention only
-        return ops.joint_attention(q, k, v, None if cross else rope, mode, bi, qw, kw, eps, self.rope_half)
+        # the logit bound depends only on the (static) norm weights: read them once per module
+        key = (id(attn), mode == _lib.MODE_FP8_QK)
+        bound = self._bounds.get(key)
+        if bound is None:
+            bound = self._bounds[key] = ops.normed_logit_bound(qw, kw, 0.0, mode == _lib.MODE_FP8_QK)
+        return ops.joint_attention(q, k, v, None if cross else rope, mode, bi, qw, kw, eps, self.rope_half, logit_bound=bound)
 
     def __call__(self, attn, hidden_states: torch.Tensor, encoder_hidden_states: Optional[torch.Tensor] = None,
                  attention_mask: Optional[torch.Tensor] = None, image_rotary_emb=None, **kwargs) -> torch.Tensor:

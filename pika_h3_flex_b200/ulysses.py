@@ -119,7 +119,8 @@ class UlyssesAttention:
     def _cuda_attn(q, k, v, mode, q_scale, k_scale, block_index):
         # head-major output so that the return exchange sends contiguous [L/P, 128] blocks without a copy
         out = torch.empty(q.shape[1], q.shape[0], ops.HEAD_DIM, dtype=torch.bfloat16, device=q.device).permute(1, 0, 2)
-        return ops.attn_fwd(q, k, v, mode, q_scale, k_scale, block_index, out=out)
+        bound = ops.normed_logit_bound(fp8=(mode == _lib.MODE_FP8_QK))  # operands come from the unit-weight prep
+        return ops.attn_fwd(q, k, v, mode, q_scale, k_scale, block_index, out=out, logit_bound=bound)
 
     def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rope: Optional[torch.Tensor]) -> torch.Tensor:
         world = dist.get_world_size(self.group)

@@ -38,7 +38,7 @@ def test_version_and_status_strings(lib):
 
 def test_struct_sizes_match_header(lib):
     # natural-alignment sizes of the two parameter structs as a C compiler lays them out
-    assert C.sizeof(_lib.AttnParams) == 208
+    assert C.sizeof(_lib.AttnParams) == 216
     assert C.sizeof(_lib.PrepParams) == 144
 
 

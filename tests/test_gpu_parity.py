@@ -343,3 +343,34 @@ def test_host_buffer_path_pipelined_over_head_groups(h, mode_name, groups):
             check(ho, ref, mx=3e-2, mean=3e-3)
     with pytest.raises(ValueError):
         host(q, hk, hv, tab, ho)  # not pinned
+
+
+# ------------------------------------------------------------------------------------------ fixed softmax reference
+@pytest.mark.parametrize("L,Lk,H", [(300, 300, 2), (1000, 1500, 3), (129, 64, 1)])
+def test_fixed_logit_bound_gives_the_same_softmax(h, L, Lk, H):
+    q, k, v = bf16_inputs(L, H, 300 + L, Lk)
+    ref, ref_lse = O.attention(q.float(), k.float(), v.float(), return_lse=True)
+    s = torch.einsum("qhd,khd->hqk", q.float(), k.float()) / 128 ** 0.5
+    true_bound = float(s.abs().max())
+    for bound in (true_bound * 1.05, 30.0, true_bound * 0.5):  # tight, loosest accepted, and too small (still exact)
+        out, lse = h.attn_fwd(dev(q), dev(k), dev(v), return_lse=True, logit_bound=bound)
+        check(out, ref, mx=3e-2 if Lk < 256 else BF16_MAX, mean=4e-3 if Lk < 256 else BF16_MEAN)
+        assert float((lse.cpu().t() - ref_lse).abs().max()) < 2e-3
+    out = h.attn_fwd(dev(q), dev(k), dev(v), logit_bound=1e6)  # unusable bound: falls back to the running maximum
+    check(out, ref, mx=3e-2 if Lk < 256 else BF16_MAX, mean=4e-3 if Lk < 256 else BF16_MEAN)
+
+
+def test_joint_path_bound_from_norm_weights(h):
+    L, H = 700, 2
+    q, k, v = bf16_inputs(L, H, 77)
+    g = torch.Generator().manual_seed(6)
+    qw, kw = 1 + 0.3 * torch.randn(128, generator=g), 1 + 0.3 * torch.randn(128, generator=g)
+    pos = O.make_positions((4, 10, 15), 100)
+    ref = O.joint_attention(q.float(), k.float(), v.float(), pos, "dense", q_weight=qw, k_weight=kw)
+    tab = h.rope_table(dev(pos))
+    from pika_h3_flex_b200.ops import normed_logit_bound
+    b = normed_logit_bound(qw, kw)
+    assert abs(b - 128 * float(qw.abs().max()) * float(kw.abs().max()) / 128 ** 0.5 * 1.02) < 1e-4
+    for lb in (None, 0.0):  # derived bound / running maximum
+        out = h.joint_attention(dev(q), dev(k), dev(v), tab, q_weight=dev(qw), k_weight=dev(kw), logit_bound=lb)
+        check(out, ref)
