@@ -31,16 +31,24 @@ constexpr int kStages = 5;
 constexpr int kStageBytes = 32768;
 constexpr int kQTileBytes = 32768;
 constexpr int kHalfBytes = 16384;  // one [128 rows][128 bytes] swizzled box
-constexpr int kAttnThreads = 384;  // warpgroups 0,1: softmax; warpgroup 2: producer, issuer, two idle warps
-// Register re-allocation: setmaxnreg.inc BLOCKS until the registers exist, and they can only come from what
-// the CTA owns at launch (registers per thread reported by the compiler x 384) minus what the helper
-// warpgroup gives back.  kLaunchRegs is checked against the real kernel attribute before every first launch.
-constexpr int kLaunchRegs = 168;
-constexpr int kSoftmaxRegs = 208;
-constexpr int kHelperRegs = 88;
-static_assert(2 * 128 * kSoftmaxRegs + 128 * kHelperRegs <= kLaunchRegs * kAttnThreads, "setmaxnreg budget exceeds the launch allocation");
-constexpr int kProducerWarp = 8;
-constexpr int kIssuerWarp = 9;
+// Thread layout.  Running-maximum kernels: warpgroups 0,1 = softmax of stream 0,1 (a warp walks both halves of
+// every tile, they share the row's running maximum); warpgroup 2 = producer, two issuers, one idle warp.
+// Fixed-reference kernels have no per-row state besides the row sum, so every (stream, half) gets its own
+// warpgroup: four softmax warps per SM sub-partition instead of two hide each other's TMEM-load, store and
+// barrier latencies.
+// Register re-allocation: setmaxnreg.inc BLOCKS until the registers exist, and they can only come from what the
+// CTA owns at launch (registers per thread reported by the compiler x threads) minus what the helper warpgroup
+// gives back.  kLaunchRegs is checked against the real kernel attribute before every first launch.
+template <bool kFixed>
+struct AttnLayout {
+  static constexpr int kSoftmaxWarps = kFixed ? 16 : 8;
+  static constexpr int kThreads = (kSoftmaxWarps + 4) * 32;
+  static constexpr int kLaunchRegs = kFixed ? 96 : 168;
+  static constexpr int kSoftmaxRegs = kFixed ? 104 : 208;
+  static constexpr int kHelperRegs = kFixed ? 64 : 88;
+  static_assert(kSoftmaxWarps * 32 * kSoftmaxRegs + 128 * kHelperRegs <= kLaunchRegs * kThreads,
+                "setmaxnreg budget exceeds the launch allocation");
+};
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 // S production: 0 = one N=64 MMA group per half (each half's S is produced while softmax works on the other
 // half, but these MMAs are shared-memory-bandwidth bound); 1 = one full-rate N=128 MMA group per key tile into
@@ -158,7 +166,7 @@ __global__ void build_pair_plan_kernel(const int32_t* __restrict__ row_ptr, cons
 // kFixed: the caller supplied an upper bound of the logits; it is used as the softmax reference for every row, so
 // there is no running maximum, no rescaling of O and no per-row state besides the row sum.
 template <bool kFp8, bool kSparse, bool kFixed>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(AttnLayout<kFixed>::kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnArgs args) {
   extern __shared__ uint8_t smem_raw[];
@@ -169,6 +177,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t ring_smem = base + 2 * kQTileBytes;
   AttnBars* bars = reinterpret_cast<AttnBars*>(smem + 2 * kQTileBytes + kStages * kStageBytes);
 
+  using LY = AttnLayout<kFixed>;
+  constexpr int kProducerWarp = LY::kSoftmaxWarps;
+  constexpr int kIssuerWarp = LY::kSoftmaxWarps + 1;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int head = blockIdx.x / args.n_qpairs;
@@ -231,8 +242,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   WaitCtx wc{bars, args.status, args.wait_ns};
 
-  if (warp >= 8) {
-   setmaxnreg_dec<kHelperRegs>();
+  if (warp >= LY::kSoftmaxWarps) {
+   setmaxnreg_dec<LY::kHelperRegs>();
    if (warp == kProducerWarp) {
     // =========================================================== producer
     // The whole warp walks the loop (uniform control flow, uniform operands); one elected lane issues.
@@ -380,7 +391,121 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     __syncwarp();
    }
   } else {
-    setmaxnreg_inc<kSoftmaxRegs>();
+    setmaxnreg_inc<LY::kSoftmaxRegs>();
+    if constexpr (kFixed) {
+    // =========================================================== softmax, fixed reference: one warpgroup per (stream, half)
+    const int wg = warp >> 2;
+    const int t = wg & 1;               // stream
+    const int hf = wg >> 1;             // which 64-key half of every tile this warpgroup owns
+    const int quarter = warp & 3;       // TMEM lane quarter this warp may touch
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t sb = tmem + lane_base + t * kTile + hf * 64;
+    const uint32_t o_addr = tmem + lane_base + 256 + t * kTile + hf * 64;  // epilogue: this warpgroup's 64 O columns
+    const int q_row = q0 + t * kTile + row;
+    const int last_tile = args.n_kv_tiles - 1;
+    const int tail = args.Lk - last_tile * kTile;
+    float qs = 1.0f;
+    if constexpr (kFp8) {
+      const int qb = min(q0 / kTile + t, args.nqb - 1);
+      qs = args.q_scale[head * args.nqb + qb];
+    }
+    const float m_ref = args.fixed_m;
+    float l_sum = 0.0f;
+    uint32_t j = 0;
+    bool ok = true;
+    uint32_t s[64];
+    for (int it = 0; ok && it < n_it; ++it) {
+      const int e = entry_at(it);
+      if (!((e >> t) & 1)) continue;
+      const int tile = e >> 2;
+      float c = args.scale_log2;
+      if constexpr (kFp8) c *= qs * args.k_scale[head * args.nkb + tile];
+      // with kFullS one N=128 MMA group fills both halves and signals s_full[t][0] for both warpgroups
+      ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->s_full[t][kFullS ? 0 : hf]), j & 1, kWaitSFull));
+      if (!ok) break;
+      tc_fence_after_sync();
+      tmem_ld32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_ld32(sb + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      tmem_wait_ld();
+      reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      if (tile == last_tile && tail < kTile) {
+        const int valid = tail - hf * 64;
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (i >= valid) s[i] = 0xFF800000u;  // -inf
+      }
+      uint64_t acc0 = 0, acc1 = 0;
+      const uint64_t c2 = pack2(c, c), nm2 = pack2(-m_ref, -m_ref);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const uint64_t x = fma2(pack2u(s[2 * i], s[2 * i + 1]), c2, nm2);
+        uint64_t pp;
+        if ((i & 3) < (kFp8 ? kPolyPairsFp8 : kPolyPairsBf16)) {
+          pp = exp2_poly2(x);
+        } else {
+          float x0, x1;
+          unpack2(x, x0, x1);
+          pp = pack2(ex2_approx(x0), ex2_approx(x1));
+        }
+        if (i & 1) acc1 = add2(acc1, pp);
+        else acc0 = add2(acc0, pp);
+        float p0, p1;
+        unpack2(pp, p0, p1);
+        s[i] = pack_bf16x2(p0, p1);
+      }
+      float a0, a1, a2, a3;
+      unpack2(acc0, a0, a1);
+      unpack2(acc1, a2, a3);
+      l_sum += (a0 + a1) + (a2 + a3);
+      tmem_st32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&bars->p_full[t][hf]));
+      ++j;
+    }
+    // ---- epilogue: the two warpgroups of a stream add their row sums through shared memory (the stream's Q
+    //      tile is free once its last MMA has completed) and each stores 64 of the 128 output columns
+    bool have = ok && j > 0;
+    if (have) {
+      have = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->o_full[t][1]), (j - 1) & 1, kWaitOFull));
+      if (have) tc_fence_after_sync();
+    }
+    float* lbuf = reinterpret_cast<float*>(smem + t * kQTileBytes);
+    lbuf[hf * 128 + row] = l_sum;
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");  // every thread of both warpgroups, always
+    const bool row_valid = q_row < args.Lq;
+    __nv_bfloat16* orow = args.o + static_cast<long long>(q_row) * args.o_stride_l + static_cast<long long>(head) * args.o_stride_h + 64 * hf;
+    if (have) {
+      const float l_tot = l_sum + lbuf[(hf ^ 1) * 128 + row];
+      const float inv = 1.0f / l_tot;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        uint32_t o[32];
+        tmem_ld32(o_addr + 32 * i, o);
+        tmem_wait_ld();
+        if (row_valid) {
+#pragma unroll
+          for (int x = 0; x < 32; x += 8) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[x]) * inv, __uint_as_float(o[x + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(o[x + 2]) * inv, __uint_as_float(o[x + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(o[x + 4]) * inv, __uint_as_float(o[x + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(o[x + 6]) * inv, __uint_as_float(o[x + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + 32 * i + x) = w;
+          }
+        }
+      }
+      if (row_valid && args.lse && hf == 0)
+        args.lse[static_cast<long long>(head) * args.Lq + q_row] = (m_ref + log2f(l_tot)) * 0.6931471805599453f;
+    } else if (ok && j == 0 && row_valid) {
+      const uint4 z = make_uint4(0, 0, 0, 0);  // no key tile listed for this query tile: the output row is zero
+#pragma unroll
+      for (int x = 0; x < 64; x += 8) *reinterpret_cast<uint4*>(orow + x) = z;
+      if (args.lse && hf == 0) args.lse[static_cast<long long>(head) * args.Lq + q_row] = -INFINITY;
+    }
+    } else {
     // =========================================================== softmax / rescale / epilogue
     const int t = warp >> 2;            // stream
     const int quarter = warp & 3;       // TMEM lane quarter this warp may touch
@@ -604,6 +729,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
       for (int x = 0; x < 128; x += 8) *reinterpret_cast<uint4*>(orow + x) = z;
       if (args.lse) args.lse[static_cast<long long>(head) * args.Lq + q_row] = -INFINITY;
+    }
     }
   }
 

@@ -89,11 +89,11 @@ int32_t launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
     // the in-kernel register re-allocation would block forever if the launch allocation were smaller
     cudaFuncAttributes fa;
     if (attr_err == cudaSuccess) attr_err = cudaFuncGetAttributes(&fa, h3a::attn_fwd_kernel<kFp8, kSparse, kFixed>);
-    if (attr_err == cudaSuccess && fa.numRegs < h3a::kLaunchRegs) attr_err = cudaErrorLaunchOutOfResources;
+    if (attr_err == cudaSuccess && fa.numRegs < h3a::AttnLayout<kFixed>::kLaunchRegs) attr_err = cudaErrorLaunchOutOfResources;
   });
   if (attr_err != cudaSuccess) return H3A_ERR_LAUNCH;
   const unsigned grid = static_cast<unsigned>(a.n_qpairs) * static_cast<unsigned>(a.H);
-  h3a::attn_fwd_kernel<kFp8, kSparse, kFixed><<<grid, h3a::kAttnThreads, h3a::kAttnSmemBytes, st>>>(mq, mk, mv, a);
+  h3a::attn_fwd_kernel<kFp8, kSparse, kFixed><<<grid, h3a::AttnLayout<kFixed>::kThreads, h3a::kAttnSmemBytes, st>>>(mq, mk, mv, a);
   return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
 }
 
