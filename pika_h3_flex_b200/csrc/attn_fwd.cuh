@@ -61,7 +61,10 @@ constexpr bool kFullS = H3A_FULL_S != 0;
 #define H3A_POLY_PAIRS 1
 #endif
 constexpr int kPolyPairsBf16 = H3A_POLY_PAIRS;  // of every 4 element pairs, how many use the polynomial exp2 (0..4)
-constexpr int kPolyPairsFp8 = 0;               // measured: with the cheaper e4m3 S MMAs the MUFU-only loop is faster
+#ifndef H3A_POLY_FP8
+#define H3A_POLY_FP8 0
+#endif
+constexpr int kPolyPairsFp8 = H3A_POLY_FP8;    // FP8 mode has its own share: its S MMAs are cheaper, the balance differs
 
 struct AttnBars {
   uint64_t kv_full[kStages];
