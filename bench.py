@@ -36,6 +36,8 @@ WORKLOADS = {
     "cfg3_sparse": ((31, 48, 84), 1024, 40, "block_sparse", (2, 8, 8), 1003),
     "cfg3_sparse20": ((31, 48, 84), 1024, 40, "block_sparse", (3, 48, 84), 1003),
     "cfg0_dense": ((4, 32, 32), 0, 8, "dense_bf16", None, 1000),
+    # config 4's cross-attention: the 49,384 joint tokens attend to 512 text tokens (already projected to 40 x 128)
+    "cfg4_cross": ((31, 30, 52), 1024, 40, "cross_bf16", None, 1004),
     # small cases for profiler captures: inputs above the L2 size, a few ms per launch
     "prof_dense": ((15, 32, 32), 1024, 16, "dense_bf16", None, 2001),
     "prof_fp8": ((15, 32, 32), 1024, 16, "fp8_qk", None, 2001),
@@ -127,8 +129,10 @@ def cpu_oracle_sample(name: str, target_seconds: float = 15.0, threads: int | No
     torch.set_num_threads(threads)
     Hs = min(H, 4)  # heads in the sample (per-head work is identical)
     g = torch.Generator().manual_seed(seed)
-    k = torch.randn(L, Hs, 128, generator=g)
-    v = torch.randn(L, Hs, 128, generator=g)
+    cross = mode == "cross_bf16"
+    Lk = 512 if cross else L
+    k = torch.randn(Lk, Hs, 128, generator=g)
+    v = torch.randn(Lk, Hs, 128, generator=g)
     pos = O.make_positions(grid, n_audio)
     cos, sin = O.rope_table(pos)
     csr = None
@@ -145,8 +149,11 @@ def cpu_oracle_sample(name: str, target_seconds: float = 15.0, threads: int | No
         q = torch.randn(L, Hs, 128, generator=torch.Generator().manual_seed(seed + 1))
         t0 = time.perf_counter()
         # preparation of the sampled rows and of all keys, then exact attention for the sampled rows
-        qn = O.apply_rope(O.rms_norm(q[rows]), cos[rows], sin[rows])
-        kn = O.apply_rope(O.rms_norm(k), cos, sin)
+        if cross:
+            qn, kn = O.rms_norm(q[rows]), O.rms_norm(k)
+        else:
+            qn = O.apply_rope(O.rms_norm(q[rows]), cos[rows], sin[rows])
+            kn = O.apply_rope(O.rms_norm(k), cos, sin)
         if mode == "fp8_qk":
             kq, sk = O.quantize_e4m3_blocks(kn)
             kn = O.dequantize_blocks(kq, sk)
@@ -157,7 +164,7 @@ def cpu_oracle_sample(name: str, target_seconds: float = 15.0, threads: int | No
             full_q[rows] = qn
             O.attention(full_q, kn, v, csr=csr, q_rows=rows, chunk=512)
         dt = time.perf_counter() - t0
-        flops = 4.0 * n_rows * L * 128 * Hs * (1.0 if csr is None else 1.0)
+        flops = 4.0 * n_rows * Lk * 128 * Hs
         return dt, flops
 
     run(64)  # warm-up (thread pool, allocator)
@@ -166,7 +173,7 @@ def cpu_oracle_sample(name: str, target_seconds: float = 15.0, threads: int | No
     dt, flops = run(n_rows)
     # the masked oracle still evaluates full rows, so its useful FLOPs are scaled by the density
     tflops = flops * density / dt / 1e12
-    return tflops, threads, f"{n_rows} query rows x {Hs} heads x all {L} keys of {name} (prep + exact softmax attention, fp32)", dt
+    return tflops, threads, f"{n_rows} query rows x {Hs} heads x all {Lk} keys of {name} (prep + exact softmax attention, fp32)", dt
 
 
 def run_reference(args):
@@ -175,6 +182,7 @@ def run_reference(args):
         return
     name = args.workload
     grid, n_audio, L, H, mode, window, seed = workload_dims(name)
+    Lk = 512 if mode == "cross_bf16" else L
     per_step = max(2.0, min(20.0, 90.0 / max(1, args.steps + args.warmup)))
     vals, times = [], []
     cores = os.cpu_count() or 1
@@ -189,7 +197,7 @@ def run_reference(args):
         "impl": "reference", "metric": "attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "L": L, "H": H, "d": 128, "mode": mode,
+        "config": {"workload": name, "L": L, "Lk": Lk, "H": H, "d": 128, "mode": mode,
                    "note": "CPU restatement of the reference attention (oracle); each step is a bounded sample"},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -220,7 +228,8 @@ def run_ours(args):
 
     name = args.workload
     grid, n_audio, L, H, mode_name, window, seed = workload_dims(name)
-    mode = {"dense_bf16": _lib.MODE_DENSE_BF16, "fp8_qk": _lib.MODE_FP8_QK, "block_sparse": _lib.MODE_BLOCK_SPARSE}[mode_name]
+    mode = {"dense_bf16": _lib.MODE_DENSE_BF16, "fp8_qk": _lib.MODE_FP8_QK, "block_sparse": _lib.MODE_BLOCK_SPARSE,
+            "cross_bf16": _lib.MODE_DENSE_BF16}[mode_name]
     if L % world:
         raise SystemExit(f"sequence length {L} does not split over {world} ranks")
     Ls = L // world
@@ -238,7 +247,11 @@ def run_ours(args):
         bi_host = h3.build_block_index(grid, n_audio, window)
         density = bi_host.density
         bi = bi_host.to(dev)
-    flops = 4.0 * L * L * 128 * H * density
+    cross = mode_name == "cross_bf16"
+    Lk = 512 if cross else L
+    if cross and world > 1:
+        raise SystemExit("cross-attention needs no exchange: run it per rank with --gpus 1")
+    flops = 4.0 * L * Lk * 128 * H * density
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     attn_events = []
 
@@ -251,8 +264,12 @@ def run_ours(args):
         if bi is not None:
             ws = torch.empty((bi.nnz + (L + 255) // 256) * 4 + 16, dtype=torch.uint8, device=dev)
 
+        if cross:  # keys and values are the text tokens; QK-RMSNorm without rotation
+            k = k[:Lk].contiguous()
+            v = v[:Lk].contiguous()
+
         def step(record=False):
-            qp, kp, qs, ks = h3.qk_prep(q, k, rope, rope, fp8=(mode == _lib.MODE_FP8_QK))
+            qp, kp, qs, ks = h3.qk_prep(q, k, None if cross else rope, None if cross else rope, fp8=(mode == _lib.MODE_FP8_QK))
             if record:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
@@ -316,7 +333,10 @@ def run_ours(args):
 
     # ---- end to end from host buffers through the public call
     e2e = None
-    if world == 1:
+    if world == 1 and cross:
+        e2e = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+               "note": "host-buffer end-to-end is measured on the self-attention workloads"}
+    elif world == 1:
         hq, hk, hv = (torch.empty(L, H, 128, dtype=torch.bfloat16).pin_memory() for _ in range(3))
         for dst, src_t in ((hq, q), (hk, k), (hv, v)):
             dst.copy_(src_t)
@@ -356,7 +376,7 @@ def run_ours(args):
             "metric": "attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16" if mode != _lib.MODE_FP8_QK else "e4m3(QK)+bf16(PV)", "data": "synthetic",
-            "config": {"workload": name, "L": L, "H": H, "d": 128, "mode": mode_name, "density": density,
+            "config": {"workload": name, "L": L, "Lk": Lk, "H": H, "d": 128, "mode": mode_name, "density": density,
                        "flops_per_step": flops, "step": "qk_prep(RMSNorm+RoPE) + attention forward",
                        "softmax_reference": "running row maximum" if bound == 0.0 else "fixed logit bound %.2f from QK-RMSNorm" % bound,
                        "parallelism": "single GPU" if world == 1 else f"ulysses{world} (seq<->head all-to-all, NCCL)",

@@ -192,6 +192,14 @@ int32_t h3a_attn_fwd_sparse_static(const h3a_attn_params* p, void* stream);
 /* Capacity of that built-in scratch in plan entries (int32). */
 int32_t h3a_static_scratch_capacity(size_t* plan_entries);
 
+/*
+ * Diagnostic for the bounded device-side waits (no counterpart in the reference): launches one warp that waits,
+ * with the helper the attention kernels use, on a barrier that nothing ever signals.  After at most
+ * wait_limit_ns (1 ns .. 1 s) the warp gives up, writes code 9 into *status_word and returns; the context stays
+ * usable.  Lets a deployment check that a lost signal turns into H3A_ERR_TIMEOUT instead of a hung GPU.
+ */
+int32_t h3a_selftest_wait_timeout(int32_t* status_word, int64_t wait_limit_ns, void* stream);
+
 /* Copy the device status word to the host after synchronising `stream`; maps non-zero to H3A_ERR_TIMEOUT. */
 int32_t h3a_read_device_status(const int32_t* status_word, void* stream, int32_t* raw);
 

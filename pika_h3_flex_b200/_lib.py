@@ -33,6 +33,7 @@ EXPORTS = (
     "h3a_attn_fwd_sparse_static",
     "h3a_static_scratch_capacity",
     "h3a_memcpy2d_async",
+    "h3a_selftest_wait_timeout",
 )
 
 
@@ -105,6 +106,8 @@ def load() -> C.CDLL:
     lib.h3a_static_scratch_capacity.restype = C.c_int32
     lib.h3a_memcpy2d_async.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int32, C.c_void_p]
     lib.h3a_memcpy2d_async.restype = C.c_int32
+    lib.h3a_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
+    lib.h3a_selftest_wait_timeout.restype = C.c_int32
     _lib = lib
     return lib
 

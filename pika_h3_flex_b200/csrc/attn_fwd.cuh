@@ -144,6 +144,21 @@ __device__ __forceinline__ bool bounded_wait(const WaitCtx& c, uint32_t bar, uin
   return true;
 }
 
+// Diagnostic: one warp waits, with the same bounded wait the attention kernel uses, on an mbarrier that nothing
+// ever arrives on.  The wait must run out, record kWaitSelfTest in the status word and return.
+constexpr int kWaitSelfTest = 9;
+__global__ void wait_selftest_kernel(int* status, long long limit_ns) {
+  __shared__ AttnBars bars;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bars.q_full), 1);
+    bars.abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  WaitCtx wc{&bars, status, limit_ns};
+  bounded_wait(wc, smem_u32(&bars.q_full), 0, kWaitSelfTest);
+}
+
 // Merge the sorted key-tile lists of query tiles 2p and 2p+1 into one list with stream flags.
 __global__ void build_pair_plan_kernel(const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ col_idx,
                                        int nqb, int n_qpairs, int32_t* __restrict__ plan, int32_t* __restrict__ plan_cnt) {

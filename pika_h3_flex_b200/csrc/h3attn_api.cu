@@ -321,6 +321,14 @@ int32_t h3a_memcpy2d_async(void* dst, size_t dst_pitch, const void* src, size_t 
   return e == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
 }
 
+int32_t h3a_selftest_wait_timeout(int32_t* status_word, int64_t wait_limit_ns, void* stream) {
+  if (!status_word || wait_limit_ns <= 0 || wait_limit_ns > 1000000000ll) return H3A_ERR_ARG;
+  int32_t rc = check_arch();
+  if (rc != H3A_OK) return rc;
+  h3a::wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status_word, wait_limit_ns);
+  return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
+}
+
 int32_t h3a_static_scratch_capacity(size_t* plan_entries) {
   if (!plan_entries) return H3A_ERR_ARG;
   *plan_entries = kStaticScratchInts;

@@ -374,3 +374,52 @@ def test_joint_path_bound_from_norm_weights(h):
     for lb in (None, 0.0):  # derived bound / running maximum
         out = h.joint_attention(dev(q), dev(k), dev(v), tab, q_weight=dev(qw), k_weight=dev(kw), logit_bound=lb)
         check(out, ref)
+
+
+# ------------------------------------------------------------------------------------------ config 4: cross-attention
+def test_config4_cross_attention_shape(h):
+    """49,384 joint tokens attend to 512 text tokens (config 4), 4 of the 40 heads, QK-RMSNorm without rotation."""
+    Lq, Lk, H = 49384, 512, 4
+    g = torch.Generator(device="cuda").manual_seed(1004)
+    q = torch.randn(Lq, H, 128, device="cuda", generator=g).bfloat16()
+    k = torch.randn(Lk, H, 128, device="cuda", generator=g).bfloat16()
+    v = torch.randn(Lk, H, 128, device="cuda", generator=g).bfloat16()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = h.joint_attention(q, k, v, None, status_word=status)
+    assert h.read_status(status) == 0
+    rows = torch.cat([torch.arange(0, Lq, 613), torch.tensor([Lq - 1, Lq - 104, Lq - 105])])
+    qn, kn = O.rms_norm(q[rows].float().cpu()), O.rms_norm(k.float().cpu())
+    check(out[rows], O.attention(qn, kn, v.float().cpu()))
+    o1 = h.joint_attention(q, k, torch.ones_like(v), None)
+    assert float((o1.float() - 1).abs().max()) <= 8e-3
+
+
+# ------------------------------------------------------------------------------------------ bounded waits
+def test_wait_that_nothing_signals_runs_out_and_is_reported(h):
+    """The bounded wait of the attention kernels, on a barrier nothing ever signals: it must give up after the
+    limit, report through the status word (code 9) and leave the context usable - no trap, no hang."""
+    import time
+
+    lib = h._lib.load()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    t0 = time.perf_counter()
+    assert lib.h3a_selftest_wait_timeout(status.data_ptr(), 20_000_000, stream) == 0  # 20 ms
+    raw = h.read_status(status)
+    dt = time.perf_counter() - t0
+    assert (raw & 0xFF) == 9, hex(raw)
+    assert 0.015 < dt < 5.0, dt
+    assert lib.h3a_read_device_status(status.data_ptr(), stream, None) == h._lib.H3A_ERR_TIMEOUT
+    assert lib.h3a_selftest_wait_timeout(status.data_ptr(), 0, stream) == h._lib.H3A_ERR_ARG
+    # the context is still usable and a normal call reports no timeout
+    q, k, v = (dev(x) for x in bf16_inputs(512, 2, 124))
+    status.zero_()
+    out = h.attn_fwd(q, k, v, status_word=status)
+    assert h.read_status(status) == 0
+    check(out, O.attention(q.float().cpu(), k.float().cpu(), v.float().cpu()))
+    # a status word that is already non-zero makes a launch return at once without touching the output
+    status.fill_(5)
+    canary = torch.full_like(out, 3.0)
+    h.attn_fwd(q, k, v, out=canary, status_word=status)
+    torch.cuda.synchronize()
+    assert float((canary.float() - 3).abs().max()) == 0.0
