@@ -95,6 +95,10 @@ typedef struct h3a_attn_params {
                              the same softmax (any reference is exact), without the max pass and without rescaling.
                              A bound that is too small only costs range, not correctness, up to a factor 2^40.
                              0 = unknown: running maximum. */
+  int32_t sparse_heavy_pairs; /* BLOCK_SPARSE scheduling hint: the first this-many pairs of query tiles (256 rows
+                             each) list far more key tiles than the rest (the dense audio rows of the joint
+                             sequence); their CTAs of all heads are started first.  0 = no hint.  Never affects
+                             results. */
 } h3a_attn_params;
 
 /*

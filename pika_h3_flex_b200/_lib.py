@@ -49,7 +49,7 @@ class AttnParams(C.Structure):
         ("q_scale", C.c_void_p), ("k_scale", C.c_void_p),
         ("row_ptr", C.c_void_p), ("col_idx", C.c_void_p), ("nnz", C.c_int32),
         ("lse", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("status_word", C.c_void_p), ("wait_limit_ns", C.c_int64), ("logit_bound", C.c_float),
+        ("status_word", C.c_void_p), ("wait_limit_ns", C.c_int64), ("logit_bound", C.c_float), ("sparse_heavy_pairs", C.c_int32),
     ]
 
 

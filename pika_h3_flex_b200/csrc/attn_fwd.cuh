@@ -99,6 +99,7 @@ struct AttnArgs {
   int* status;             // device status word or null
   long long wait_ns;
   float fixed_m;           // fixed softmax reference in log2 units (kFixed kernels)
+  int heavy_pairs;         // sparse: leading query-tile pairs whose CTAs (of every head) are scheduled first
 };
 
 // status word layout: bits [0,8) code, bits [8,32) blockIdx.x (truncated)
@@ -200,8 +201,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr int kIssuerWarp = LY::kSoftmaxWarps + 1;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int head = blockIdx.x / args.n_qpairs;
-  const int pair = blockIdx.x % args.n_qpairs;
+  // CTA -> (head, pair): head-major, so that the CTAs running at the same time share one head's K/V in L2.
+  // Block-sparse: the few pairs with long key lists (dense audio rows) of ALL heads come first, otherwise the
+  // ones of the last heads would start late and run on alone at the end.
+  int head, pair;
+  if (kSparse && args.heavy_pairs > 0) {
+    const int n_heavy_ctas = args.heavy_pairs * args.H;
+    if (static_cast<int>(blockIdx.x) < n_heavy_ctas) {
+      head = blockIdx.x / args.heavy_pairs;
+      pair = blockIdx.x % args.heavy_pairs;
+    } else {
+      const int r = blockIdx.x - n_heavy_ctas, n_light = args.n_qpairs - args.heavy_pairs;
+      head = r / n_light;
+      pair = args.heavy_pairs + r % n_light;
+    }
+  } else {
+    head = blockIdx.x / args.n_qpairs;
+    pair = blockIdx.x % args.n_qpairs;
+  }
   const int q0 = pair * 2 * kTile;
 
   constexpr uint32_t kQBytes = kFp8 ? kHalfBytes : kQTileBytes;  // bytes per Q tile
@@ -483,16 +500,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_arrive(smem_u32(&bars->p_full[t][hf]));
       ++j;
     }
-    // ---- epilogue: the two warpgroups of a stream add their row sums through shared memory (the stream's Q
-    //      tile is free once its last MMA has completed) and each stores 64 of the 128 output columns
+    // ---- epilogue: the two warpgroups of a stream add their row sums through shared memory and each stores 64
+    //      of the 128 output columns.  The exchange buffer is the stream's Q tile, which is free only when EVERY
+    //      MMA of the stream has completed.  A warpgroup may be up to a tile ahead of its partner, so it must
+    //      not judge that by the partner's barrier (a parity wait two phases behind passes at once): each waits
+    //      for its OWN last P V (never more than one phase away), then a named barrier joins the two.
     bool have = ok && j > 0;
     if (have) {
-      have = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->o_full[t][1]), (j - 1) & 1, kWaitOFull));
+      have = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->o_full[t][hf]), (j - 1) & 1, kWaitOFull));
       if (have) tc_fence_after_sync();
     }
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");  // every thread of both warpgroups, always
     float* lbuf = reinterpret_cast<float*>(smem + t * kQTileBytes);
     lbuf[hf * 128 + row] = l_sum;
-    asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");  // every thread of both warpgroups, always
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");
+    if (have) tc_fence_after_sync();
     const bool row_valid = q_row < args.Lq;
     __nv_bfloat16* orow = args.o + static_cast<long long>(q_row) * args.o_stride_l + static_cast<long long>(head) * args.o_stride_h + 64 * hf;
     if (have) {

@@ -200,6 +200,7 @@ int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream) {
                                                                                          a.n_qpairs, plan, plan_cnt);
     if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
     a.row_ptr = p->row_ptr; a.plan = plan; a.plan_cnt = plan_cnt;
+    a.heavy_pairs = (p->sparse_heavy_pairs > 0 && p->sparse_heavy_pairs < a.n_qpairs) ? p->sparse_heavy_pairs : 0;
     return fixed ? launch_attn<false, true, true>(mq, mk, mv, a, st) : launch_attn<false, true, false>(mq, mk, mv, a, st);
   }
   if (fp8) return fixed ? launch_attn<true, false, true>(mq, mk, mv, a, st) : launch_attn<true, false, false>(mq, mk, mv, a, st);

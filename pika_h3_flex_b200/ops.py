@@ -48,19 +48,37 @@ class BlockIndex:
     nnz: int
     n_q_tiles: int
     n_k_tiles: int
+    heavy_pairs: int = 0  # scheduling hint: leading query-tile pairs with far longer key lists than the rest
 
     @property
     def density(self) -> float:
         return self.nnz / float(self.n_q_tiles * self.n_k_tiles)
 
     def to(self, device) -> "BlockIndex":
-        return BlockIndex(self.row_ptr.to(device), self.col_idx.to(device), self.nnz, self.n_q_tiles, self.n_k_tiles)
+        return BlockIndex(self.row_ptr.to(device), self.col_idx.to(device), self.nnz, self.n_q_tiles, self.n_k_tiles,
+                          self.heavy_pairs)
 
     @staticmethod
     def from_csr(row_ptr, col_idx, n_k_tiles: int) -> "BlockIndex":
         rp = torch.as_tensor(np.asarray(row_ptr), dtype=torch.int32)
         ci = torch.as_tensor(np.asarray(col_idx), dtype=torch.int32)
-        return BlockIndex(rp, ci, int(ci.numel()), int(rp.numel() - 1), int(n_k_tiles))
+        return BlockIndex(rp, ci, int(ci.numel()), int(rp.numel() - 1), int(n_k_tiles), _leading_heavy_pairs(rp.numpy()))
+
+
+def _leading_heavy_pairs(row_ptr: np.ndarray) -> int:
+    """Number of leading pairs of query tiles whose key lists are more than 4x the median pair's (the dense
+    audio rows at the head of the joint sequence); 0 when there is no such prefix."""
+    per_row = np.diff(row_ptr.astype(np.int64))
+    if per_row.size < 4:
+        return 0
+    if per_row.size % 2:
+        per_row = np.append(per_row, 0)
+    per_pair = per_row[0::2] + per_row[1::2]
+    thresh = 4 * max(1.0, float(np.median(per_pair)))
+    n = 0
+    while n < per_pair.size and per_pair[n] > thresh:
+        n += 1
+    return n if n < per_pair.size else 0
 
 
 def build_block_index(grid: Tuple[int, int, int], n_audio: int, window: Tuple[int, int, int] = (2, 8, 8)) -> BlockIndex:
@@ -78,7 +96,8 @@ def build_block_index(grid: Tuple[int, int, int], n_audio: int, window: Tuple[in
         lib.h3a_build_block_index(*args, row_ptr.ctypes.data, col_idx.ctypes.data, C.byref(nnz)),
         "h3a_build_block_index(fill)",
     )
-    return BlockIndex(torch.from_numpy(row_ptr), torch.from_numpy(col_idx[: nnz.value].copy()), int(nnz.value), nb, nb)
+    return BlockIndex(torch.from_numpy(row_ptr), torch.from_numpy(col_idx[: nnz.value].copy()), int(nnz.value), nb, nb,
+                      _leading_heavy_pairs(row_ptr))
 
 
 def rope_table(pos: torch.Tensor, split=ROPE_SPLIT, theta: float = 10000.0) -> torch.Tensor:
@@ -207,6 +226,7 @@ def attn_fwd(
         if not block_index.row_ptr.is_cuda:
             raise ValueError("block index must be on the device (BlockIndex.to(device))")
         p.row_ptr, p.col_idx, p.nnz = block_index.row_ptr.data_ptr(), block_index.col_idx.data_ptr(), block_index.nnz
+        p.sparse_heavy_pairs = block_index.heavy_pairs
         need = C.c_size_t(0)
         check(lib.h3a_attn_workspace_bytes(C.byref(p), C.byref(need)), "h3a_attn_workspace_bytes")
         if workspace is None or workspace.numel() * workspace.element_size() < need.value:
