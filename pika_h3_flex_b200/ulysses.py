@@ -15,7 +15,7 @@ memory through the collective before a kernel reads it.
 """
 from __future__ import annotations
 
-from typing import Callable, List, Optional
+from typing import Callable, List, Optional, Sequence
 
 import torch
 import torch.distributed as dist
@@ -51,30 +51,41 @@ def _exchange(send_blocks: List[Optional[torch.Tensor]], recv_blocks: List[Optio
     return reqs
 
 
-def seq_to_head(x_hm: torch.Tensor, group=None, async_op: bool = False):
+def seq_to_head(x_hm: torch.Tensor, group=None, async_op: bool = False, out: Optional[torch.Tensor] = None,
+                slots: Optional[Sequence[int]] = None):
     """``x_hm [Hp, Ls, C]`` head-major local shard (all padded heads, local tokens) ->
-    ``[Hp/P, P*Ls, C]`` (local heads, every token).  Returns ``(out, requests)``."""
+    ``[Hp/P, P*Ls, C]`` (local heads, every token).  ``slots`` restricts the exchange to some of the ``Hp/P``
+    local head slots (the rest of ``out`` is left alone).  Returns ``(out, requests)``."""
     world = dist.get_world_size(group)
     Hp, Ls, Cc = x_hm.shape
     if Hp % world:
         raise ValueError(f"heads {Hp} not a multiple of world size {world}; pad first")
     hp = Hp // world
-    out = torch.empty(hp, world * Ls, Cc, dtype=x_hm.dtype, device=x_hm.device)
-    send = [[x_hm[p * hp + j] for j in range(hp)] for p in range(world)]
-    recv = [[out[j, p * Ls : (p + 1) * Ls] for j in range(hp)] for p in range(world)]
+    if out is None:
+        out = torch.empty(hp, world * Ls, Cc, dtype=x_hm.dtype, device=x_hm.device)
+    slots = range(hp) if slots is None else slots
+    send = [[x_hm[p * hp + j] for j in slots] for p in range(world)]
+    recv = [[out[j, p * Ls : (p + 1) * Ls] for j in slots] for p in range(world)]
     return out, _exchange(send, recv, group, async_op)
 
 
-def head_to_seq(o_hm: torch.Tensor, group=None, async_op: bool = False):
-    """Inverse of :func:`seq_to_head`: ``o_hm [Hp/P, P*Ls, C]`` -> ``[Hp, Ls, C]``."""
+def head_to_seq(o_hm: torch.Tensor, group=None, async_op: bool = False, out: Optional[torch.Tensor] = None,
+                slots: Optional[Sequence[int]] = None, hp: Optional[int] = None):
+    """Inverse of :func:`seq_to_head`: ``o_hm [n, P*Ls, C]`` (the local head slots ``slots``, ``n = len(slots)``,
+    of ``hp`` in total) -> rows ``p*hp + slot`` of ``out [hp*P, Ls, C]``."""
     world = dist.get_world_size(group)
-    hp, L, Cc = o_hm.shape
+    n, L, Cc = o_hm.shape
     if L % world:
         raise ValueError("sequence length not a multiple of world size")
     Ls = L // world
-    out = torch.empty(hp * world, Ls, Cc, dtype=o_hm.dtype, device=o_hm.device)
-    send = [[o_hm[j, p * Ls : (p + 1) * Ls] for j in range(hp)] for p in range(world)]
-    recv = [[out[p * hp + j] for j in range(hp)] for p in range(world)]
+    hp = n if hp is None else hp
+    slots = list(range(n)) if slots is None else list(slots)
+    if len(slots) != n:
+        raise ValueError("o_hm must hold exactly the listed head slots")
+    if out is None:
+        out = torch.empty(hp * world, Ls, Cc, dtype=o_hm.dtype, device=o_hm.device)
+    send = [[o_hm[i, p * Ls : (p + 1) * Ls] for i in range(n)] for p in range(world)]
+    recv = [[out[p * hp + j] for j in slots] for p in range(world)]
     return out, _exchange(send, recv, group, async_op)
 
 
@@ -103,8 +114,9 @@ class UlyssesAttention:
 
     def __init__(self, group=None, mode: int = _lib.MODE_DENSE_BF16, block_index: Optional[ops.BlockIndex] = None,
                  prep_fn: Optional[Callable] = None, attn_fn: Optional[Callable] = None,
-                 to_head_major: Optional[Callable] = None):
+                 to_head_major: Optional[Callable] = None, head_groups: int = 2):
         self.group = group
+        self.head_groups = head_groups
         self.mode = mode
         self.block_index = block_index
         self.prep_fn = prep_fn or self._cuda_prep
@@ -122,6 +134,22 @@ class UlyssesAttention:
         bound = ops.normed_logit_bound(fp8=(mode == _lib.MODE_FP8_QK))  # operands come from the unit-weight prep
         return ops.attn_fwd(q, k, v, mode, q_scale, k_scale, block_index, out=out, logit_bound=bound)
 
+    def _head_slot_groups(self, hp: int, L: int, like: torch.Tensor):
+        """Split the ``hp`` local head slots into at most two groups.  On a GPU the cut is placed so that the two
+        attention launches together need no more waves of CTAs (one CTA per 256 query rows and head, one CTA
+        per SM at a time) than a single launch would; if no cut achieves that, one group is used."""
+        if self.head_groups < 2 or hp < 2:
+            return [range(hp)]
+        if not like.is_cuda:
+            return [range(0, hp // 2), range(hp // 2, hp)]
+        sms = torch.cuda.get_device_properties(like.device).multi_processor_count
+        nq = (L + 255) // 256
+        waves = lambda n: -(-n * nq // sms)
+        best = min(range(1, hp), key=lambda c: (waves(c) + waves(hp - c), abs(c - hp // 2)))
+        if waves(best) + waves(hp - best) > waves(hp):
+            return [range(hp)]
+        return [range(0, best), range(best, hp)]
+
     def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rope: Optional[torch.Tensor]) -> torch.Tensor:
         world = dist.get_world_size(self.group)
         Ls, H, _ = q.shape
@@ -129,21 +157,38 @@ class UlyssesAttention:
         if fp8 and Ls % ops.TILE:
             raise ValueError("FP8 mode under Ulysses needs the local sequence length to be a multiple of 128")
         Hp = padded_heads(H, world)
+        hp = Hp // world
         # token-local work first: the wire then carries final operands
         qp, kp, qs, ks = self.prep_fn(q, k, rope, rope, fp8)
         # prepared tensors are logical [Ls, H, C] views of head-major storage
         q_hm = _pad_heads_hm(qp.permute(1, 0, 2).contiguous(), Hp)
         k_hm = _pad_heads_hm(kp.permute(1, 0, 2).contiguous(), Hp)
-        qh, rq = seq_to_head(q_hm, self.group, async_op=True)
-        kh, rk = seq_to_head(k_hm, self.group, async_op=True)
-        v_hm = _pad_heads_hm(self.to_head_major(v), Hp)  # overlaps the Q/K exchanges
-        vh, rv = seq_to_head(v_hm, self.group, async_op=True)
+        v_hm = _pad_heads_hm(self.to_head_major(v), Hp)
         qsh = ksh = None
         if fp8:
             qsh = scales_seq_to_head(_pad_heads_hm(qs, Hp), self.group)
             ksh = scales_seq_to_head(_pad_heads_hm(ks, Hp), self.group)
-        for r in rq + rk + rv:
+        # The local head slots are handled in groups: while one group is in attention the next group's operands
+        # are arriving and the previous group's output is leaving.
+        groups = self._head_slot_groups(hp, world * Ls, q)
+        qh = kh = vh = None
+        inbound = []
+        for sl in groups:
+            qh, r1 = seq_to_head(q_hm, self.group, True, qh, sl)
+            kh, r2 = seq_to_head(k_hm, self.group, True, kh, sl)
+            vh, r3 = seq_to_head(v_hm, self.group, True, vh, sl)
+            inbound.append(r1 + r2 + r3)
+        o_hm = None
+        outbound = []
+        for sl, reqs in zip(groups, inbound):
+            for r in reqs:
+                r.wait()
+            j0, j1 = sl.start, sl.stop
+            oh = self.attn_fn(qh[j0:j1].permute(1, 0, 2), kh[j0:j1].permute(1, 0, 2), vh[j0:j1].permute(1, 0, 2), self.mode,
+                              None if qsh is None else qsh[j0:j1].contiguous(), None if ksh is None else ksh[j0:j1].contiguous(),
+                              self.block_index)
+            o_hm, r = head_to_seq(oh.permute(1, 0, 2).contiguous(), self.group, True, o_hm, sl, hp)
+            outbound += r
+        for r in outbound:
             r.wait()
-        oh = self.attn_fn(qh.permute(1, 0, 2), kh.permute(1, 0, 2), vh.permute(1, 0, 2), self.mode, qsh, ksh, self.block_index)
-        o_hm, _ = head_to_seq(oh.permute(1, 0, 2).contiguous(), self.group)
         return o_hm[:H].permute(1, 0, 2)
