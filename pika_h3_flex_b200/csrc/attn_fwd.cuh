@@ -145,6 +145,23 @@ __device__ __forceinline__ bool bounded_wait(const WaitCtx& c, uint32_t bar, uin
   return true;
 }
 
+// Whole-warp wait.  Default: every lane polls and the verdicts are combined, which keeps control flow uniform.
+// H3A_ONE_LANE_WAIT=1 lets lane 0 poll and broadcasts its verdict; measured 15 % slower (the divergent branch
+// costs more than 32 lanes polling one barrier word).
+#ifndef H3A_ONE_LANE_WAIT
+#define H3A_ONE_LANE_WAIT 0
+#endif
+__device__ __forceinline__ bool warp_wait(const WaitCtx& c, uint32_t bar, uint32_t parity, int code) {
+#if H3A_ONE_LANE_WAIT
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = bounded_wait(c, bar, parity, code) ? 1 : 0;
+  __syncwarp();
+  return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
+#else
+  return __all_sync(0xFFFFFFFFu, bounded_wait(c, bar, parity, code));
+#endif
+}
+
 // Diagnostic: one warp waits, with the same bounded wait the attention kernel uses, on an mbarrier that nothing
 // ever arrives on.  The wait must run out, record kWaitSelfTest in the status word and return.
 constexpr int kWaitSelfTest = 9;
@@ -300,7 +317,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int kv = 0; kv < 2; ++kv) {  // K tile, then V tile
         const int s = cnt % kStages;
         const uint32_t ph = (cnt / kStages) & 1;
-        ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->kv_empty[s]), ph ^ 1u, kWaitKvEmpty));
+        ok = warp_wait(wc, smem_u32(&bars->kv_empty[s]), ph ^ 1u, kWaitKvEmpty);
         if (!ok) break;
         const uint32_t fb = smem_u32(&bars->kv_full[s]);
         const uint32_t dst = ring_smem + s * kStageBytes;
@@ -330,7 +347,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       constexpr uint32_t idesc_s = kFp8 ? umma_idesc(UMMA_FMT_E4M3, UMMA_FMT_E4M3, 0, 0, 128, kSN)
                                         : umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 0, 128, kSN);
       constexpr uint32_t idesc_pv = umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 1, 128, 128);
-      bool ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->q_full), 0, kWaitQFull));
+      bool ok = warp_wait(wc, smem_u32(&bars->q_full), 0, kWaitQFull);
       tc_fence_after_sync();
       uint32_t p_cnt[2] = {0, 0};
       uint32_t pv_cnt = 0;
@@ -373,7 +390,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
       if (ok) {  // prologue: both S halves of entry 0
         const int f0 = entry_at(0) & 3;
-        ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->kv_full[0]), 0, kWaitKvFullK));
+        ok = warp_wait(wc, smem_u32(&bars->kv_full[0]), 0, kWaitKvFullK);
         if (ok) {
           tc_fence_after_sync();
           if ((f0 >> t) & 1) {
@@ -390,14 +407,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int cv = 2 * it + 1, ck = 2 * it + 2;
         const int sv = cv % kStages, sk = ck % kStages;
         const bool mine = (f >> t) & 1, mine_next = (fn >> t) & 1;
-        ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->kv_full[sv]), (cv / kStages) & 1, kWaitKvFullV));
+        ok = warp_wait(wc, smem_u32(&bars->kv_full[sv]), (cv / kStages) & 1, kWaitKvFullV);
         if (!ok) break;
         bool k_ready = false;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           if (ok && mine) {
             H3A_STAMP(2 + t, 2 * it + hf, 0);
-            ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->p_full[t][hf]), p_cnt[hf] & 1, kWaitPFull));
+            ok = warp_wait(wc, smem_u32(&bars->p_full[t][hf]), p_cnt[hf] & 1, kWaitPFull);
             if (ok) {
               ++p_cnt[hf];
               tc_fence_after_sync();
@@ -407,7 +424,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
           }
           if (ok && has_next && !k_ready) {
-            ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->kv_full[sk]), (ck / kStages) & 1, kWaitKvFullK));
+            ok = warp_wait(wc, smem_u32(&bars->kv_full[sk]), (ck / kStages) & 1, kWaitKvFullK);
             if (ok) {
               k_ready = true;
               tc_fence_after_sync();
@@ -456,8 +473,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int tile = e >> 2;
       float c = args.scale_log2;
       if constexpr (kFp8) c *= qs * args.k_scale[head * args.nkb + tile];
+      if (row == 0 && t == 0) H3A_STAMP(hf, j, 0);
       // with kFullS one N=128 MMA group fills both halves and signals s_full[t][0] for both warpgroups
-      ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->s_full[t][kFullS ? 0 : hf]), j & 1, kWaitSFull));
+      ok = warp_wait(wc, smem_u32(&bars->s_full[t][kFullS ? 0 : hf]), j & 1, kWaitSFull);
       if (!ok) break;
       tc_fence_after_sync();
       tmem_ld32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
@@ -465,6 +483,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_wait_ld();
       reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      if (row == 0 && t == 0) H3A_STAMP(hf, j, 2);
       if (tile == last_tile && tail < kTile) {
         const int valid = tail - hf * 64;
 #pragma unroll
@@ -494,10 +513,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       unpack2(acc0, a0, a1);
       unpack2(acc1, a2, a3);
       l_sum += (a0 + a1) + (a2 + a3);
+      if (row == 0 && t == 0) H3A_STAMP(hf, j, 4);
       tmem_st32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&bars->p_full[t][hf]));
+      if (row == 0 && t == 0) H3A_STAMP(hf, j, 5);
       ++j;
     }
     // ---- epilogue: the two warpgroups of a stream add their row sums through shared memory and each stores 64
@@ -507,7 +528,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     //      for its OWN last P V (never more than one phase away), then a named barrier joins the two.
     bool have = ok && j > 0;
     if (have) {
-      have = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->o_full[t][hf]), (j - 1) & 1, kWaitOFull));
+      have = warp_wait(wc, smem_u32(&bars->o_full[t][hf]), (j - 1) & 1, kWaitOFull);
       if (have) tc_fence_after_sync();
     }
     asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");  // every thread of both warpgroups, always
@@ -580,7 +601,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     };
     // wait for S[t][hf] of the stream's tile number `jt`, then start its load
     auto fetch_s = [&](uint32_t (&r)[64], int hf, uint32_t jt) -> bool {
-      const bool got = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->s_full[t][hf]), jt & 1, kWaitSFull));
+      const bool got = warp_wait(wc, smem_u32(&bars->s_full[t][hf]), jt & 1, kWaitSFull);
       if (got) load_s(r, hf);
       return got;
     };
@@ -627,7 +648,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // O_t must be quiescent: the previous P V of this stream has to be complete (MMAs complete
           // in issue order, so it is the only one that can still be running).  Each (stream, half)
           // barrier advances one phase per key tile, so a parity wait is never two phases behind.
-          if (!__all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->o_full[t][hf ^ 1]), (hf ? j : j - 1) & 1, kWaitOFull)))
+          if (!warp_wait(wc, smem_u32(&bars->o_full[t][hf ^ 1]), (hf ? j : j - 1) & 1, kWaitOFull))
             return false;
           tc_fence_after_sync();
 #pragma unroll
@@ -739,7 +760,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const bool row_valid = q_row < args.Lq;
     __nv_bfloat16* orow = args.o + static_cast<long long>(q_row) * args.o_stride_l + static_cast<long long>(head) * args.o_stride_h;
     if (ok && j > 0) {
-      ok = __all_sync(0xFFFFFFFFu, bounded_wait(wc, smem_u32(&bars->o_full[t][1]), (j - 1) & 1, kWaitOFull));
+      ok = warp_wait(wc, smem_u32(&bars->o_full[t][1]), (j - 1) & 1, kWaitOFull);
       if (ok) {
         tc_fence_after_sync();
         const float inv = 1.0f / l_sum;
