@@ -79,19 +79,25 @@ size_t sparse_workspace_bytes(const h3a_attn_params* p) {
   return (static_cast<size_t>(p->nnz) + n_qpairs) * sizeof(int32_t);
 }
 
+constexpr int kMaxDevices = 64;
+
 template <bool kFp8, bool kSparse, bool kFixed = false>
 int32_t launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a, cudaStream_t st) {
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(h3a::attn_fwd_kernel<kFp8, kSparse, kFixed>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    h3a::kAttnSmemBytes);
+  // function attributes belong to a device's context: set them once per device this process launches on
+  static std::once_flag once[kMaxDevices];
+  static cudaError_t attr_err[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return H3A_ERR_LAUNCH;
+  std::call_once(once[dev], [dev] {
+    cudaError_t e = cudaFuncSetAttribute(h3a::attn_fwd_kernel<kFp8, kSparse, kFixed>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         h3a::kAttnSmemBytes);
     // the in-kernel register re-allocation would block forever if the launch allocation were smaller
     cudaFuncAttributes fa;
-    if (attr_err == cudaSuccess) attr_err = cudaFuncGetAttributes(&fa, h3a::attn_fwd_kernel<kFp8, kSparse, kFixed>);
-    if (attr_err == cudaSuccess && fa.numRegs < h3a::AttnLayout<kFixed>::kLaunchRegs) attr_err = cudaErrorLaunchOutOfResources;
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, h3a::attn_fwd_kernel<kFp8, kSparse, kFixed>);
+    if (e == cudaSuccess && fa.numRegs < h3a::AttnLayout<kFixed>::kLaunchRegs) e = cudaErrorLaunchOutOfResources;
+    attr_err[dev] = e;
   });
-  if (attr_err != cudaSuccess) return H3A_ERR_LAUNCH;
+  if (attr_err[dev] != cudaSuccess) return H3A_ERR_LAUNCH;
   const unsigned grid = static_cast<unsigned>(a.n_qpairs) * static_cast<unsigned>(a.H);
   h3a::attn_fwd_kernel<kFp8, kSparse, kFixed><<<grid, h3a::AttnLayout<kFixed>::kThreads, h3a::kAttnSmemBytes, st>>>(mq, mk, mv, a);
   return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
@@ -104,7 +110,6 @@ int32_t launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
 constexpr size_t kStaticScratchInts = 262144;
 static __device__ __align__(256) int32_t g_static_scratch[kStaticScratchInts];
 
-constexpr int kMaxDevices = 64;
 std::mutex g_scratch_mutex;
 int32_t* g_scratch_addr[kMaxDevices] = {};  // device address of g_static_scratch, per device ordinal
 
