@@ -120,9 +120,10 @@ __device__ unsigned long long* g_trace = nullptr;
 #endif
 
 struct WaitCtx {
-  AttnBars* bars;
+  volatile uint32_t* abort_flag;  // this CTA's flag
   int* status;
   long long limit_ns;
+  uint32_t peer_abort;            // shared::cluster address of the peer CTA's flag (CTA pairs), else 0
 };
 
 __device__ __forceinline__ bool bounded_wait(const WaitCtx& c, uint32_t bar, uint32_t parity, int code) {
@@ -131,12 +132,13 @@ __device__ __forceinline__ bool bounded_wait(const WaitCtx& c, uint32_t bar, uin
   uint64_t t0 = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++polls & 63u) == 0u) {
-      if (c.bars->abort_flag) return false;
+      if (*c.abort_flag) return false;
       uint64_t now = global_timer_ns();
       if (t0 == 0) {
         t0 = now;
       } else if (static_cast<long long>(now - t0) > c.limit_ns) {
-        c.bars->abort_flag = 1u;
+        *c.abort_flag = 1u;
+        if (c.peer_abort) st_shared_cluster_u32(c.peer_abort, 1u);  // the peer's waits give up at their next check
         if (c.status) atomicCAS(c.status, 0, code | (static_cast<int>(blockIdx.x & 0x7FFFFF) << 8));
         return false;
       }
@@ -173,7 +175,7 @@ __global__ void wait_selftest_kernel(int* status, long long limit_ns) {
     fence_mbar_init();
   }
   __syncthreads();
-  WaitCtx wc{&bars, status, limit_ns};
+  WaitCtx wc{&bars.abort_flag, status, limit_ns, 0u};
   bounded_wait(wc, smem_u32(&bars.q_full), 0, kWaitSelfTest);
 }
 
@@ -292,7 +294,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem = bars->tmem_base;
 
-  WaitCtx wc{bars, args.status, args.wait_ns};
+  WaitCtx wc{&bars->abort_flag, args.status, args.wait_ns, 0u};
 
   if (warp >= LY::kSoftmaxWarps) {
    setmaxnreg_dec<LY::kHelperRegs>();

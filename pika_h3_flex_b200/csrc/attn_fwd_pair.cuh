@@ -1,0 +1,407 @@
+// Dense forward attention on CTA PAIRS: two CTAs on neighbouring SMs (a cluster of two) run every MMA
+// together (tcgen05 cta_group::2, M = 256 = 128 query rows in each CTA), so each CTA stages only HALF of every
+// K and V tile in its shared memory and fetches half of the B operand per MMA.  The single-CTA kernel is bound by
+// shared-memory bandwidth (operand fetch plus TMA writes); the pair moves 30 % fewer bytes through each SM's
+// shared memory for the same math.
+//
+// A pair owns 512 query rows of one head: CTA r (rank in the cluster) rows [512 c + 256 r, +256) as two streams of
+// 128 rows, exactly the row layout of the single-CTA kernel.  Per CTA, as there:
+//   warp 16  producer : TMA loads of its Q tiles (once) and of ITS HALF of K_j / V_j into a ring of 16 KB stages;
+//                       the bytes of both CTAs are counted on the mbarriers of rank 0
+//   warps 17,18       : rank 0 only - one issuer per stream; S = Q_t K^T (N = 64 keys per MMA group, 32 key rows
+//                       from each CTA) and O_t += P V (P from TMEM, each CTA supplies 64 of V's 128 columns);
+//                       every commit is sent to the barrier in both CTAs
+//   warps 0-15        : softmax with the fixed reference, one warpgroup per (stream, 64-key half); P is published
+//                       with one arrive per warp on rank 0's barrier (local or through the cluster)
+// Only the fixed-reference softmax is implemented here (dense bf16 and FP8-QK); everything else runs on the
+// single-CTA kernel.
+//
+// Shared memory of a CTA:  Q tiles 2 x 32 KB | ring of 8 stages x 16 KB | barriers
+//   K stage (bf16): [dim half][64-key half][32 keys][128 B]   - the 32 keys this CTA supplies to each N = 64 group
+//   K stage (e4m3): [64-key half][32 keys][128 B]
+//   V stage       : [128 keys][64 dims]                       - this CTA's half of the output columns
+// TMEM: as in the single-CTA kernel, at the same addresses in both CTAs.
+//
+// Cluster protocol.  A cluster barrier after the mbarrier set-up (no remote arrive or TMA completion may reach
+// an uninitialised barrier) and one before TMEM is freed (no CTA leaves while its peer may still signal its
+// barriers or the pair's MMAs may still run).  Every thread reaches both on every path; all other waits are
+// bounded as in the single-CTA kernel, and a CTA that gives up also raises its peer's abort flag.
+#pragma once
+#include "attn_fwd.cuh"
+
+namespace h3a {
+
+constexpr int kPairStages = 8;
+constexpr int kPairStageBytes = 16384;
+constexpr int kPairThreads = AttnLayout<true>::kThreads;
+
+struct PairBars {
+  uint64_t kv_full[kPairStages];   // waited on in rank 0: counts the bytes of both CTAs' halves
+  uint64_t kv_empty[kPairStages];  // in both CTAs: one commit from each of rank 0's issuers
+  uint64_t q_full;                 // rank 0
+  uint64_t s_full[2][2];           // [stream][half], both CTAs
+  uint64_t p_full[2][2];           // rank 0: one arrive per softmax warp of the (stream, half) warpgroup of BOTH CTAs
+  uint64_t o_full[2][2];           // both CTAs
+  uint64_t drain[2];               // rank 0: last commit of issuer t
+  uint32_t tmem_base;
+  volatile uint32_t abort_flag;
+  uint32_t early_exit;
+};
+static_assert(sizeof(PairBars) <= 512, "barrier block too large");
+
+constexpr int kPairSmemBytes = 2 * kQTileBytes + kPairStages * kPairStageBytes + 1024 /*align slack*/ + 512 /*barriers*/;
+static_assert(kPairSmemBytes <= 232448, "shared memory budget");
+
+enum : int { kWaitDrain = 8 };
+
+template <bool kFp8>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, const AttnArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;  // the same offset in both CTAs: MMA descriptors are shared
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const uint32_t q_smem = base;
+  const uint32_t ring_smem = base + 2 * kQTileBytes;
+  PairBars* bars = reinterpret_cast<PairBars*>(smem + 2 * kQTileBytes + kPairStages * kPairStageBytes);
+
+  using LY = AttnLayout<true>;
+  constexpr int kProducerWarp = LY::kSoftmaxWarps;
+  constexpr int kIssuerWarp = LY::kSoftmaxWarps + 1;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int n_clusters = (args.Lq + 4 * kTile - 1) / (4 * kTile);
+  const int cid = blockIdx.x >> 1;
+  const int head = cid / n_clusters;
+  const int q0 = (cid % n_clusters) * 4 * kTile + static_cast<int>(rank) * 2 * kTile;
+  const int n_it = args.n_kv_tiles;
+
+  constexpr uint32_t kQBytes = kFp8 ? kHalfBytes : kQTileBytes;  // bytes per Q tile
+  constexpr uint32_t kKHalfBytes = kFp8 ? 8192 : 16384;          // this CTA's half of a K tile
+  constexpr uint32_t kVHalfBytes = 16384;
+
+  // ---- set-up
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kPairStages; ++i) {
+      mbar_init(smem_u32(&bars->kv_full[i]), 1);
+      mbar_init(smem_u32(&bars->kv_empty[i]), 2);
+    }
+    mbar_init(smem_u32(&bars->q_full), 1);
+    for (int t = 0; t < 2; ++t) {
+      for (int hf = 0; hf < 2; ++hf) {
+        mbar_init(smem_u32(&bars->s_full[t][hf]), 1);
+        mbar_init(smem_u32(&bars->p_full[t][hf]), 8);
+        mbar_init(smem_u32(&bars->o_full[t][hf]), 1);
+      }
+      mbar_init(smem_u32(&bars->drain[t]), 1);
+    }
+    bars->abort_flag = 0;
+    bars->early_exit = (args.status != nullptr && *reinterpret_cast<volatile int*>(args.status) != 0) ? 1u : 0u;
+    fence_mbar_init();
+  }
+  if (warp == kProducerWarp && lane == 0) {
+    prefetch_tmap(&tm_q);
+    prefetch_tmap(&tm_k);
+    prefetch_tmap(&tm_v);
+  }
+  cluster_sync_all();  // barriers of both CTAs are initialised; rank 0's verdict below is visible
+  // an earlier CTA of this launch already gave up: the pair does nothing (rank 0 decides for both)
+  const bool run = ld_shared_cluster_u32(mapa_shared(smem_u32(&bars->early_exit), 0)) == 0u;
+  uint32_t tmem = 0;
+  const uint32_t bars0 = mapa_shared(smem_u32(bars), 0);         // rank 0's barrier block
+  const uint32_t bars_peer = mapa_shared(smem_u32(bars), rank ^ 1u);
+  auto at0 = [&](const void* local) { return bars0 + (smem_u32(local) - smem_u32(bars)); };
+  auto at_peer = [&](const void* local) { return bars_peer + (smem_u32(local) - smem_u32(bars)); };
+  WaitCtx wc{&bars->abort_flag, args.status, args.wait_ns, at_peer(const_cast<const uint32_t*>(&bars->abort_flag))};
+
+  if (run) {
+  if (warp == kIssuerWarp) {
+    tmem_alloc_pair(smem_u32(&bars->tmem_base), 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  tmem = bars->tmem_base;
+
+  if (warp >= LY::kSoftmaxWarps) {
+   setmaxnreg_dec<LY::kHelperRegs>();
+   if (warp == kProducerWarp) {
+    // =========================================================== producer (both CTAs)
+    const uint32_t leader = elect_one();
+    {
+      if (rank == 0) mbar_arrive_expect_tx_if(leader, smem_u32(&bars->q_full), 2 * 2 * kQBytes);  // Q tiles of both CTAs
+      const uint32_t qbar = at0(&bars->q_full);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        tma_load_3d_pair_if(leader, q_smem + t * kQTileBytes, &tm_q, qbar, 0, q0 + t * kTile, head);
+        if constexpr (!kFp8) tma_load_3d_pair_if(leader, q_smem + t * kQTileBytes + kHalfBytes, &tm_q, qbar, 64, q0 + t * kTile, head);
+      }
+    }
+    int cnt = 0;
+    bool ok = true;
+    for (int it = 0; ok && it < n_it; ++it) {
+#pragma unroll
+      for (int kv = 0; kv < 2; ++kv) {  // K half-tile, then V half-tile
+        const int s = cnt % kPairStages;
+        const uint32_t ph = (cnt / kPairStages) & 1;
+        ok = warp_wait(wc, smem_u32(&bars->kv_empty[s]), ph ^ 1u, kWaitKvEmpty);
+        if (!ok) break;
+        const uint32_t fb = at0(&bars->kv_full[s]);
+        const uint32_t dst = ring_smem + s * kPairStageBytes;
+        if (kv == 0) {
+          if (rank == 0) mbar_arrive_expect_tx_if(leader, smem_u32(&bars->kv_full[s]), 2 * kKHalfBytes);
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {  // the 32 keys this CTA supplies to the N = 64 group of half hf
+            const int key0 = it * kTile + 64 * hf + 32 * static_cast<int>(rank);
+            if constexpr (kFp8) {
+              tma_load_3d_pair_if(leader, dst + hf * 4096, &tm_k, fb, 0, key0, head);
+            } else {
+              tma_load_3d_pair_if(leader, dst + hf * 4096, &tm_k, fb, 0, key0, head);
+              tma_load_3d_pair_if(leader, dst + 8192 + hf * 4096, &tm_k, fb, 64, key0, head);
+            }
+          }
+        } else {
+          if (rank == 0) mbar_arrive_expect_tx_if(leader, smem_u32(&bars->kv_full[s]), 2 * kVHalfBytes);
+          tma_load_3d_pair_if(leader, dst, &tm_v, fb, 64 * static_cast<int>(rank), it * kTile, head);
+        }
+        ++cnt;
+      }
+    }
+    __syncwarp();
+  } else if ((warp == kIssuerWarp || warp == kIssuerWarp + 1) && rank == 0) {
+    // =========================================================== MMA issuers of the pair (rank 0), one warp per stream
+    if (n_it > 0) {
+      const int t = warp - kIssuerWarp;
+      const uint32_t leader = elect_one();
+      constexpr uint32_t idesc_s = kFp8 ? umma_idesc(UMMA_FMT_E4M3, UMMA_FMT_E4M3, 0, 0, 256, 64)
+                                        : umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 0, 256, 64);
+      constexpr uint32_t idesc_pv = umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 1, 256, 128);
+      bool ok = warp_wait(wc, smem_u32(&bars->q_full), 0, kWaitQFull);
+      tc_fence_after_sync();
+      uint32_t p_cnt[2] = {0, 0};
+      uint32_t pv_cnt = 0;
+      const uint64_t q_desc = umma_desc_sw128(q_smem + t * kQTileBytes, 16, 1024);
+      const uint64_t k_desc0 = umma_desc_sw128(ring_smem, 16, 1024);
+      const uint64_t v_desc0 = umma_desc_sw128(ring_smem, 16, 1024);
+      const uint32_t s_tmem = tmem + t * kTile;
+      const uint32_t o_tmem = tmem + 256 + t * kTile;
+      // one commit for each CTA's copy of the barrier (a single instruction that signals both was measured
+      // and is not faster)
+      auto commit_both = [&](const void* local) {
+        umma_pair_commit_if(leader, smem_u32(local));
+        umma_pair_commit_if(leader, at_peer(local));
+      };
+      // S[t][hf] = Q_t K[hf]^T for keys [64 hf, +64) of ring stage `sk`: 32 key rows from each CTA
+      auto issue_s = [&](int hf, int sk) {
+        const uint64_t kd = k_desc0 + static_cast<uint64_t>((sk * kPairStageBytes + hf * 4096) >> 4);
+        const uint32_t d = s_tmem + hf * 64;
+        if constexpr (kFp8) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_pair_e4m3_ss_if(leader, d, q_desc + (k * 32 >> 4), kd + (k * 32 >> 4), idesc_s, k > 0);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {  // dims 64..127: second box of Q (16 KB on) and of this K half (8 KB on)
+            const uint32_t offq = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
+            const uint32_t offk = ((k >> 2) * 8192 + (k & 3) * 32) >> 4;
+            umma_pair_bf16_ss_if(leader, d, q_desc + offq, kd + offk, idesc_s, k > 0);
+          }
+        }
+        commit_both(&bars->s_full[t][hf]);
+      };
+      // O_t += P[t][hf] V[hf]: A = P from each CTA's TMEM, B = this CTA's 64 columns of V, MN-major
+      auto issue_pv = [&](int hf, int sv, bool last) {
+        const uint64_t vd = v_desc0 + static_cast<uint64_t>((sv * kPairStageBytes + hf * 8192) >> 4);
+        const uint32_t a = s_tmem + hf * 64;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_pair_bf16_ts_if(leader, o_tmem, a + k * 8, vd + (k * 2048 >> 4), idesc_pv, (pv_cnt > 0 || k > 0) ? 1u : 0u);
+        ++pv_cnt;
+        if (last) commit_both(&bars->o_full[t][hf]);  // only the epilogue waits for O
+      };
+
+      if (ok) {  // prologue: both S halves of tile 0
+        ok = warp_wait(wc, smem_u32(&bars->kv_full[0]), 0, kWaitKvFullK);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_s(0, 0);
+          issue_s(1, 0);
+          commit_both(&bars->kv_empty[0]);
+        }
+      }
+      for (int it = 0; ok && it < n_it; ++it) {
+        const bool has_next = (it + 1 < n_it);
+        const int cv = 2 * it + 1, ck = 2 * it + 2;
+        const int sv = cv % kPairStages, sk = ck % kPairStages;
+        ok = warp_wait(wc, smem_u32(&bars->kv_full[sv]), (cv / kPairStages) & 1, kWaitKvFullV);
+        if (!ok) break;
+        bool k_ready = false;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          H3A_STAMP(2 + t, 2 * it + hf, 0);
+          ok = warp_wait(wc, smem_u32(&bars->p_full[t][hf]), p_cnt[hf] & 1, kWaitPFull);
+          if (!ok) break;
+          ++p_cnt[hf];
+          tc_fence_after_sync();
+          H3A_STAMP(2 + t, 2 * it + hf, 1);
+          issue_pv(hf, sv, !has_next);
+          H3A_STAMP(2 + t, 2 * it + hf, 2);
+          if (has_next && !k_ready) {
+            ok = warp_wait(wc, smem_u32(&bars->kv_full[sk]), (ck / kPairStages) & 1, kWaitKvFullK);
+            if (!ok) break;
+            k_ready = true;
+            tc_fence_after_sync();
+          }
+          if (has_next) issue_s(hf, sk);
+          H3A_STAMP(2 + t, 2 * it + hf, 3);
+        }
+        if (!ok) break;
+        commit_both(&bars->kv_empty[sv]);
+        if (has_next) commit_both(&bars->kv_empty[sk]);
+      }
+      // the commits to the peer's barriers were issued before this one and complete in order: once it has
+      // arrived nothing of this issuer is still on its way to the peer CTA
+      if (ok) {
+        umma_pair_commit_if(leader, smem_u32(&bars->drain[t]));
+        warp_wait(wc, smem_u32(&bars->drain[t]), 0, kWaitDrain);
+      }
+    }
+    __syncwarp();
+   }
+  } else {
+    setmaxnreg_inc<LY::kSoftmaxRegs>();
+    // =========================================================== softmax, fixed reference: one warpgroup per (stream, half)
+    const int wg = warp >> 2;
+    const int t = wg & 1;
+    const int hf = wg >> 1;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t sb = tmem + lane_base + t * kTile + hf * 64;
+    const uint32_t o_addr = tmem + lane_base + 256 + t * kTile + hf * 64;
+    const int q_row = q0 + t * kTile + row;
+    const int last_tile = args.n_kv_tiles - 1;
+    const int tail = args.Lk - last_tile * kTile;
+    const uint32_t p_bar = at0(&bars->p_full[t][hf]);
+    float qs = 1.0f;
+    if constexpr (kFp8) {
+      const int qb = min(q0 / kTile + t, args.nqb - 1);
+      qs = args.q_scale[head * args.nqb + qb];
+    }
+    const float m_ref = args.fixed_m;
+    float l_sum = 0.0f;
+    uint32_t j = 0;
+    bool ok = true;
+    uint32_t s[64];
+    for (int it = 0; ok && it < n_it; ++it) {
+      float c = args.scale_log2;
+      if constexpr (kFp8) c *= qs * args.k_scale[head * args.nkb + it];
+      if (row == 0 && t == 0) H3A_STAMP(hf, j, 0);
+      ok = warp_wait(wc, smem_u32(&bars->s_full[t][hf]), j & 1, kWaitSFull);
+      if (!ok) break;
+      tc_fence_after_sync();
+      tmem_ld32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_ld32(sb + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      tmem_wait_ld();
+      reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      if (row == 0 && t == 0) H3A_STAMP(hf, j, 2);
+      if (it == last_tile && tail < kTile) {
+        const int valid = tail - hf * 64;
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (i >= valid) s[i] = 0xFF800000u;  // -inf
+      }
+      uint64_t acc0 = 0, acc1 = 0;
+      const uint64_t c2 = pack2(c, c), nm2 = pack2(-m_ref, -m_ref);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const uint64_t x = fma2(pack2u(s[2 * i], s[2 * i + 1]), c2, nm2);
+        uint64_t pp;
+        if ((i & 3) < (kFp8 ? kPolyPairsFp8 : kPolyPairsBf16)) {
+          pp = exp2_poly2(x);
+        } else {
+          float x0, x1;
+          unpack2(x, x0, x1);
+          pp = pack2(ex2_approx(x0), ex2_approx(x1));
+        }
+        if (i & 1) acc1 = add2(acc1, pp);
+        else acc0 = add2(acc0, pp);
+        float p0, p1;
+        unpack2(pp, p0, p1);
+        s[i] = pack_bf16x2(p0, p1);
+      }
+      float a0, a1, a2, a3;
+      unpack2(acc0, a0, a1);
+      unpack2(acc1, a2, a3);
+      l_sum += (a0 + a1) + (a2 + a3);
+      if (row == 0 && t == 0) H3A_STAMP(hf, j, 4);
+      tmem_st32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(smem_u32(&bars->p_full[t][hf]));
+        else mbar_arrive_cluster(p_bar);
+      }
+      if (row == 0 && t == 0) H3A_STAMP(hf, j, 5);
+      ++j;
+    }
+    // ---- epilogue: as in the single-CTA kernel (own last P V, named barrier, row sums through the Q tile)
+    bool have = ok && j > 0;
+    if (have) {
+      have = warp_wait(wc, smem_u32(&bars->o_full[t][hf]), 0, kWaitOFull);  // its only phase: the last tile's P V
+      if (have) tc_fence_after_sync();
+    }
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");
+    float* lbuf = reinterpret_cast<float*>(smem + t * kQTileBytes);
+    lbuf[hf * 128 + row] = l_sum;
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");
+    if (have) tc_fence_after_sync();
+    const bool row_valid = q_row < args.Lq;
+    __nv_bfloat16* orow = args.o + static_cast<long long>(q_row) * args.o_stride_l + static_cast<long long>(head) * args.o_stride_h + 64 * hf;
+    if (have) {
+      const float l_tot = l_sum + lbuf[(hf ^ 1) * 128 + row];
+      const float inv = 1.0f / l_tot;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        uint32_t o[32];
+        tmem_ld32(o_addr + 32 * i, o);
+        tmem_wait_ld();
+        if (row_valid) {
+#pragma unroll
+          for (int x = 0; x < 32; x += 8) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[x]) * inv, __uint_as_float(o[x + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(o[x + 2]) * inv, __uint_as_float(o[x + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(o[x + 4]) * inv, __uint_as_float(o[x + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(o[x + 6]) * inv, __uint_as_float(o[x + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + 32 * i + x) = w;
+          }
+        }
+      }
+      if (row_valid && args.lse && hf == 0)
+        args.lse[static_cast<long long>(head) * args.Lq + q_row] = (m_ref + log2f(l_tot)) * 0.6931471805599453f;
+    }
+  }
+  }  // run
+
+  // ---- tear-down
+  tc_fence_before_sync();
+  __syncthreads();
+  if (bars->abort_flag) {
+    // a wait gave up: give copies and MMAs in flight a bounded time to land before anything goes away
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  cluster_sync_all();  // neither CTA frees TMEM or leaves while the other may still use it or signal its barriers
+  if (run && warp == kIssuerWarp) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem, 512);
+  }
+}
+
+}  // namespace h3a

@@ -7,11 +7,13 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
 
 #include "attn_fwd.cuh"
+#include "attn_fwd_pair.cuh"
 #include "qk_prep.cuh"
 
 namespace {
@@ -37,8 +39,9 @@ EncodeTiledFn get_encode_fn() {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// x[l*stride_l + h*stride_h + c]: dims (128, L, H); box = (box_inner, 128 rows, 1 head), 128-byte swizzle.
-int32_t make_map(CUtensorMap* m, const void* ptr, bool fp8, int64_t L, int64_t H, int64_t stride_l, int64_t stride_h) {
+// x[l*stride_l + h*stride_h + c]: dims (128, L, H); box = (box_inner, box_rows, 1 head), 128-byte swizzle.
+int32_t make_map(CUtensorMap* m, const void* ptr, bool fp8, int64_t L, int64_t H, int64_t stride_l, int64_t stride_h,
+                 uint32_t box_rows = 128) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return H3A_ERR_DRIVER;
   const int64_t es = fp8 ? 1 : 2;
@@ -46,7 +49,7 @@ int32_t make_map(CUtensorMap* m, const void* ptr, bool fp8, int64_t L, int64_t H
   if (stride_l <= 0 || stride_h <= 0) return H3A_ERR_ARG;
   cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(L), static_cast<cuuint64_t>(H)};
   cuuint64_t strides[2] = {static_cast<cuuint64_t>(stride_l * es), static_cast<cuuint64_t>(stride_h * es)};
-  cuuint32_t box[3] = {fp8 ? 128u : 64u, 128u, 1u};
+  cuuint32_t box[3] = {fp8 ? 128u : 64u, box_rows, 1u};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = enc(m, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims,
                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -100,6 +103,37 @@ int32_t launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
   if (attr_err[dev] != cudaSuccess) return H3A_ERR_LAUNCH;
   const unsigned grid = static_cast<unsigned>(a.n_qpairs) * static_cast<unsigned>(a.H);
   h3a::attn_fwd_kernel<kFp8, kSparse, kFixed><<<grid, h3a::AttnLayout<kFixed>::kThreads, h3a::kAttnSmemBytes, st>>>(mq, mk, mv, a);
+  return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
+}
+
+// Dense attention with a fixed softmax reference runs on CTA pairs (attn_fwd_pair.cuh).  H3A_PAIR=0 in the
+// environment (read once) keeps every launch on the single-CTA kernel, for side-by-side measurements.
+bool pair_kernel_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("H3A_PAIR");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
+
+template <bool kFp8>
+int32_t launch_attn_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a, cudaStream_t st) {
+  static std::once_flag once[kMaxDevices];
+  static cudaError_t attr_err[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return H3A_ERR_LAUNCH;
+  std::call_once(once[dev], [dev] {
+    cudaError_t e = cudaFuncSetAttribute(h3a::attn_fwd_pair_kernel<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         h3a::kPairSmemBytes);
+    cudaFuncAttributes fa;
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, h3a::attn_fwd_pair_kernel<kFp8>);
+    if (e == cudaSuccess && fa.numRegs < h3a::AttnLayout<true>::kLaunchRegs) e = cudaErrorLaunchOutOfResources;
+    attr_err[dev] = e;
+  });
+  if (attr_err[dev] != cudaSuccess) return H3A_ERR_LAUNCH;
+  const unsigned n_clusters = static_cast<unsigned>((a.Lq + 511) / 512);
+  const unsigned grid = 2u * n_clusters * static_cast<unsigned>(a.H);  // the kernel carries its cluster shape (2,1,1)
+  h3a::attn_fwd_pair_kernel<kFp8><<<grid, h3a::kPairThreads, h3a::kPairSmemBytes, st>>>(mq, mk, mv, a);
   return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
 }
 
@@ -207,6 +241,11 @@ int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream) {
     a.row_ptr = p->row_ptr; a.plan = plan; a.plan_cnt = plan_cnt;
     a.heavy_pairs = (p->sparse_heavy_pairs > 0 && p->sparse_heavy_pairs < a.n_qpairs) ? p->sparse_heavy_pairs : 0;
     return fixed ? launch_attn<false, true, true>(mq, mk, mv, a, st) : launch_attn<false, true, false>(mq, mk, mv, a, st);
+  }
+  if (fixed && pair_kernel_enabled()) {
+    // CTA pairs: each CTA stages 32-key boxes of K (its share of every 64-key MMA group) and 64 columns of V
+    if ((rc = make_map(&mk, p->k, fp8, p->Lk, p->H, p->k_stride_l, p->k_stride_h, 32)) != H3A_OK) return rc;
+    return fp8 ? launch_attn_pair<true>(mq, mk, mv, a, st) : launch_attn_pair<false>(mq, mk, mv, a, st);
   }
   if (fp8) return fixed ? launch_attn<true, false, true>(mq, mk, mv, a, st) : launch_attn<true, false, false>(mq, mk, mv, a, st);
   return fixed ? launch_attn<false, false, true>(mq, mk, mv, a, st) : launch_attn<false, false, false>(mq, mk, mv, a, st);

@@ -457,3 +457,86 @@ def test_repeated_sparse_launches_with_uneven_streams_stay_finite(h, cfg0):
         assert bool(torch.isfinite(out.float()).all())
         first = out if first is None else first
         assert torch.equal(out, first)
+
+
+# ------------------------------------------------------------------------------------------ CTA-pair kernel
+# Dense attention with a fixed softmax reference runs on pairs of CTAs (one MMA of 256 rows per pair).  The cases
+# cover: one pair with its second CTA partly or wholly beyond the last query row, ragged key tails, several pairs
+# per head, several heads, and the FP8 operands.
+PAIR_BOUND = 14.0  # |q.k|/sqrt(128) of unit-normal rows stays far below this
+
+
+@pytest.mark.parametrize("L,Lk,H", [(512, 128, 1), (256, 300, 1), (257, 129, 2), (700, 1000, 3), (1536, 2048, 2), (4096, 4096, 4)])
+def test_pair_kernel_dense_shapes(h, L, Lk, H):
+    q, k, v = bf16_inputs(L, H, 900 + L + Lk, Lk)
+    ref, ref_lse = O.attention(q.float(), k.float(), v.float(), return_lse=True)
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out, lse = h.attn_fwd(dev(q), dev(k), dev(v), return_lse=True, logit_bound=PAIR_BOUND, status_word=st)
+    assert h.read_status(st) == 0
+    check(out, ref, mx=3e-2 if Lk < 256 else BF16_MAX, mean=4e-3 if Lk < 256 else BF16_MEAN)
+    assert float((lse.cpu().t() - ref_lse).abs().max()) < 2e-3
+
+
+@pytest.mark.parametrize("L,H", [(512, 2), (1000, 2), (130, 1)])
+def test_pair_kernel_fp8(h, L, H):
+    q, k, v = bf16_inputs(L, H, 950 + L)
+    qq, sq = O.quantize_e4m3_blocks(q.float())
+    kq, sk = O.quantize_e4m3_blocks(k.float())
+    ref = O.attention(O.dequantize_blocks(qq, sq), O.dequantize_blocks(kq, sk), v.float())
+    to_dev = lambda x: dev(x.to(torch.float8_e4m3fn).view(torch.uint8).permute(1, 0, 2).contiguous()).permute(1, 0, 2)
+    out = h.attn_fwd(to_dev(qq), to_dev(kq), dev(v), h.MODE_FP8_QK, dev(sq), dev(sk), logit_bound=PAIR_BOUND)
+    check(out, ref, mx=3e-2 if L < 256 else BF16_MAX, mean=4e-3 if L < 256 else BF16_MEAN)
+
+
+def test_pair_kernel_agrees_with_single_cta_kernel(h, tmp_path):
+    """The same seeded case through the single-CTA kernel (H3A_PAIR=0 is read once per process, so a child
+    process runs it): both kernels do the same arithmetic per row in the same order."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = tmp_path / "single.pt"
+    code = (
+        "import sys, torch; sys.path.insert(0, %r)\n"
+        "import pika_h3_flex_b200 as h\n"
+        "g = torch.Generator().manual_seed(77)\n"
+        "q, k, v = (torch.randn(1100, 3, 128, generator=g).bfloat16().cuda() for _ in range(3))\n"
+        "torch.save(h.attn_fwd(q, k, v, logit_bound=%r).cpu(), %r)\n" % (root, PAIR_BOUND, str(path))
+    )
+    env = dict(os.environ, H3A_PAIR="0")
+    subprocess.run([sys.executable, "-c", code], check=True, env=env, timeout=300)
+    g = torch.Generator().manual_seed(77)
+    q, k, v = (torch.randn(1100, 3, 128, generator=g).bfloat16().cuda() for _ in range(3))
+    out = h.attn_fwd(q, k, v, logit_bound=PAIR_BOUND).cpu()
+    single = torch.load(path)
+    assert float((out.float() - single.float()).abs().max()) <= 1e-3
+    check(out, O.attention(q.float().cpu(), k.float().cpu(), v.float().cpu()))
+
+
+def test_pair_kernel_skips_work_when_the_status_word_is_already_set(h):
+    """A launch whose status word already holds an error does nothing: every pair reads rank 0's verdict,
+    passes both cluster barriers and returns without touching TMEM or the output."""
+    q, k, v = bf16_inputs(1024, 2, 970)
+    st = torch.full((1,), 0x105, dtype=torch.int32, device="cuda")
+    out = torch.full((1024, 2, 128), 7.0, dtype=torch.bfloat16, device="cuda")
+    h.attn_fwd(dev(q), dev(k), dev(v), out=out, logit_bound=PAIR_BOUND, status_word=st)
+    torch.cuda.synchronize()
+    assert bool((out == 7.0).all())
+    assert int(st.item()) == 0x105
+    st.zero_()
+    h.attn_fwd(dev(q), dev(k), dev(v), out=out, logit_bound=PAIR_BOUND, status_word=st)  # the context is still usable
+    assert h.read_status(st) == 0
+    check(out, O.attention(q.float(), k.float(), v.float()))
+
+
+def test_pair_kernel_repeated_launches_are_bit_identical(h):
+    q, k, v = bf16_inputs(2304, 4, 980, 3000)
+    qd, kd, vd = dev(q), dev(k), dev(v)
+    first = None
+    for _ in range(30):
+        out = torch.full((2304, 4, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+        h.attn_fwd(qd, kd, vd, out=out, logit_bound=PAIR_BOUND)
+        assert bool(torch.isfinite(out.float()).all())
+        first = out if first is None else first
+        assert torch.equal(out, first)
+    check(first, O.attention(q.float(), k.float(), v.float()))
