@@ -43,11 +43,11 @@ WORKLOADS = {
     "prof_fp8": ((15, 32, 32), 1024, 16, "fp8_qk", None, 2001),
     "prof_sparse": ((31, 32, 32), 1024, 16, "block_sparse", (3, 32, 32), 2003),
 }
-# dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_kernel launch, from the ncu captures summarised
+# dram__bytes_read.sum + dram__bytes_write.sum of one attention-kernel launch, from the ncu captures summarised
 # under profiles/ (None until a capture of that workload exists)
 NCU_TRAFFIC_BYTES = {
-    "prof_dense": 251.6e6,           # measured (profiles/attn_fwd_dense_bf16_prof_dense.md)
-    "cfg1_dense": 251.6e6 * 7.535,   # the same capture scaled by the units per launch (L*H: 49,384*40 / 16,384*16)
+    "prof_dense": 250.9e6,           # measured (profiles/attn_fwd_dense_bf16_prof_dense.md)
+    "cfg1_dense": 250.9e6 * 7.535,   # the same capture scaled by the units per launch (L*H: 49,384*40 / 16,384*16)
 }
 
 

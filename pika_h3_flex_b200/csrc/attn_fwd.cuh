@@ -119,12 +119,21 @@ __device__ unsigned long long* g_trace = nullptr;
 #define H3A_STAMP(role, idx, k) do {} while (0)
 #endif
 
+// The limits and the status word are read from the kernel's argument block when a wait runs out, so that a
+// wait context costs two registers in the loops that carry it.
 struct WaitCtx {
-  volatile uint32_t* abort_flag;  // this CTA's flag
-  int* status;
-  long long limit_ns;
+  uint32_t abort_smem;            // shared-memory address of this CTA's abort flag
   uint32_t peer_abort;            // shared::cluster address of the peer CTA's flag (CTA pairs), else 0
+  const AttnArgs* args;           // status word and time limit
 };
+__device__ __forceinline__ uint32_t ld_shared_u32_volatile(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_shared_u32_volatile(uint32_t addr, uint32_t v) {
+  asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ bool bounded_wait(const WaitCtx& c, uint32_t bar, uint32_t parity, int code) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -132,14 +141,14 @@ __device__ __forceinline__ bool bounded_wait(const WaitCtx& c, uint32_t bar, uin
   uint64_t t0 = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++polls & 63u) == 0u) {
-      if (*c.abort_flag) return false;
+      if (ld_shared_u32_volatile(c.abort_smem)) return false;
       uint64_t now = global_timer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (static_cast<long long>(now - t0) > c.limit_ns) {
-        *c.abort_flag = 1u;
+      } else if (static_cast<long long>(now - t0) > c.args->wait_ns) {
+        st_shared_u32_volatile(c.abort_smem, 1u);
         if (c.peer_abort) st_shared_cluster_u32(c.peer_abort, 1u);  // the peer's waits give up at their next check
-        if (c.status) atomicCAS(c.status, 0, code | (static_cast<int>(blockIdx.x & 0x7FFFFF) << 8));
+        if (c.args->status) atomicCAS(c.args->status, 0, code | (static_cast<int>(blockIdx.x & 0x7FFFFF) << 8));
         return false;
       }
     }
@@ -167,7 +176,7 @@ __device__ __forceinline__ bool warp_wait(const WaitCtx& c, uint32_t bar, uint32
 // Diagnostic: one warp waits, with the same bounded wait the attention kernel uses, on an mbarrier that nothing
 // ever arrives on.  The wait must run out, record kWaitSelfTest in the status word and return.
 constexpr int kWaitSelfTest = 9;
-__global__ void wait_selftest_kernel(int* status, long long limit_ns) {
+__global__ void wait_selftest_kernel(const AttnArgs args) {
   __shared__ AttnBars bars;
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&bars.q_full), 1);
@@ -175,7 +184,7 @@ __global__ void wait_selftest_kernel(int* status, long long limit_ns) {
     fence_mbar_init();
   }
   __syncthreads();
-  WaitCtx wc{&bars.abort_flag, status, limit_ns, 0u};
+  WaitCtx wc{smem_u32(const_cast<const uint32_t*>(&bars.abort_flag)), 0u, &args};
   bounded_wait(wc, smem_u32(&bars.q_full), 0, kWaitSelfTest);
 }
 
@@ -294,7 +303,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem = bars->tmem_base;
 
-  WaitCtx wc{&bars->abort_flag, args.status, args.wait_ns, 0u};
+  WaitCtx wc{smem_u32(const_cast<const uint32_t*>(&bars->abort_flag)), 0u, &args};
 
   if (warp >= LY::kSoftmaxWarps) {
    setmaxnreg_dec<LY::kHelperRegs>();

@@ -4,8 +4,9 @@
 // shared-memory bandwidth (operand fetch plus TMA writes); the pair moves 30 % fewer bytes through each SM's
 // shared memory for the same math.
 //
-// A pair owns 512 query rows of one head: CTA r (rank in the cluster) rows [512 c + 256 r, +256) as two streams of
-// 128 rows, exactly the row layout of the single-CTA kernel.  Per CTA, as there:
+// A pair owns four consecutive 128-row query tiles of one head; stream t of CTA r (rank in the cluster) is tile
+// 4 c + 2 t + r, so one M = 256 MMA covers two ADJACENT query tiles (in the block-sparse mode their key lists
+// overlap most, and a key tile is computed for both when either lists it).  Per CTA, as in the single-CTA kernel:
 //   warp 16  producer : TMA loads of its Q tiles (once) and of ITS HALF of K_j / V_j into a ring of 16 KB stages;
 //                       the bytes of both CTAs are counted on the mbarriers of rank 0
 //   warps 17,18       : rank 0 only - one issuer per stream; S = Q_t K^T (N = 64 keys per MMA group, 32 key rows
@@ -13,8 +14,12 @@
 //                       every commit is sent to the barrier in both CTAs
 //   warps 0-15        : softmax with the fixed reference, one warpgroup per (stream, 64-key half); P is published
 //                       with one arrive per warp on rank 0's barrier (local or through the cluster)
-// Only the fixed-reference softmax is implemented here (dense bf16 and FP8-QK); everything else runs on the
-// single-CTA kernel.
+// Only the fixed-reference softmax is implemented here (dense bf16, FP8-QK, block-sparse); the running-maximum
+// softmax runs on the single-CTA kernel.
+//
+// Block-sparse: the four key-tile lists of a pair are merged into one plan, entry = (key tile << 4) | flags, flag
+// bit 2 t + r set when query tile 4 c + 2 t + r lists the key tile.  Both CTAs load every listed tile; stream t
+// computes an entry when either of its two query tiles lists it, and the CTA whose tile does not writes P = 0.
 //
 // Shared memory of a CTA:  Q tiles 2 x 32 KB | ring of 8 stages x 16 KB | barriers
 //   K stage (bf16): [dim half][64-key half][32 keys][128 B]   - the 32 keys this CTA supplies to each N = 64 group
@@ -41,7 +46,7 @@ struct PairBars {
   uint64_t q_full;                 // rank 0
   uint64_t s_full[2][2];           // [stream][half], both CTAs
   uint64_t p_full[2][2];           // rank 0: one arrive per softmax warp of the (stream, half) warpgroup of BOTH CTAs
-  uint64_t o_full[2][2];           // both CTAs
+  uint64_t o_full[2];              // both CTAs: every MMA of stream t has completed (one phase, after the last tile)
   uint64_t drain[2];               // rank 0: last commit of issuer t
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
@@ -53,8 +58,55 @@ constexpr int kPairSmemBytes = 2 * kQTileBytes + kPairStages * kPairStageBytes +
 static_assert(kPairSmemBytes <= 232448, "shared memory budget");
 
 enum : int { kWaitDrain = 8 };
+// S production: 0 = one N = 64 MMA group per 64-key half (32 key rows from each CTA); 1 = one N = 128 group per key
+// tile (64 key rows from each CTA, 25 % less operand traffic, but both halves of a stream become available, and
+// are needed back, together: two dependency chains per CTA instead of four; measured 11 % slower).  The host
+// picks the matching K box (32 or 64 rows) from kPairKBoxRows.
+#ifndef H3A_PAIR_FULL_S
+#define H3A_PAIR_FULL_S 0
+#endif
+constexpr bool kPairFullS = H3A_PAIR_FULL_S != 0;
+constexpr int kPairKBoxRows = kPairFullS ? 64 : 32;
+#ifndef H3A_PAIR_SOFTMAX_REGS
+#define H3A_PAIR_SOFTMAX_REGS 104
+#endif
+#ifndef H3A_PAIR_HELPER_REGS
+#define H3A_PAIR_HELPER_REGS 64
+#endif
+constexpr int kPairSoftmaxRegs = H3A_PAIR_SOFTMAX_REGS, kPairHelperRegs = H3A_PAIR_HELPER_REGS;
+static_assert(512 * kPairSoftmaxRegs + 128 * kPairHelperRegs <= AttnLayout<true>::kLaunchRegs * kPairThreads,
+              "setmaxnreg budget exceeds the launch allocation");
 
-template <bool kFp8>
+// Merge the sorted key-tile lists of query tiles 4c .. 4c+3 into one list with a flag bit per query tile.
+__global__ void build_cluster_plan_kernel(const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ col_idx,
+                                          int nqb, int n_clusters, int32_t* __restrict__ plan, int32_t* __restrict__ plan_cnt) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= n_clusters) return;
+  int pos[4], end[4];
+  for (int i = 0; i < 4; ++i) {
+    const int r = 4 * c + i;
+    pos[i] = (r < nqb) ? row_ptr[r] : 0;
+    end[i] = (r < nqb) ? row_ptr[r + 1] : 0;
+  }
+  int32_t* out = plan + row_ptr[4 * c];  // the merged list is never longer than the four lists together
+  int n = 0;
+  for (;;) {
+    int lo = 0x7FFFFFFF;
+    for (int i = 0; i < 4; ++i)
+      if (pos[i] < end[i]) lo = min(lo, col_idx[pos[i]]);
+    if (lo == 0x7FFFFFFF) break;
+    int f = 0;
+    for (int i = 0; i < 4; ++i)
+      if (pos[i] < end[i] && col_idx[pos[i]] == lo) {
+        f |= 1 << i;
+        ++pos[i];
+      }
+    out[n++] = (lo << 4) | f;
+  }
+  plan_cnt[c] = n;
+}
+
+template <bool kFp8, bool kSparse>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const AttnArgs args) {
@@ -74,9 +126,38 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const uint32_t rank = cluster_ctarank();
   const int n_clusters = (args.Lq + 4 * kTile - 1) / (4 * kTile);
   const int cid = blockIdx.x >> 1;
-  const int head = cid / n_clusters;
-  const int q0 = (cid % n_clusters) * 4 * kTile + static_cast<int>(rank) * 2 * kTile;
-  const int n_it = args.n_kv_tiles;
+  // pair -> (head, group of four query tiles): head-major; block-sparse: the groups with long key lists (dense
+  // audio rows) of ALL heads first, as in the single-CTA kernel
+  int head = cid / n_clusters, cl = cid % n_clusters;
+  if constexpr (kSparse) {
+    const int heavy = (args.heavy_pairs + 1) / 2;
+    if (heavy > 0 && heavy < n_clusters) {
+      if (cid < heavy * args.H) {
+        head = cid / heavy;
+        cl = cid % heavy;
+      } else {
+        const int r = cid - heavy * args.H, n_light = n_clusters - heavy;
+        head = r / n_light;
+        cl = heavy + r % n_light;
+      }
+    }
+  }
+  auto q_tile = [&](int t) { return 4 * cl + 2 * t + static_cast<int>(rank); };  // query tile of this CTA's stream t
+
+  // ---- plan: which key tiles, for which of the pair's four query tiles
+  int n_it;
+  const int32_t* plan = nullptr;
+  if constexpr (kSparse) {
+    plan = args.plan + args.row_ptr[min(4 * cl, args.nqb)];
+    n_it = args.plan_cnt[cl];
+  } else {
+    n_it = args.n_kv_tiles;
+  }
+  auto entry_at = [&](int it) -> int {
+    if constexpr (kSparse) return plan[it];
+    else return (it << 4) | 15;
+  };
+  auto stream_needs = [](int e, int t) { return ((e >> (2 * t)) & 3) != 0; };
 
   constexpr uint32_t kQBytes = kFp8 ? kHalfBytes : kQTileBytes;  // bytes per Q tile
   constexpr uint32_t kKHalfBytes = kFp8 ? 8192 : 16384;          // this CTA's half of a K tile
@@ -93,8 +174,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       for (int hf = 0; hf < 2; ++hf) {
         mbar_init(smem_u32(&bars->s_full[t][hf]), 1);
         mbar_init(smem_u32(&bars->p_full[t][hf]), 8);
-        mbar_init(smem_u32(&bars->o_full[t][hf]), 1);
       }
+      mbar_init(smem_u32(&bars->o_full[t]), 1);
       mbar_init(smem_u32(&bars->drain[t]), 1);
     }
     bars->abort_flag = 0;
@@ -114,7 +195,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const uint32_t bars_peer = mapa_shared(smem_u32(bars), rank ^ 1u);
   auto at0 = [&](const void* local) { return bars0 + (smem_u32(local) - smem_u32(bars)); };
   auto at_peer = [&](const void* local) { return bars_peer + (smem_u32(local) - smem_u32(bars)); };
-  WaitCtx wc{&bars->abort_flag, args.status, args.wait_ns, at_peer(const_cast<const uint32_t*>(&bars->abort_flag))};
+  WaitCtx wc{smem_u32(const_cast<const uint32_t*>(&bars->abort_flag)), at_peer(const_cast<const uint32_t*>(&bars->abort_flag)), &args};
 
   if (run) {
   if (warp == kIssuerWarp) {
@@ -127,7 +208,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   tmem = bars->tmem_base;
 
   if (warp >= LY::kSoftmaxWarps) {
-   setmaxnreg_dec<LY::kHelperRegs>();
+   setmaxnreg_dec<kPairHelperRegs>();
    if (warp == kProducerWarp) {
     // =========================================================== producer (both CTAs)
     const uint32_t leader = elect_one();
@@ -136,13 +217,14 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const uint32_t qbar = at0(&bars->q_full);
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
-        tma_load_3d_pair_if(leader, q_smem + t * kQTileBytes, &tm_q, qbar, 0, q0 + t * kTile, head);
-        if constexpr (!kFp8) tma_load_3d_pair_if(leader, q_smem + t * kQTileBytes + kHalfBytes, &tm_q, qbar, 64, q0 + t * kTile, head);
+        tma_load_3d_pair_if(leader, q_smem + t * kQTileBytes, &tm_q, qbar, 0, q_tile(t) * kTile, head);
+        if constexpr (!kFp8) tma_load_3d_pair_if(leader, q_smem + t * kQTileBytes + kHalfBytes, &tm_q, qbar, 64, q_tile(t) * kTile, head);
       }
     }
     int cnt = 0;
     bool ok = true;
     for (int it = 0; ok && it < n_it; ++it) {
+      const int tile = entry_at(it) >> 4;
 #pragma unroll
       for (int kv = 0; kv < 2; ++kv) {  // K half-tile, then V half-tile
         const int s = cnt % kPairStages;
@@ -153,19 +235,21 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const uint32_t dst = ring_smem + s * kPairStageBytes;
         if (kv == 0) {
           if (rank == 0) mbar_arrive_expect_tx_if(leader, smem_u32(&bars->kv_full[s]), 2 * kKHalfBytes);
+          if constexpr (kPairFullS) {  // the 64 keys this CTA supplies to the N = 128 group
+            const int key0 = tile * kTile + 64 * static_cast<int>(rank);
+            tma_load_3d_pair_if(leader, dst, &tm_k, fb, 0, key0, head);
+            if constexpr (!kFp8) tma_load_3d_pair_if(leader, dst + 8192, &tm_k, fb, 64, key0, head);
+          } else {
 #pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {  // the 32 keys this CTA supplies to the N = 64 group of half hf
-            const int key0 = it * kTile + 64 * hf + 32 * static_cast<int>(rank);
-            if constexpr (kFp8) {
+            for (int hf = 0; hf < 2; ++hf) {  // the 32 keys this CTA supplies to the N = 64 group of half hf
+              const int key0 = tile * kTile + 64 * hf + 32 * static_cast<int>(rank);
               tma_load_3d_pair_if(leader, dst + hf * 4096, &tm_k, fb, 0, key0, head);
-            } else {
-              tma_load_3d_pair_if(leader, dst + hf * 4096, &tm_k, fb, 0, key0, head);
-              tma_load_3d_pair_if(leader, dst + 8192 + hf * 4096, &tm_k, fb, 64, key0, head);
+              if constexpr (!kFp8) tma_load_3d_pair_if(leader, dst + 8192 + hf * 4096, &tm_k, fb, 64, key0, head);
             }
           }
         } else {
           if (rank == 0) mbar_arrive_expect_tx_if(leader, smem_u32(&bars->kv_full[s]), 2 * kVHalfBytes);
-          tma_load_3d_pair_if(leader, dst, &tm_v, fb, 64 * static_cast<int>(rank), it * kTile, head);
+          tma_load_3d_pair_if(leader, dst, &tm_v, fb, 64 * static_cast<int>(rank), tile * kTile, head);
         }
         ++cnt;
       }
@@ -176,8 +260,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     if (n_it > 0) {
       const int t = warp - kIssuerWarp;
       const uint32_t leader = elect_one();
-      constexpr uint32_t idesc_s = kFp8 ? umma_idesc(UMMA_FMT_E4M3, UMMA_FMT_E4M3, 0, 0, 256, 64)
-                                        : umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 0, 256, 64);
+      constexpr uint32_t kSN = kPairFullS ? 128 : 64;
+      constexpr uint32_t idesc_s = kFp8 ? umma_idesc(UMMA_FMT_E4M3, UMMA_FMT_E4M3, 0, 0, 256, kSN)
+                                        : umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 0, 256, kSN);
       constexpr uint32_t idesc_pv = umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 1, 256, 128);
       bool ok = warp_wait(wc, smem_u32(&bars->q_full), 0, kWaitQFull);
       tc_fence_after_sync();
@@ -213,27 +298,32 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         commit_both(&bars->s_full[t][hf]);
       };
       // O_t += P[t][hf] V[hf]: A = P from each CTA's TMEM, B = this CTA's 64 columns of V, MN-major
-      auto issue_pv = [&](int hf, int sv, bool last) {
+      auto issue_pv = [&](int hf, int sv) {
         const uint64_t vd = v_desc0 + static_cast<uint64_t>((sv * kPairStageBytes + hf * 8192) >> 4);
         const uint32_t a = s_tmem + hf * 64;
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           umma_pair_bf16_ts_if(leader, o_tmem, a + k * 8, vd + (k * 2048 >> 4), idesc_pv, (pv_cnt > 0 || k > 0) ? 1u : 0u);
         ++pv_cnt;
-        if (last) commit_both(&bars->o_full[t][hf]);  // only the epilogue waits for O
       };
 
-      if (ok) {  // prologue: both S halves of tile 0
+      // Each issuer walks every plan entry, also those its stream skips: a K/V stage is released by one commit
+      // from each issuer, and waiting for the stage first keeps the two in step.
+      if (ok) {  // prologue: both S halves of entry 0
         ok = warp_wait(wc, smem_u32(&bars->kv_full[0]), 0, kWaitKvFullK);
         if (ok) {
           tc_fence_after_sync();
-          issue_s(0, 0);
-          issue_s(1, 0);
+          if (stream_needs(entry_at(0), t)) {
+            issue_s(0, 0);
+            if constexpr (!kPairFullS) issue_s(1, 0);
+          }
           commit_both(&bars->kv_empty[0]);
         }
       }
       for (int it = 0; ok && it < n_it; ++it) {
         const bool has_next = (it + 1 < n_it);
+        const bool mine = stream_needs(entry_at(it), t);
+        const bool mine_next = has_next && stream_needs(entry_at(it + 1), t);
         const int cv = 2 * it + 1, ck = 2 * it + 2;
         const int sv = cv % kPairStages, sk = ck % kPairStages;
         ok = warp_wait(wc, smem_u32(&bars->kv_full[sv]), (cv / kPairStages) & 1, kWaitKvFullV);
@@ -241,27 +331,31 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         bool k_ready = false;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-          H3A_STAMP(2 + t, 2 * it + hf, 0);
-          ok = warp_wait(wc, smem_u32(&bars->p_full[t][hf]), p_cnt[hf] & 1, kWaitPFull);
-          if (!ok) break;
-          ++p_cnt[hf];
-          tc_fence_after_sync();
-          H3A_STAMP(2 + t, 2 * it + hf, 1);
-          issue_pv(hf, sv, !has_next);
-          H3A_STAMP(2 + t, 2 * it + hf, 2);
+          if (mine) {
+            H3A_STAMP(2 + t, 2 * it + hf, 0);
+            ok = warp_wait(wc, smem_u32(&bars->p_full[t][hf]), p_cnt[hf] & 1, kWaitPFull);
+            if (!ok) break;
+            ++p_cnt[hf];
+            tc_fence_after_sync();
+            H3A_STAMP(2 + t, 2 * it + hf, 1);
+            issue_pv(hf, sv);
+            H3A_STAMP(2 + t, 2 * it + hf, 2);
+          }
           if (has_next && !k_ready) {
             ok = warp_wait(wc, smem_u32(&bars->kv_full[sk]), (ck / kPairStages) & 1, kWaitKvFullK);
             if (!ok) break;
             k_ready = true;
             tc_fence_after_sync();
           }
-          if (has_next) issue_s(hf, sk);
+          if (mine_next && (!kPairFullS || hf == 1)) issue_s(kPairFullS ? 0 : hf, sk);  // full: both halves at once
           H3A_STAMP(2 + t, 2 * it + hf, 3);
         }
         if (!ok) break;
         commit_both(&bars->kv_empty[sv]);
         if (has_next) commit_both(&bars->kv_empty[sk]);
       }
+      // only the epilogue waits for O: one arrive per CTA once every MMA of the stream has completed
+      if (ok) commit_both(&bars->o_full[t]);
       // the commits to the peer's barriers were issued before this one and complete in order: once it has
       // arrived nothing of this issuer is still on its way to the peer CTA
       if (ok) {
@@ -272,7 +366,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     __syncwarp();
    }
   } else {
-    setmaxnreg_inc<LY::kSoftmaxRegs>();
+    setmaxnreg_inc<kPairSoftmaxRegs>();
     // =========================================================== softmax, fixed reference: one warpgroup per (stream, half)
     const int wg = warp >> 2;
     const int t = wg & 1;
@@ -282,13 +376,14 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t sb = tmem + lane_base + t * kTile + hf * 64;
     const uint32_t o_addr = tmem + lane_base + 256 + t * kTile + hf * 64;
-    const int q_row = q0 + t * kTile + row;
+    const int q_row = q_tile(t) * kTile + row;
+    const int own_bit = 2 * t + static_cast<int>(rank);  // this CTA's query tile among the pair's four
     const int last_tile = args.n_kv_tiles - 1;
     const int tail = args.Lk - last_tile * kTile;
     const uint32_t p_bar = at0(&bars->p_full[t][hf]);
     float qs = 1.0f;
     if constexpr (kFp8) {
-      const int qb = min(q0 / kTile + t, args.nqb - 1);
+      const int qb = min(q_tile(t), args.nqb - 1);
       qs = args.q_scale[head * args.nqb + qb];
     }
     const float m_ref = args.fixed_m;
@@ -297,19 +392,35 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     bool ok = true;
     uint32_t s[64];
     for (int it = 0; ok && it < n_it; ++it) {
+      const int e = entry_at(it);
+      if (!stream_needs(e, t)) continue;
+      const int tile = e >> 4;
       float c = args.scale_log2;
-      if constexpr (kFp8) c *= qs * args.k_scale[head * args.nkb + it];
+      if constexpr (kFp8) c *= qs * args.k_scale[head * args.nkb + tile];
       if (row == 0 && t == 0) H3A_STAMP(hf, j, 0);
-      ok = warp_wait(wc, smem_u32(&bars->s_full[t][hf]), j & 1, kWaitSFull);
+      ok = warp_wait(wc, smem_u32(&bars->s_full[t][kPairFullS ? 0 : hf]), j & 1, kWaitSFull);
       if (!ok) break;
       tc_fence_after_sync();
+      if (kSparse && !((e >> own_bit) & 1)) {
+        // the key tile is listed only for the peer's query tile: this CTA's rows contribute nothing (P = 0); the
+        // S of the pair's MMA is complete, so its buffer may be overwritten
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[i] = 0u;
+        tmem_st32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(p_bar);
+        ++j;
+        continue;
+      }
       tmem_ld32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_ld32(sb + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
       tmem_wait_ld();
       reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&s[32]));
       if (row == 0 && t == 0) H3A_STAMP(hf, j, 2);
-      if (it == last_tile && tail < kTile) {
+      if (tile == last_tile && tail < kTile) {
         const int valid = tail - hf * 64;
 #pragma unroll
         for (int i = 0; i < 64; ++i)
@@ -343,17 +454,14 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) {
-        if (rank == 0) mbar_arrive(smem_u32(&bars->p_full[t][hf]));
-        else mbar_arrive_cluster(p_bar);
-      }
+      if (lane == 0) mbar_arrive_cluster(p_bar);  // rank 0's barrier: its own CTA's or the peer's
       if (row == 0 && t == 0) H3A_STAMP(hf, j, 5);
       ++j;
     }
     // ---- epilogue: as in the single-CTA kernel (own last P V, named barrier, row sums through the Q tile)
     bool have = ok && j > 0;
     if (have) {
-      have = warp_wait(wc, smem_u32(&bars->o_full[t][hf]), 0, kWaitOFull);  // its only phase: the last tile's P V
+      have = warp_wait(wc, smem_u32(&bars->o_full[t]), 0, kWaitOFull);  // its only phase: every MMA of the stream is done
       if (have) tc_fence_after_sync();
     }
     asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");
@@ -363,8 +471,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     if (have) tc_fence_after_sync();
     const bool row_valid = q_row < args.Lq;
     __nv_bfloat16* orow = args.o + static_cast<long long>(q_row) * args.o_stride_l + static_cast<long long>(head) * args.o_stride_h + 64 * hf;
-    if (have) {
-      const float l_tot = l_sum + lbuf[(hf ^ 1) * 128 + row];
+    const float l_tot = l_sum + lbuf[(hf ^ 1) * 128 + row];
+    if (have && l_tot > 0.0f) {
       const float inv = 1.0f / l_tot;
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
@@ -385,6 +493,12 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       }
       if (row_valid && args.lse && hf == 0)
         args.lse[static_cast<long long>(head) * args.Lq + q_row] = (m_ref + log2f(l_tot)) * 0.6931471805599453f;
+    } else if (ok && row_valid && (j == 0 || have)) {
+      // no key tile listed for this query tile (the stream may still have run for the peer's tile): zero rows
+      const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int x = 0; x < 64; x += 8) *reinterpret_cast<uint4*>(orow + x) = z;
+      if (args.lse && hf == 0) args.lse[static_cast<long long>(head) * args.Lq + q_row] = -INFINITY;
     }
   }
   }  // run

@@ -116,24 +116,24 @@ bool pair_kernel_enabled() {
   return on;
 }
 
-template <bool kFp8>
+template <bool kFp8, bool kSparse = false>
 int32_t launch_attn_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a, cudaStream_t st) {
   static std::once_flag once[kMaxDevices];
   static cudaError_t attr_err[kMaxDevices];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return H3A_ERR_LAUNCH;
   std::call_once(once[dev], [dev] {
-    cudaError_t e = cudaFuncSetAttribute(h3a::attn_fwd_pair_kernel<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(h3a::attn_fwd_pair_kernel<kFp8, kSparse>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          h3a::kPairSmemBytes);
     cudaFuncAttributes fa;
-    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, h3a::attn_fwd_pair_kernel<kFp8>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, h3a::attn_fwd_pair_kernel<kFp8, kSparse>);
     if (e == cudaSuccess && fa.numRegs < h3a::AttnLayout<true>::kLaunchRegs) e = cudaErrorLaunchOutOfResources;
     attr_err[dev] = e;
   });
   if (attr_err[dev] != cudaSuccess) return H3A_ERR_LAUNCH;
   const unsigned n_clusters = static_cast<unsigned>((a.Lq + 511) / 512);
   const unsigned grid = 2u * n_clusters * static_cast<unsigned>(a.H);  // the kernel carries its cluster shape (2,1,1)
-  h3a::attn_fwd_pair_kernel<kFp8><<<grid, h3a::kPairThreads, h3a::kPairSmemBytes, st>>>(mq, mk, mv, a);
+  h3a::attn_fwd_pair_kernel<kFp8, kSparse><<<grid, h3a::kPairThreads, h3a::kPairSmemBytes, st>>>(mq, mk, mv, a);
   return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
 }
 
@@ -235,16 +235,30 @@ int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream) {
     int32_t* plan = static_cast<int32_t*>(p->workspace);
     int32_t* plan_cnt = plan + p->nnz;
     const int threads = 128;
+    a.row_ptr = p->row_ptr; a.plan = plan; a.plan_cnt = plan_cnt;
+    a.heavy_pairs = (p->sparse_heavy_pairs > 0 && p->sparse_heavy_pairs < a.n_qpairs) ? p->sparse_heavy_pairs : 0;
+    // A CTA pair computes a key tile for two adjacent query tiles whenever either lists it.  With very sparse
+    // neighbourhood masks that duplicated work outweighs what the pair saves (measured: 7 % density, 7 % extra
+    // tiles, 3 % slower; 23 % density, 0.4 % extra, 7 % faster), so sparse launches go to pairs from 12 % up.
+    const double density = static_cast<double>(p->nnz) / (static_cast<double>(a.nqb) * static_cast<double>(a.nkb));
+    if (fixed && pair_kernel_enabled() && density >= 0.12) {
+      // CTA pairs: one merged plan per four query tiles (never longer than the four lists together, and there
+      // are no more groups of four than pairs of two, so the same workspace holds it)
+      const int n_clusters = (p->Lq + 511) / 512;
+      h3a::build_cluster_plan_kernel<<<(n_clusters + threads - 1) / threads, threads, 0, st>>>(p->row_ptr, p->col_idx, a.nqb,
+                                                                                              n_clusters, plan, plan_cnt);
+      if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
+      if ((rc = make_map(&mk, p->k, false, p->Lk, p->H, p->k_stride_l, p->k_stride_h, h3a::kPairKBoxRows)) != H3A_OK) return rc;
+      return launch_attn_pair<false, true>(mq, mk, mv, a, st);
+    }
     h3a::build_pair_plan_kernel<<<(a.n_qpairs + threads - 1) / threads, threads, 0, st>>>(p->row_ptr, p->col_idx, a.nqb,
                                                                                          a.n_qpairs, plan, plan_cnt);
     if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
-    a.row_ptr = p->row_ptr; a.plan = plan; a.plan_cnt = plan_cnt;
-    a.heavy_pairs = (p->sparse_heavy_pairs > 0 && p->sparse_heavy_pairs < a.n_qpairs) ? p->sparse_heavy_pairs : 0;
     return fixed ? launch_attn<false, true, true>(mq, mk, mv, a, st) : launch_attn<false, true, false>(mq, mk, mv, a, st);
   }
   if (fixed && pair_kernel_enabled()) {
     // CTA pairs: each CTA stages 32-key boxes of K (its share of every 64-key MMA group) and 64 columns of V
-    if ((rc = make_map(&mk, p->k, fp8, p->Lk, p->H, p->k_stride_l, p->k_stride_h, 32)) != H3A_OK) return rc;
+    if ((rc = make_map(&mk, p->k, fp8, p->Lk, p->H, p->k_stride_l, p->k_stride_h, h3a::kPairKBoxRows)) != H3A_OK) return rc;
     return fp8 ? launch_attn_pair<true>(mq, mk, mv, a, st) : launch_attn_pair<false>(mq, mk, mv, a, st);
   }
   if (fp8) return fixed ? launch_attn<true, false, true>(mq, mk, mv, a, st) : launch_attn<true, false, false>(mq, mk, mv, a, st);
@@ -370,7 +384,11 @@ int32_t h3a_selftest_wait_timeout(int32_t* status_word, int64_t wait_limit_ns, v
   if (!status_word || wait_limit_ns <= 0 || wait_limit_ns > 1000000000ll) return H3A_ERR_ARG;
   int32_t rc = check_arch();
   if (rc != H3A_OK) return rc;
-  h3a::wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status_word, wait_limit_ns);
+  AttnArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.status = status_word;
+  a.wait_ns = wait_limit_ns;
+  h3a::wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
 }
 

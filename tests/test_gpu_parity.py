@@ -540,3 +540,36 @@ def test_pair_kernel_repeated_launches_are_bit_identical(h):
         first = out if first is None else first
         assert torch.equal(out, first)
     check(first, O.attention(q.float(), k.float(), v.float()))
+
+
+@pytest.mark.parametrize("rows", [
+    # a query tile with no key tile whose partner in the MMA (the adjacent tile) has some; uneven lists
+    [[0, 1, 2, 3], [1, 2], [], [0, 4, 5, 6, 7], [0, 5], [], [3], []],
+    # four consecutive query tiles (one CTA pair) with no key tile at all, ragged last tile
+    [[0, 1, 2, 3, 4, 5], [1, 7, 8], [2, 3], [0, 9], [], [], [], [], [0, 1, 2, 3, 4, 5, 6, 7, 8, 9], [5, 6, 7]],
+])
+def test_pair_kernel_block_sparse_structures(h, rows):
+    """Block-sparse launches above 12 % density run on CTA pairs with one merged plan per four query tiles."""
+    n = len(rows)
+    nnz = sum(len(r) for r in rows)
+    assert nnz / (n * n) >= 0.12
+    L, H = n * 128 - 37, 2
+    rp = np.cumsum([0] + [len(r) for r in rows]).astype(np.int32)
+    ci = np.array([c for r in rows for c in r], dtype=np.int32)
+    q, k, v = bf16_inputs(L, H, 990 + n)
+    ref, ref_lse = O.attention(q.float(), k.float(), v.float(), csr=(rp, ci), return_lse=True)
+    bi = h.BlockIndex.from_csr(rp, ci, n).to("cuda")
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    first = None
+    for _ in range(10):
+        out = torch.full((L, H, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+        out, lse = h.attn_fwd(dev(q), dev(k), dev(v), h.MODE_BLOCK_SPARSE, block_index=bi, out=out, return_lse=True,
+                              logit_bound=PAIR_BOUND, status_word=st)
+        assert h.read_status(st) == 0
+        first = out if first is None else first
+        assert torch.equal(out, first)
+    check(first, torch.nan_to_num(ref))
+    empty = torch.tensor([len(r) == 0 for r in rows]).repeat_interleave(128)[:L]
+    assert bool((first.float().cpu()[empty] == 0).all())
+    assert bool(torch.isinf(lse.cpu()[:, empty]).all())
+    assert float((lse.cpu().t()[~empty] - ref_lse[~empty]).abs().max()) < 2e-3
