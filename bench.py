@@ -281,7 +281,7 @@ def run_ours(args):
 
         launches_per_step = 3 + (1 if bi is not None else 0)
     else:
-        ua = UlyssesAttention(None, mode, bi)
+        ua = UlyssesAttention(None, mode, bi, head_groups=args.head_groups)
 
         def step(record=False):
             return ua(q, k, v, rope)
@@ -400,6 +400,7 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg1_dense")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the cpu_baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--head-groups", type=int, default=2, help="N > 1: head groups the exchanges are pipelined over (1 = no overlap)")
     ap.add_argument("--online-max", action="store_true", help="use the running-maximum kernel instead of the fixed logit bound")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -51,3 +51,73 @@ def test_ulysses_wrapper_cuda_path(nccl_group, mode_name):
         assert st["rel_l2"] <= 6e-2, st
     else:
         assert st["max_abs"] <= 3e-2 and st["mean_abs"] <= 3e-3, st
+
+
+_CHILD = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, {root!r})
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+import pika_h3_flex_b200 as h
+from pika_h3_flex_b200.ulysses import UlyssesAttention
+from oracle import oracle as O
+grid, n_audio, H = (4, 8, 12), 128, {heads}
+pos = O.make_positions(grid, n_audio)
+L = pos.shape[0]
+q, k, v = (t.bfloat16() for t in O.seeded_qkv(L, H, seed=33))
+Ls = L // world
+sl = slice(rank * Ls, (rank + 1) * Ls)
+ok = True
+for mode_name in ("dense", "fp8_qk", "block_sparse"):
+    csr, bi, mode = None, None, h.MODE_DENSE_BF16
+    if mode_name == "block_sparse":
+        bih = h.build_block_index(grid, n_audio, (1, 2, 2))
+        csr, bi, mode = (bih.row_ptr.numpy(), bih.col_idx.numpy()), bih.to("cuda"), h.MODE_BLOCK_SPARSE
+    elif mode_name == "fp8_qk":
+        mode = h.MODE_FP8_QK
+    ref = O.joint_attention(q.float(), k.float(), v.float(), pos, mode_name, csr=csr)[sl]
+    for groups in (1, 2):
+        ua = UlyssesAttention(None, mode, bi, head_groups=groups)
+        out = ua(q[sl].cuda(), k[sl].cuda(), v[sl].cuda(), h.rope_table(pos[sl].cuda()))
+        st = O.error_stats(out.float().cpu(), ref)
+        good = st["rel_l2"] <= (6e-2 if mode_name == "fp8_qk" else 1e-2)
+        print(rank, mode_name, groups, st, flush=True)
+        ok = ok and good and tuple(out.shape) == (Ls, H, 128)
+flag = torch.tensor([1 if ok else 0], device="cuda")
+dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+dist.destroy_process_group()
+sys.exit(0 if int(flag.item()) == 1 else 1)
+"""
+
+
+@pytest.mark.parametrize("world,heads", [(2, 4), (2, 3), (4, 6)])
+def test_ulysses_multi_gpu_exchange_matches_oracle(world, heads, tmp_path):
+    """Ranks as child processes, one per GPU, NCCL: the all_to_all transport (blocks staged per peer, then placed)
+    must give every rank the oracle's rows of its sequence shard; heads = 3 on 2 ranks and 6 on 4 also pads."""
+    import subprocess
+    import sys
+
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "child.py"
+    script.write_text(_CHILD.format(root=root, heads=heads))
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
+    outs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o, _ = p.communicate()
+        outs.append(o.decode(errors="replace"))
+    assert all(p.returncode == 0 for p in procs), "\n".join(x[-2000:] for x in outs)
