@@ -260,9 +260,13 @@ def run_ours(args):
     bound = 0.0 if args.online_max else normed_logit_bound(fp8=(mode == _lib.MODE_FP8_QK))  # unit-weight QK-RMSNorm
     if world == 1:
         out = torch.empty(L, H, 128, dtype=torch.bfloat16, device=dev)
-        ws = torch.empty(16, dtype=torch.uint8, device=dev)
         if bi is not None:
             ws = torch.empty((bi.nnz + (L + 255) // 256) * 4 + 16, dtype=torch.uint8, device=dev)
+            split_bytes = 0
+        else:  # optional scratch: the CTA pairs of the last, partly filled wave split the key range
+            from pika_h3_flex_b200.ops import split_workspace_bytes
+            split_bytes = split_workspace_bytes(L, Lk, H, mode, bound)
+            ws = torch.empty(max(16, split_bytes), dtype=torch.uint8, device=dev)
 
         if cross:  # keys and values are the text tokens; QK-RMSNorm without rotation
             k = k[:Lk].contiguous()
@@ -279,7 +283,8 @@ def run_ours(args):
                 attn_events.append((e0, e1))
             return out
 
-        launches_per_step = 3 + (1 if bi is not None else 0)
+        # prep (2) + attention (1) [+ plan | + combine of the split last wave]; V is used where it lies
+        launches_per_step = 3 + (1 if bi is not None else 0) + (1 if split_bytes else 0)
     else:
         ua = UlyssesAttention(None, mode, bi, head_groups=args.head_groups)
 

@@ -100,6 +100,13 @@ struct AttnArgs {
   long long wait_ns;
   float fixed_m;           // fixed softmax reference in log2 units (kFixed kernels)
   int heavy_pairs;         // sparse: leading query-tile pairs whose CTAs (of every head) are scheduled first
+  // CTA pairs, dense: pairs numbered split_begin and up (the ones that would form a last, partly empty wave) are
+  // each handled by kv_splits CTA pairs, every one over its share of the key tiles; they leave un-normalised
+  // partial outputs and row sums in `part`, which combine_partials_kernel adds up (the fixed softmax reference
+  // makes partial results of one row directly addable).  kv_splits <= 1: off.
+  int split_begin;
+  int kv_splits;
+  float* part;             // [slot][4 query tiles][128 rows][128 + 1] fp32: O columns, then the row sum
 };
 
 // status word layout: bits [0,8) code, bits [8,32) blockIdx.x (truncated)

@@ -106,6 +106,46 @@ __global__ void build_cluster_plan_kernel(const int32_t* __restrict__ row_ptr, c
   plan_cnt[c] = n;
 }
 
+// Partial results of the split pairs: `part` holds [slot][4 query tiles][128 rows][128] un-normalised output sums,
+// then [slot][4][128] row sums; slot = (pair - split_begin) * kv_splits + share.
+__device__ __forceinline__ long long part_slots(const AttnArgs& a, int n_clusters) {
+  return static_cast<long long>(n_clusters * a.H - a.split_begin) * a.kv_splits;
+}
+// Adds the shares up and writes the rows: one block per (split group of four query tiles, query tile), 16
+// threads per row (8 columns each), 16 rows per pass.
+__global__ void combine_partials_kernel(const AttnArgs args, int n_clusters) {
+  // a wait gave up (now or in an earlier launch on this status word): the shares are incomplete, write nothing
+  if (args.status != nullptr && *reinterpret_cast<volatile int*>(args.status) != 0) return;
+  const int g = blockIdx.x >> 2, tile_in_group = blockIdx.x & 3;
+  const int cidx = args.split_begin + g;
+  const int head = cidx / n_clusters, cl = cidx % n_clusters;
+  const int sub = threadIdx.x & 15, r0 = threadIdx.x >> 4;
+  const float* part_l = args.part + part_slots(args, n_clusters) * 4 * 128 * 128;
+  for (int row = r0; row < 128; row += 16) {
+    const int q_row = (4 * cl + tile_in_group) * kTile + row;
+    if (q_row >= args.Lq) break;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float l = 0.f;
+    for (int s = 0; s < args.kv_splits; ++s) {
+      const long long rix = (static_cast<long long>(g * args.kv_splits + s) * 4 + tile_in_group) * 128 + row;
+      const float4 a = *reinterpret_cast<const float4*>(args.part + rix * 128 + 8 * sub);
+      const float4 b = *reinterpret_cast<const float4*>(args.part + rix * 128 + 8 * sub + 4);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+      l += part_l[rix];
+    }
+    const float inv = 1.0f / l;
+    uint4 w;
+    w.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
+    w.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
+    w.z = pack_bf16x2(acc[4] * inv, acc[5] * inv);
+    w.w = pack_bf16x2(acc[6] * inv, acc[7] * inv);
+    __nv_bfloat16* orow = args.o + static_cast<long long>(q_row) * args.o_stride_l + static_cast<long long>(head) * args.o_stride_h;
+    *reinterpret_cast<uint4*>(orow + 8 * sub) = w;
+    if (sub == 0 && args.lse) args.lse[static_cast<long long>(head) * args.Lq + q_row] = (args.fixed_m + log2f(l)) * 0.6931471805599453f;
+  }
+}
+
 template <bool kFp8, bool kSparse>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -125,7 +165,18 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const int n_clusters = (args.Lq + 4 * kTile - 1) / (4 * kTile);
-  const int cid = blockIdx.x >> 1;
+  int cid = blockIdx.x >> 1;
+  // dense: the pairs from split_begin on share their group of query tiles with kv_splits - 1 others
+  int split = 0, n_splits = 1, part_slot = -1;
+  if constexpr (!kSparse) {
+    if (args.kv_splits > 1 && cid >= args.split_begin) {
+      const int x = cid - args.split_begin;
+      n_splits = args.kv_splits;
+      split = x % n_splits;
+      cid = args.split_begin + x / n_splits;
+      part_slot = x;
+    }
+  }
   // pair -> (head, group of four query tiles): head-major; block-sparse: the groups with long key lists (dense
   // audio rows) of ALL heads first, as in the single-CTA kernel
   int head = cid / n_clusters, cl = cid % n_clusters;
@@ -153,9 +204,14 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   } else {
     n_it = args.n_kv_tiles;
   }
+  int it0 = 0;  // first key tile of this pair's share
+  if constexpr (!kSparse) {
+    it0 = (args.n_kv_tiles * split) / n_splits;
+    n_it = (args.n_kv_tiles * (split + 1)) / n_splits - it0;
+  }
   auto entry_at = [&](int it) -> int {
     if constexpr (kSparse) return plan[it];
-    else return (it << 4) | 15;
+    else return ((it0 + it) << 4) | 15;
   };
   auto stream_needs = [](int e, int t) { return ((e >> (2 * t)) & 3) != 0; };
 
@@ -472,7 +528,23 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const bool row_valid = q_row < args.Lq;
     __nv_bfloat16* orow = args.o + static_cast<long long>(q_row) * args.o_stride_l + static_cast<long long>(head) * args.o_stride_h + 64 * hf;
     const float l_tot = l_sum + lbuf[(hf ^ 1) * 128 + row];
-    if (have && l_tot > 0.0f) {
+    if (!kSparse && part_slot >= 0) {
+      // a share of the key tiles: leave the un-normalised sums for the combining kernel
+      if (have) {
+        const long long rix = (static_cast<long long>(part_slot) * 4 + own_bit) * 128 + row;
+        float* prow = args.part + rix * 128 + 64 * hf;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + 32 * i, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int x = 0; x < 32; x += 4)
+            *reinterpret_cast<uint4*>(prow + 32 * i + x) = make_uint4(o[x], o[x + 1], o[x + 2], o[x + 3]);
+        }
+        if (hf == 0) args.part[part_slots(args, n_clusters) * 4 * 128 * 128 + rix] = l_tot;
+      }
+    } else if (have && l_tot > 0.0f) {
       const float inv = 1.0f / l_tot;
 #pragma unroll
       for (int i = 0; i < 2; ++i) {

@@ -116,6 +116,53 @@ bool pair_kernel_enabled() {
   return on;
 }
 
+// ---- dense launches on CTA pairs: the last, partly filled wave --------------------------------------------
+// One pair of CTAs runs per pair of SMs.  When the number of pairs is not a multiple of that, the pairs of the
+// last wave are each replaced by S pairs that walk 1/S of the key tiles and leave partial sums in the caller's
+// workspace (see AttnArgs::split_begin); a small kernel adds them up.  S minimises the length of that tail.
+struct SplitPlan {
+  int split_begin = 0, kv_splits = 1, groups = 0;
+  size_t bytes = 0;
+};
+
+int sm_count_of_current_device() {
+  static int cached[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+SplitPlan plan_split(int64_t Lq, int64_t Lk, int64_t H) {
+  SplitPlan sp;
+  const int sms = sm_count_of_current_device();
+  const int64_t wave = sms / 2, total = (Lq + 511) / 512 * H, n_kv = (Lk + 127) / 128;
+  sp.split_begin = static_cast<int>(total);
+  if (wave <= 0 || total > (1 << 28)) return sp;
+  const int64_t rest = total % wave;
+  if (rest == 0) return sp;
+  const double eps = 4.5 / static_cast<double>(n_kv);  // set-up, partial store and combine, relative to a full pair
+  double best = 1.0 + eps;
+  int best_s = 1;
+  for (int64_t s = 2; s <= 16 && s * 4 <= n_kv && rest * s <= 4 * wave; ++s) {
+    const double t = static_cast<double>((rest * s + wave - 1) / wave) * (1.0 / static_cast<double>(s) + eps);
+    if (t < best - 0.02) {
+      best = t;
+      best_s = static_cast<int>(s);
+    }
+  }
+  if (best_s > 1) {
+    sp.split_begin = static_cast<int>(total - rest);
+    sp.kv_splits = best_s;
+    sp.groups = static_cast<int>(rest);
+    sp.bytes = static_cast<size_t>(rest) * best_s * (4 * 128 * 128 + 4 * 128) * sizeof(float);
+  }
+  return sp;
+}
+
 template <bool kFp8, bool kSparse = false>
 int32_t launch_attn_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a, cudaStream_t st) {
   static std::once_flag once[kMaxDevices];
@@ -132,9 +179,17 @@ int32_t launch_attn_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUt
   });
   if (attr_err[dev] != cudaSuccess) return H3A_ERR_LAUNCH;
   const unsigned n_clusters = static_cast<unsigned>((a.Lq + 511) / 512);
-  const unsigned grid = 2u * n_clusters * static_cast<unsigned>(a.H);  // the kernel carries its cluster shape (2,1,1)
-  h3a::attn_fwd_pair_kernel<kFp8, kSparse><<<grid, h3a::kPairThreads, h3a::kPairSmemBytes, st>>>(mq, mk, mv, a);
-  return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
+  unsigned pairs = n_clusters * static_cast<unsigned>(a.H);
+  const bool split = !kSparse && a.kv_splits > 1;
+  if (split) pairs = static_cast<unsigned>(a.split_begin) + (pairs - static_cast<unsigned>(a.split_begin)) * static_cast<unsigned>(a.kv_splits);
+  h3a::attn_fwd_pair_kernel<kFp8, kSparse><<<2u * pairs, h3a::kPairThreads, h3a::kPairSmemBytes, st>>>(mq, mk, mv, a);  // cluster shape (2,1,1) is the kernel's
+  if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
+  if (split) {
+    const unsigned groups = n_clusters * static_cast<unsigned>(a.H) - static_cast<unsigned>(a.split_begin);
+    h3a::combine_partials_kernel<<<4u * groups, 256, 0, st>>>(a, static_cast<int>(n_clusters));
+    if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
+  }
+  return H3A_OK;
 }
 
 // ---- static scratch for h3a_attn_fwd_sparse_static -------------------------------------------------------
@@ -190,7 +245,14 @@ const char* h3a_status_string(int32_t s) {
 
 int32_t h3a_attn_workspace_bytes(const h3a_attn_params* p, size_t* bytes) {
   if (!p || !bytes) return H3A_ERR_ARG;
-  *bytes = (p->mode == H3A_MODE_BLOCK_SPARSE) ? sparse_workspace_bytes(p) : 0;
+  if (p->mode == H3A_MODE_BLOCK_SPARSE) {
+    *bytes = sparse_workspace_bytes(p);
+  } else {
+    // optional: partial sums of the split last wave (dense launches with a logit bound); without it the launch
+    // simply does not split
+    const bool fixed = p->logit_bound > 0.f && p->logit_bound <= 30.f;
+    *bytes = (fixed && pair_kernel_enabled() && p->Lq > 0 && p->Lk > 0 && p->H > 0) ? plan_split(p->Lq, p->Lk, p->H).bytes : 0;
+  }
   return H3A_OK;
 }
 
@@ -257,6 +319,16 @@ int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream) {
     return fixed ? launch_attn<false, true, true>(mq, mk, mv, a, st) : launch_attn<false, true, false>(mq, mk, mv, a, st);
   }
   if (fixed && pair_kernel_enabled()) {
+    a.split_begin = static_cast<int>((p->Lq + 511) / 512 * p->H);
+    a.kv_splits = 1;
+    if (p->workspace && aligned16(p->workspace)) {
+      const SplitPlan sp = plan_split(p->Lq, p->Lk, p->H);
+      if (sp.kv_splits > 1 && p->workspace_bytes >= sp.bytes) {
+        a.split_begin = sp.split_begin;
+        a.kv_splits = sp.kv_splits;
+        a.part = static_cast<float*>(p->workspace);
+      }
+    }
     // CTA pairs: each CTA stages 32-key boxes of K (its share of every 64-key MMA group) and 64 columns of V
     if ((rc = make_map(&mk, p->k, fp8, p->Lk, p->H, p->k_stride_l, p->k_stride_h, h3a::kPairKBoxRows)) != H3A_OK) return rc;
     return fp8 ? launch_attn_pair<true>(mq, mk, mv, a, st) : launch_attn_pair<false>(mq, mk, mv, a, st);

@@ -240,8 +240,29 @@ def attn_fwd(
         p.status_word = status_word.data_ptr()
     p.wait_limit_ns = int(wait_limit_ns)
     p.logit_bound = float(logit_bound)
+    if mode != _lib.MODE_BLOCK_SPARSE and logit_bound > 0:
+        # optional scratch: lets the launch split the key range for the CTAs of its last, partly filled wave
+        need = C.c_size_t(0)
+        check(lib.h3a_attn_workspace_bytes(C.byref(p), C.byref(need)), "h3a_attn_workspace_bytes")
+        if need.value:
+            if workspace is None:  # a caller's own workspace is passed as it is: one that is too small means "do not split"
+                workspace = torch.empty(need.value, dtype=torch.uint8, device=q.device)
+            p.workspace, p.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
     check(lib.h3a_attn_fwd(C.byref(p), _stream()), "h3a_attn_fwd")
     return (out, lse) if return_lse else out
+
+
+def split_workspace_bytes(Lq: int, Lk: int, H: int, mode: int = _lib.MODE_DENSE_BF16, logit_bound: float = 0.0) -> int:
+    """Bytes of optional scratch with which a dense / FP8-QK launch of this shape splits the key range for the CTA
+    pairs of its last, partly filled wave on the current device (0: such a launch does not split).  ``attn_fwd``
+    allocates it per call when no ``workspace`` is given; callers in a loop can allocate it once."""
+    if mode == _lib.MODE_BLOCK_SPARSE or logit_bound <= 0:
+        return 0
+    p = AttnParams()
+    p.Lq, p.Lk, p.H, p.d, p.B, p.mode, p.logit_bound = int(Lq), int(Lk), int(H), HEAD_DIM, 1, int(mode), float(logit_bound)
+    need = C.c_size_t(0)
+    check(_lib.load().h3a_attn_workspace_bytes(C.byref(p), C.byref(need)), "h3a_attn_workspace_bytes")
+    return int(need.value)
 
 
 def static_scratch_capacity() -> int:

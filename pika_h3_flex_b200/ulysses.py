@@ -192,19 +192,37 @@ class UlyssesAttention:
         bound = ops.normed_logit_bound(fp8=(mode == _lib.MODE_FP8_QK))  # operands come from the unit-weight prep
         return ops.attn_fwd(q, k, v, mode, q_scale, k_scale, block_index, out=out, logit_bound=bound)
 
+    @staticmethod
+    def _waves(n_heads: int, L: int, sms: int) -> float:
+        """Estimated duration of one dense attention launch over ``n_heads`` heads, in units of one CTA pair's full
+        walk over the keys: whole waves of pairs (one pair per two SMs) plus the last, partly filled wave, which the
+        library shortens by splitting the key range (same model as the library's own choice of the split)."""
+        wave = max(1, sms // 2)
+        total = (L + 511) // 512 * n_heads
+        n_kv = (L + 127) // 128
+        full, rest = divmod(total, wave)
+        if rest == 0:
+            return float(full)
+        eps = 4.5 / n_kv
+        tail = 1.0 + eps
+        s = 2
+        while s <= 16 and s * 4 <= n_kv and rest * s <= 4 * wave:
+            tail = min(tail, -(-rest * s // wave) * (1.0 / s + eps))
+            s += 1
+        return full + tail
+
     def _head_slot_groups(self, hp: int, L: int, like: torch.Tensor):
-        """Split the ``hp`` local head slots into at most two groups.  On a GPU the cut is placed so that the two
-        attention launches together need no more waves of CTAs (one CTA per 256 query rows and head, one CTA
-        per SM at a time) than a single launch would; if no cut achieves that, one group is used."""
+        """Split the ``hp`` local head slots into at most two groups, so that one group's exchanges overlap the
+        other's attention.  On a GPU the cut is placed where the two attention launches together are estimated to
+        take no longer (within 2 %) than a single launch would; if no cut achieves that, one group is used."""
         if self.head_groups < 2 or hp < 2:
             return [range(hp)]
         if not like.is_cuda:
             return [range(0, hp // 2), range(hp // 2, hp)]
         sms = torch.cuda.get_device_properties(like.device).multi_processor_count
-        nq = 2 * ((L + 511) // 512)  # CTAs per head: pairs of CTAs, each pair 512 query rows
-        waves = lambda n: -(-n * nq // sms)
-        best = min(range(1, hp), key=lambda c: (waves(c) + waves(hp - c), abs(c - hp // 2)))
-        if waves(best) + waves(hp - best) > waves(hp):
+        cost = lambda c: self._waves(c, L, sms) + self._waves(hp - c, L, sms)
+        best = min(range(1, hp), key=lambda c: (round(cost(c), 3), abs(c - hp // 2)))
+        if cost(best) > 1.02 * self._waves(hp, L, sms):
             return [range(hp)]
         return [range(0, best), range(best, hp)]
 

@@ -573,3 +573,38 @@ def test_pair_kernel_block_sparse_structures(h, rows):
     assert bool((first.float().cpu()[empty] == 0).all())
     assert bool(torch.isinf(lse.cpu()[:, empty]).all())
     assert float((lse.cpu().t()[~empty] - ref_lse[~empty]).abs().max()) < 2e-3
+
+
+@pytest.mark.parametrize("L,Lk,H,fp8", [(1000, 1500, 3, False), (4096, 4096, 4, False), (2100, 8192, 5, False), (1536, 4096, 3, True)])
+def test_pair_kernel_split_last_wave(h, L, Lk, H, fp8):
+    """With the optional workspace the pairs of the last, partly filled wave each walk a share of the key tiles and a
+    second kernel adds the shares; without it nothing is split.  Both must give the oracle's rows (and each other's,
+    up to the order of the additions)."""
+    from pika_h3_flex_b200 import _lib
+    import ctypes as C
+
+    q, k, v = bf16_inputs(L, H, 1200 + L, Lk)
+    if fp8:
+        qq, sq = O.quantize_e4m3_blocks(q.float())
+        kq, sk = O.quantize_e4m3_blocks(k.float())
+        ref, ref_lse = O.attention(O.dequantize_blocks(qq, sq), O.dequantize_blocks(kq, sk), v.float(), return_lse=True)
+        to_dev = lambda x: dev(x.to(torch.float8_e4m3fn).view(torch.uint8).permute(1, 0, 2).contiguous()).permute(1, 0, 2)
+        args = (to_dev(qq), to_dev(kq), dev(v), h.MODE_FP8_QK, dev(sq), dev(sk))
+    else:
+        ref, ref_lse = O.attention(q.float(), k.float(), v.float(), return_lse=True)
+        args = (dev(q), dev(k), dev(v))
+    # the size query says whether this shape splits on this device
+    p = _lib.AttnParams()
+    p.Lq, p.Lk, p.H, p.d, p.B, p.mode, p.logit_bound = L, Lk, H, 128, 1, int(h.MODE_FP8_QK if fp8 else h.MODE_DENSE_BF16), PAIR_BOUND
+    need = C.c_size_t(0)
+    assert _lib.load().h3a_attn_workspace_bytes(C.byref(p), C.byref(need)) == 0
+    assert need.value > 0, "these shapes are chosen so that the last wave is split on a 148-SM device"
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    split, lse = h.attn_fwd(*args, logit_bound=PAIR_BOUND, return_lse=True, status_word=st)  # wrapper supplies the workspace
+    assert h.read_status(st) == 0
+    small = torch.empty(16, dtype=torch.uint8, device="cuda")  # too small: the launch must not split
+    whole = h.attn_fwd(*args, logit_bound=PAIR_BOUND, workspace=small)
+    check(split, ref)
+    check(whole, ref)
+    assert float((split.float() - whole.float()).abs().max()) <= 2e-3
+    assert float((lse.cpu().t() - ref_lse).abs().max()) < 2e-3
