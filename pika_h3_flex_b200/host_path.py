@@ -27,19 +27,37 @@ def _copy_heads(dst: torch.Tensor, src: torch.Tensor, h0: int, h1: int, to_host:
     )
 
 
+def default_head_groups(H: int, copy_to_compute: float = 0.75) -> list:
+    """Head groups for the pipeline.  Only the first group's copy-in and the last group's copy-out are exposed, so
+    both are small; in between a group is as large as its copy-in can be while still finishing before the groups
+    ahead of it have been computed.  ``copy_to_compute`` = time to bring one head's Q, K, V in / time to compute
+    one head (0.75 measured for dense bf16 at the 480p-like length over PCIe 5 x16); with copy time c per head the
+    condition  c * n_g <= c * first + (c / copy_to_compute - c) * heads_before_g  gives the growth rule below."""
+    first = max(1, H // 20)
+    last = max(1, H // 16) if H > 2 else 0
+    if first + last >= H:
+        return [H]
+    groups, done = [first], first
+    gain = max(0.0, 1.0 / max(copy_to_compute, 1e-3) - 1.0)
+    while done < H - last:
+        n = max(1, min(int(first + gain * done), H - last - done))
+        groups.append(n)
+        done += n
+    if H - done > 0:
+        groups.append(H - done)
+    return groups
+
+
 class HostJointAttention:
     """``out_host = HostJointAttention(L, H)(q_host, k_host, v_host, rope, out_host)`` with pinned ``[L, H, 128]``
     bf16 host tensors.  Device staging buffers and streams are created once and reused."""
 
     def __init__(self, L: int, H: int, mode: int = _lib.MODE_DENSE_BF16, block_index: Optional[ops.BlockIndex] = None,
-                 head_groups: Optional[Sequence[int]] = None, device=None):
+                 head_groups: Optional[Sequence[int]] = None, device=None, copy_to_compute: float = 0.75):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.L, self.H, self.mode, self.block_index = L, H, mode, block_index
-        if head_groups is None:  # a small first group shortens the exposed first transfer
-            first = max(1, H // 8)
-            rest = H - first
-            n = max(1, min(3, rest))
-            head_groups = [first] + [rest // n + (1 if i < rest % n else 0) for i in range(n)] if rest else [first]
+        if head_groups is None:
+            head_groups = default_head_groups(H, copy_to_compute)
         if sum(head_groups) != H:
             raise ValueError("head_groups must sum to H")
         self.groups = list(head_groups)
