@@ -70,10 +70,16 @@ class B200AttnProcessor:
     block_index   ``ops.BlockIndex`` on the device (``block_sparse`` only; self-attention only)
     rope_half     rotary pairs ``(j, j+64)`` instead of ``(2j, 2j+1)``
     qk_norm       apply per-head RMSNorm even when the module has no ``norm_q`` / ``norm_k`` (unit weights)
+    group         a ``torch.distributed`` process group (NCCL, one process per GPU): Ulysses sequence parallelism.
+                  ``hidden_states`` is then this rank's shard ``[1, S/P, D]`` of the packed sequence (rank r holds
+                  tokens ``[r*S/P, (r+1)*S/P)``; rotary inputs are the rows of the same shard) and so is the result.
+                  The projections stay token-local; the exchange of Q runs under the K projection and that of K
+                  under the V projection.  Cross-attention needs no exchange (keys and values are replicated).
     """
 
     def __init__(self, mode: str = "dense_bf16", block_index: Optional[ops.BlockIndex] = None, rope_half: bool = False,
-                 rope_split=ops.ROPE_SPLIT, rope_theta: float = 10000.0, qk_norm: bool = True, eps: float = 1e-6):
+                 rope_split=ops.ROPE_SPLIT, rope_theta: float = 10000.0, qk_norm: bool = True, eps: float = 1e-6,
+                 group=None, sequence_parallel: bool = False):
         if mode not in MODES:
             raise ValueError(f"mode must be one of {sorted(MODES)}")
         if mode == "block_sparse" and block_index is None:
@@ -88,6 +94,11 @@ class B200AttnProcessor:
         self.eps = eps
         self._rope_cache = RopeCache()
         self._bounds = {}
+        self._ulysses = None
+        if group is not None or sequence_parallel:  # sequence_parallel=True with group=None: the default group
+            from .ulysses import UlyssesAttention
+
+            self._ulysses = UlyssesAttention(group, MODES[mode], block_index)
 
     # ---- rotary information from whatever the caller passes
     def _rope(self, S: int, image_rotary_emb, kwargs) -> Optional[torch.Tensor]:
@@ -120,23 +131,43 @@ class B200AttnProcessor:
         to = dict(dtype=torch.bfloat16)
         return (q.to(**to).view(-1, H, ops.HEAD_DIM), k.to(**to).view(-1, H, ops.HEAD_DIM), v.to(**to).view(-1, H, ops.HEAD_DIM))
 
-    def attention(self, attn, q, k, v, rope, cross: bool):
-        """Norm + rotation + attention on ``[L, H, 128]`` projections (one GPU)."""
+    def _norm_and_bound(self, attn, mode):
         qw, qeps = _norm_params(getattr(attn, "norm_q", None))
         kw, keps = _norm_params(getattr(attn, "norm_k", None))
         if not self.qk_norm and qw is None and kw is None:
             raise NotImplementedError("the fused Q/K preparation always normalises; qk_norm=False needs norm-free modules")
         eps = qeps or keps or self.eps
-        mode = MODES[self.mode]
-        bi = self.block_index
-        if cross and mode == _lib.MODE_BLOCK_SPARSE:
-            mode, bi = _lib.MODE_DENSE_BF16, None  # the block index describes the joint self-attention only
         # the logit bound depends only on the (static) norm weights: read them once per module
         key = (id(attn), mode == _lib.MODE_FP8_QK)
         bound = self._bounds.get(key)
         if bound is None:
             bound = self._bounds[key] = ops.normed_logit_bound(qw, kw, 0.0, mode == _lib.MODE_FP8_QK)
+        return qw, kw, eps, bound
+
+    def attention(self, attn, q, k, v, rope, cross: bool):
+        """Norm + rotation + attention on ``[L, H, 128]`` projections (one GPU)."""
+        mode = MODES[self.mode]
+        bi = self.block_index
+        if cross and mode == _lib.MODE_BLOCK_SPARSE:
+            mode, bi = _lib.MODE_DENSE_BF16, None  # the block index describes the joint self-attention only
+        qw, kw, eps, bound = self._norm_and_bound(attn, mode)
         return ops.joint_attention(q, k, v, None if cross else rope, mode, bi, qw, kw, eps, self.rope_half, logit_bound=bound)
+
+    def attention_sequence_parallel(self, attn, hidden_states, rope):
+        """Self-attention with the sequence sharded over the group: each projection is computed when the previous
+        tensor's exchange is already on its way."""
+        H = attn.heads
+        qw, kw, eps, bound = self._norm_and_bound(attn, MODES[self.mode])
+
+        def proj(lin):
+            def f():
+                y = lin(hidden_states)
+                if y.shape[-1] != H * ops.HEAD_DIM:
+                    raise ValueError(f"inner dim {y.shape[-1]} != heads {H} x 128")
+                return y.to(torch.bfloat16).view(-1, H, ops.HEAD_DIM)
+            return f
+
+        return self._ulysses.run(proj(attn.to_q), proj(attn.to_k), proj(attn.to_v), rope, qw, kw, eps, self.rope_half, bound)
 
     def __call__(self, attn, hidden_states: torch.Tensor, encoder_hidden_states: Optional[torch.Tensor] = None,
                  attention_mask: Optional[torch.Tensor] = None, image_rotary_emb=None, **kwargs) -> torch.Tensor:
@@ -148,9 +179,12 @@ class B200AttnProcessor:
             raise RuntimeError("B200AttnProcessor needs CUDA tensors (there is no CPU path)")
         S = hidden_states.shape[1]
         cross = encoder_hidden_states is not None
-        q, k, v = self.project(attn, hidden_states, encoder_hidden_states)
         rope = None if cross else self._rope(S, image_rotary_emb, kwargs)
-        o = self.attention(attn, q, k, v, rope, cross)
+        if self._ulysses is not None and not cross:
+            o = self.attention_sequence_parallel(attn, hidden_states, rope)
+        else:
+            q, k, v = self.project(attn, hidden_states, encoder_hidden_states)
+            o = self.attention(attn, q, k, v, rope, cross)
         o = o.reshape(1, S, -1).to(hidden_states.dtype)
         to_out = attn.to_out
         o = to_out[0](o)

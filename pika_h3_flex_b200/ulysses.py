@@ -147,11 +147,12 @@ def head_to_seq(o_hm: torch.Tensor, group=None, async_op: bool = False, out: Opt
     return out, _exchange(send, recv, group, async_op)
 
 
-def scales_seq_to_head(s: torch.Tensor, group=None) -> torch.Tensor:
+def scales_seq_to_head(s: torch.Tensor, group=None, async_op: bool = False):
     """FP8 block scales ``[Hp, nb_local]`` -> ``[Hp/P, P*nb_local]`` (needs Ls % 128 == 0 so that blocks do
-    not straddle ranks)."""
-    out, _ = seq_to_head(s[:, :, None].contiguous(), group)
-    return out[:, :, 0].contiguous()
+    not straddle ranks).  With ``async_op`` returns ``(fetch, requests)``: call ``fetch()`` after waiting."""
+    out, reqs = seq_to_head(s[:, :, None].contiguous(), group, async_op)
+    fetch = lambda: out[:, :, 0].contiguous()
+    return (fetch, reqs) if async_op else fetch()
 
 
 def _pad_heads_hm(x_hm: torch.Tensor, Hp: int) -> torch.Tensor:
@@ -163,9 +164,11 @@ def _pad_heads_hm(x_hm: torch.Tensor, Hp: int) -> torch.Tensor:
 
 class UlyssesAttention:
     """Sequence-parallel joint attention.  ``__call__(q, k, v, rope)`` takes this rank's ``[L/P, H, 128]``
-    bf16 projections and rotary table rows and returns this rank's ``[L/P, H, 128]`` output.
+    bf16 projections and rotary table rows and returns this rank's ``[L/P, H, 128]`` output.  ``run`` takes the
+    three projections as callables instead and starts each tensor's exchange as soon as that tensor exists, so the
+    exchange of Q runs under the K projection and the exchange of K under the V projection.
 
-    ``prep_fn(q, k, q_rope, k_rope, fp8) -> (q', k', q_scale, k_scale)`` and
+    ``prep_fn(q, k, q_rope, k_rope, fp8) -> (q', k', q_scale, k_scale)`` (either of q, k may be None) and
     ``attn_fn(q, k, v, mode, q_scale, k_scale, block_index)`` default to the CUDA library; the CPU tests
     inject host stand-ins to exercise the reshard logic with gloo ranks.
     """
@@ -177,20 +180,9 @@ class UlyssesAttention:
         self.head_groups = head_groups
         self.mode = mode
         self.block_index = block_index
-        self.prep_fn = prep_fn or self._cuda_prep
-        self.attn_fn = attn_fn or self._cuda_attn
+        self.prep_fn = prep_fn
+        self.attn_fn = attn_fn
         self.to_head_major = to_head_major or (lambda v: v.permute(1, 0, 2).contiguous())
-
-    @staticmethod
-    def _cuda_prep(q, k, q_rope, k_rope, fp8):
-        return ops.qk_prep(q, k, q_rope, k_rope, fp8=fp8)
-
-    @staticmethod
-    def _cuda_attn(q, k, v, mode, q_scale, k_scale, block_index):
-        # head-major output so that the return exchange sends contiguous [L/P, 128] blocks without a copy
-        out = torch.empty(q.shape[1], q.shape[0], ops.HEAD_DIM, dtype=torch.bfloat16, device=q.device).permute(1, 0, 2)
-        bound = ops.normed_logit_bound(fp8=(mode == _lib.MODE_FP8_QK))  # operands come from the unit-weight prep
-        return ops.attn_fwd(q, k, v, mode, q_scale, k_scale, block_index, out=out, logit_bound=bound)
 
     @staticmethod
     def _waves(n_heads: int, L: int, sms: int) -> float:
@@ -226,43 +218,75 @@ class UlyssesAttention:
             return [range(hp)]
         return [range(0, best), range(best, hp)]
 
-    def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rope: Optional[torch.Tensor]) -> torch.Tensor:
+    def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rope: Optional[torch.Tensor], **kw) -> torch.Tensor:
+        return self.run(lambda: q, lambda: k, lambda: v, rope, **kw)
+
+    def run(self, q_fn: Callable, k_fn: Callable, v_fn: Callable, rope: Optional[torch.Tensor],
+            q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
+            rope_half: bool = False, logit_bound: Optional[float] = None) -> torch.Tensor:
+        """``q_fn() / k_fn() / v_fn()`` return this rank's ``[L/P, H, 128]`` bf16 projections; they are called in
+        that order, each after the previous tensor's exchange has been started."""
         world = dist.get_world_size(self.group)
-        Ls, H, _ = q.shape
         fp8 = self.mode == _lib.MODE_FP8_QK
+
+        def prep(x, which):  # token-local work first: the wire then carries final operands
+            a, b = (x, None) if which == 0 else (None, x)
+            ra, rb = (rope, None) if which == 0 else (None, rope)
+            if self.prep_fn is not None:
+                r = self.prep_fn(a, b, ra, rb, fp8)
+            else:
+                r = ops.qk_prep(a, b, ra, rb, q_weight, k_weight, eps, fp8, rope_half)
+            return (r[0], r[2]) if which == 0 else (r[1], r[3])
+
+        q = q_fn()
+        Ls, H, _ = q.shape
         if fp8 and Ls % ops.TILE:
             raise ValueError("FP8 mode under Ulysses needs the local sequence length to be a multiple of 128")
         Hp = padded_heads(H, world)
         hp = Hp // world
-        # token-local work first: the wire then carries final operands
-        qp, kp, qs, ks = self.prep_fn(q, k, rope, rope, fp8)
-        # prepared tensors are logical [Ls, H, C] views of head-major storage
-        q_hm = _pad_heads_hm(qp.permute(1, 0, 2).contiguous(), Hp)
-        k_hm = _pad_heads_hm(kp.permute(1, 0, 2).contiguous(), Hp)
-        v_hm = _pad_heads_hm(self.to_head_major(v), Hp)
-        qsh = ksh = None
-        if fp8:
-            qsh = scales_seq_to_head(_pad_heads_hm(qs, Hp), self.group)
-            ksh = scales_seq_to_head(_pad_heads_hm(ks, Hp), self.group)
         # The local head slots are handled in groups: while one group is in attention the next group's operands
         # are arriving and the previous group's output is leaving.
         groups = self._head_slot_groups(hp, world * Ls, q)
-        qh = kh = vh = None
-        inbound = []
-        for sl in groups:
-            qh, r1 = seq_to_head(q_hm, self.group, True, qh, sl)
-            kh, r2 = seq_to_head(k_hm, self.group, True, kh, sl)
-            vh, r3 = seq_to_head(v_hm, self.group, True, vh, sl)
-            inbound.append(r1 + r2 + r3)
+        inbound = [[] for _ in groups]
+        scale_fetch = [None, None]
+        heads = [None, None, None]
+        for which, fn in enumerate((None, k_fn, v_fn)):
+            x = q if which == 0 else fn()
+            if tuple(x.shape) != (Ls, H, ops.HEAD_DIM):
+                raise ValueError("q, k, v must be [L/P, H, 128] shards of the same shape")
+            if which < 2:
+                xp, xs = prep(x, which)
+                x_hm = _pad_heads_hm(xp.permute(1, 0, 2).contiguous(), Hp)  # prepared tensors are views of head-major storage
+            else:
+                xs = None
+                x_hm = _pad_heads_hm(self.to_head_major(x), Hp)
+            for gi, sl in enumerate(groups):
+                heads[which], r = seq_to_head(x_hm, self.group, True, heads[which], sl)
+                inbound[gi] += r
+            if fp8 and which < 2:
+                scale_fetch[which], r = scales_seq_to_head(_pad_heads_hm(xs, Hp), self.group, True)
+                inbound[0] += r
+        qh, kh, vh = heads
+        qsh = ksh = None
+        if logit_bound is None and self.attn_fn is None:
+            logit_bound = ops.normed_logit_bound(q_weight, k_weight, 0.0, fp8)
         o_hm = None
         outbound = []
-        for sl, reqs in zip(groups, inbound):
+        for gi, (sl, reqs) in enumerate(zip(groups, inbound)):
             for r in reqs:
                 r.wait()
+            if fp8 and gi == 0:
+                qsh, ksh = scale_fetch[0](), scale_fetch[1]()
             j0, j1 = sl.start, sl.stop
-            oh = self.attn_fn(qh[j0:j1].permute(1, 0, 2), kh[j0:j1].permute(1, 0, 2), vh[j0:j1].permute(1, 0, 2), self.mode,
-                              None if qsh is None else qsh[j0:j1].contiguous(), None if ksh is None else ksh[j0:j1].contiguous(),
-                              self.block_index)
+            qg, kg, vg = (t[j0:j1].permute(1, 0, 2) for t in (qh, kh, vh))
+            sq = None if qsh is None else qsh[j0:j1].contiguous()
+            sk = None if ksh is None else ksh[j0:j1].contiguous()
+            if self.attn_fn is not None:
+                oh = self.attn_fn(qg, kg, vg, self.mode, sq, sk, self.block_index)
+            else:
+                # head-major output so that the return exchange sends contiguous blocks without a copy
+                oh = torch.empty(j1 - j0, qg.shape[0], ops.HEAD_DIM, dtype=torch.bfloat16, device=qg.device).permute(1, 0, 2)
+                ops.attn_fwd(qg, kg, vg, self.mode, sq, sk, self.block_index, out=oh, logit_bound=logit_bound)
             o_hm, r = head_to_seq(oh.permute(1, 0, 2).contiguous(), self.group, True, o_hm, sl, hp)
             outbound += r
         for r in outbound:

@@ -131,3 +131,79 @@ def test_processor_rejects_what_it_cannot_do(setup):
         proc(attn, x.cpu(), position_ids=pos)
     with pytest.raises(ValueError):
         B200AttnProcessor("block_sparse")
+
+
+_SP_CHILD = r"""
+import os, sys, importlib.util, torch, torch.distributed as dist
+sys.path.insert(0, {root!r})
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+spec = importlib.util.spec_from_file_location("stubs", {this!r})
+stubs = importlib.util.module_from_spec(spec)
+spec.loader.exec_module(stubs)
+from oracle import oracle as O
+from pika_h3_flex_b200 import build_block_index
+from pika_h3_flex_b200.processor import B200AttnProcessor
+torch.manual_seed(3)
+torch.backends.cuda.matmul.allow_tf32 = False
+attn = stubs.StubAttention(256, 3).cuda().bfloat16()      # 3 heads on 2 ranks: padded to 4
+grid, n_audio = (4, 8, 8), 256
+pos = O.make_positions(grid, n_audio)
+S = pos.shape[0]
+x = torch.randn(1, S, 256, device="cuda").bfloat16()
+Ss = S // world
+sl = slice(rank * Ss, (rank + 1) * Ss)
+bi = build_block_index(grid, n_audio, (1, 2, 2)).to("cuda")
+ok = True
+with torch.no_grad():
+    for mode, idx in (("dense_bf16", None), ("fp8_qk", None), ("block_sparse", bi)):
+        whole = B200AttnProcessor(mode, idx)(attn, x, position_ids=pos.cuda())
+        shard = B200AttnProcessor(mode, idx, sequence_parallel=True)(attn, x[:, sl].contiguous(), position_ids=pos[sl].cuda())
+        err = float((shard.float() - whole[:, sl].float()).abs().max())
+        print(rank, mode, err, flush=True)
+        ok = ok and tuple(shard.shape) == (1, Ss, 256) and err < (6e-2 if mode == "fp8_qk" else 2e-2)
+    text = torch.randn(1, 77, 256, device="cuda").bfloat16()
+    c_whole = B200AttnProcessor()(attn, x, encoder_hidden_states=text)
+    c_shard = B200AttnProcessor(sequence_parallel=True)(attn, x[:, sl].contiguous(), encoder_hidden_states=text)
+    ok = ok and float((c_shard.float() - c_whole[:, sl].float()).abs().max()) < 2e-2
+flag = torch.tensor([1 if ok else 0], device="cuda")
+dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+dist.destroy_process_group()
+sys.exit(0 if int(flag.item()) == 1 else 1)
+"""
+
+
+def test_sequence_parallel_processor_matches_single_gpu(tmp_path):
+    """Two ranks as child processes (NCCL): the processor with ``sequence_parallel=True`` on each rank's shard of
+    the packed sequence returns that shard of what the single-GPU processor returns (all three modes, padded
+    heads, cross-attention without an exchange)."""
+    import os
+    import socket
+    import subprocess
+    import sys
+
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs 2 GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "child.py"
+    script.write_text(_SP_CHILD.format(root=root, this=os.path.abspath(__file__)))
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
+    outs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o, _ = p.communicate()
+        outs.append(o.decode(errors="replace"))
+    assert all(p.returncode == 0 for p in procs), "\n".join(x[-2000:] for x in outs)

@@ -23,13 +23,19 @@ def _free_port():
 
 
 def _cpu_prep(q, k, q_rope, k_rope, fp8):
-    cos, sin = (q_rope[..., 0].double(), q_rope[..., 1].double()) if q_rope is not None else (None, None)
-    qp, kp = (O.qk_prep(q, k, cos, sin) if cos is not None else (O.rms_norm(q), O.rms_norm(k)))
-    if not fp8:
-        return qp, kp, None, None
-    qq, sq = O.quantize_e4m3_blocks(qp)
-    kq, sk = O.quantize_e4m3_blocks(kp)
-    return qq, kq, sq, sk
+    """Host stand-in for the CUDA preparation; either of q, k may be None (one tensor at a time)."""
+    outs = []
+    for x, rope in ((q, q_rope), (k, k_rope)):
+        if x is None:
+            outs.append((None, None))
+            continue
+        if rope is not None:
+            cos, sin = rope[..., 0].double(), rope[..., 1].double()
+            xp = O.qk_prep(x, x, cos, sin)[0]
+        else:
+            xp = O.rms_norm(x)
+        outs.append(O.quantize_e4m3_blocks(xp) if fp8 else (xp, None))
+    return outs[0][0], outs[1][0], outs[0][1], outs[1][1]
 
 
 def _cpu_attn(q, k, v, mode, q_scale, k_scale, block_index):
