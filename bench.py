@@ -316,12 +316,22 @@ def run_ours(args):
     e_stop.record()
     barrier()
     elapsed_ms = e_start.elapsed_time(e_stop)
-    clocks = sampler.stop() if rank == 0 else None
     if world > 1:
         t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed_ms = float(t.item())
     ms_per_step = elapsed_ms / args.steps
+    # nvidia-smi delivers a sample every 200 ms: a timed region shorter than about a second holds too few of them,
+    # so the same steps keep running (untimed, every rank alike) until the record covers 1.5 s of this load
+    extra_steps = 0
+    if elapsed_ms < 1000.0:
+        extra_steps = int(1500.0 / max(ms_per_step, 1e-3)) + 1
+        for _ in range(extra_steps):
+            step()
+        barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None and extra_steps:
+        clocks["note"] = f"timed region {elapsed_ms:.0f} ms: sampling continued over {extra_steps} identical untimed steps"
     value = flops / (ms_per_step * 1e-3) / 1e12
     if h3.read_status(status) != 0:
         raise SystemExit(f"device wait gave up: status 0x{h3.read_status(status):x}")

@@ -209,6 +209,8 @@ class UlyssesAttention:
         take no longer (within 2 %) than a single launch would; if no cut achieves that, one group is used."""
         if self.head_groups < 2 or hp < 2:
             return [range(hp)]
+        if like.is_cuda and hp < 8:
+            return [range(hp)]  # measured at 5 heads per rank (8 GPUs): a second launch costs more than the overlap gains
         if not like.is_cuda:
             return [range(0, hp // 2), range(hp // 2, hp)]
         sms = torch.cuda.get_device_properties(like.device).multi_processor_count
