@@ -342,7 +342,9 @@ def run_ours(args):
         attn_ms = sum(a.elapsed_time(b) for a, b in attn_events) / len(attn_events)
         burst, sustained, src = measured_peaks()
         achieved = flops / (attn_ms * 1e-3) / 1e12
-        pair = mode_name in ("dense_bf16", "fp8_qk", "cross_bf16") and not args.online_max and os.environ.get("H3A_PAIR", "1")[:1] != "0"
+        # which kernel the library picks: CTA pairs with a logit bound, from 16 key tiles and (sparse) 12 % density up
+        pair = (not args.online_max and os.environ.get("H3A_PAIR", "1")[:1] != "0" and (Lk + 127) // 128 >= 16
+                and (mode_name != "block_sparse" or density >= 0.12))
         roofline = {"bound": "tensor", "kernel": "attn_fwd_pair_kernel" if pair else "attn_fwd_kernel", "achieved": achieved, "peak": burst, "unit": "TFLOP/s",
                     "frac": achieved / burst, "peak_source": f"bf16 burst, of {src}", "frac_of_sustained": achieved / sustained,
                     "frac_of_spec_2250": achieved / 2250.0, "kernel_ms": attn_ms, "traffic": NCU_TRAFFIC_BYTES.get(name)}

@@ -108,6 +108,10 @@ int32_t launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
 
 // Dense attention with a fixed softmax reference runs on CTA pairs (attn_fwd_pair.cuh).  H3A_PAIR=0 in the
 // environment (read once) keeps every launch on the single-CTA kernel, for side-by-side measurements.
+// Pairs pay a cluster set-up per CTA; with very few key tiles (cross-attention to 512 text tokens = 4 tiles:
+// 0.93 ms on pairs against 0.80 ms) the single-CTA kernel is the faster one.
+constexpr int kPairMinKeyTiles = 16;
+
 bool pair_kernel_enabled() {
   static const bool on = [] {
     const char* e = std::getenv("H3A_PAIR");
@@ -251,7 +255,8 @@ int32_t h3a_attn_workspace_bytes(const h3a_attn_params* p, size_t* bytes) {
     // optional: partial sums of the split last wave (dense launches with a logit bound); without it the launch
     // simply does not split
     const bool fixed = p->logit_bound > 0.f && p->logit_bound <= 30.f;
-    *bytes = (fixed && pair_kernel_enabled() && p->Lq > 0 && p->Lk > 0 && p->H > 0) ? plan_split(p->Lq, p->Lk, p->H).bytes : 0;
+    const bool pairs = fixed && pair_kernel_enabled() && p->Lq > 0 && p->H > 0 && (p->Lk + 127) / 128 >= kPairMinKeyTiles;
+    *bytes = pairs ? plan_split(p->Lq, p->Lk, p->H).bytes : 0;
   }
   return H3A_OK;
 }
@@ -303,7 +308,7 @@ int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream) {
     // neighbourhood masks that duplicated work outweighs what the pair saves (measured: 7 % density, 7 % extra
     // tiles, 3 % slower; 23 % density, 0.4 % extra, 7 % faster), so sparse launches go to pairs from 12 % up.
     const double density = static_cast<double>(p->nnz) / (static_cast<double>(a.nqb) * static_cast<double>(a.nkb));
-    if (fixed && pair_kernel_enabled() && density >= 0.12) {
+    if (fixed && pair_kernel_enabled() && density >= 0.12 && a.n_kv_tiles >= kPairMinKeyTiles) {
       // CTA pairs: one merged plan per four query tiles (never longer than the four lists together, and there
       // are no more groups of four than pairs of two, so the same workspace holds it)
       const int n_clusters = (p->Lq + 511) / 512;
@@ -318,7 +323,7 @@ int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream) {
     if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
     return fixed ? launch_attn<false, true, true>(mq, mk, mv, a, st) : launch_attn<false, true, false>(mq, mk, mv, a, st);
   }
-  if (fixed && pair_kernel_enabled()) {
+  if (fixed && pair_kernel_enabled() && a.n_kv_tiles >= kPairMinKeyTiles) {
     a.split_begin = static_cast<int>((p->Lq + 511) / 512 * p->H);
     a.kv_splits = 1;
     if (p->workspace && aligned16(p->workspace)) {

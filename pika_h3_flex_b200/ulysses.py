@@ -170,7 +170,8 @@ class UlyssesAttention:
 
     ``prep_fn(q, k, q_rope, k_rope, fp8) -> (q', k', q_scale, k_scale)`` (either of q, k may be None) and
     ``attn_fn(q, k, v, mode, q_scale, k_scale, block_index)`` default to the CUDA library; the CPU tests
-    inject host stand-ins to exercise the reshard logic with gloo ranks.
+    inject host stand-ins to exercise the reshard logic with gloo ranks.  ``head_groups``: 1 = one attention
+    launch, 2 = up to two groups chosen by the wave model (default), or an explicit list of group sizes.
     """
 
     def __init__(self, group=None, mode: int = _lib.MODE_DENSE_BF16, block_index: Optional[ops.BlockIndex] = None,
@@ -207,6 +208,12 @@ class UlyssesAttention:
         """Split the ``hp`` local head slots into at most two groups, so that one group's exchanges overlap the
         other's attention.  On a GPU the cut is placed where the two attention launches together are estimated to
         take no longer (within 2 %) than a single launch would; if no cut achieves that, one group is used."""
+        if not isinstance(self.head_groups, int):  # explicit group sizes
+            sizes = list(self.head_groups)
+            if sum(sizes) != hp or min(sizes) < 1:
+                raise ValueError(f"head_groups {sizes} must be positive and sum to the {hp} local head slots")
+            cuts = [sum(sizes[:i]) for i in range(len(sizes) + 1)]
+            return [range(a, b) for a, b in zip(cuts[:-1], cuts[1:])]
         if self.head_groups < 2 or hp < 2:
             return [range(hp)]
         if like.is_cuda and hp < 8:

@@ -460,13 +460,13 @@ def test_repeated_sparse_launches_with_uneven_streams_stay_finite(h, cfg0):
 
 
 # ------------------------------------------------------------------------------------------ CTA-pair kernel
-# Dense attention with a fixed softmax reference runs on pairs of CTAs (one MMA of 256 rows per pair).  The cases
-# cover: one pair with its second CTA partly or wholly beyond the last query row, ragged key tails, several pairs
-# per head, several heads, and the FP8 operands.
+# Attention with a fixed softmax reference over at least 16 key tiles runs on pairs of CTAs (one MMA of 256 rows per
+# pair).  The cases cover: one pair with its second CTA partly or wholly beyond the last query row, ragged key
+# tails, several pairs per head, several heads, and the FP8 operands.
 PAIR_BOUND = 14.0  # |q.k|/sqrt(128) of unit-normal rows stays far below this
 
 
-@pytest.mark.parametrize("L,Lk,H", [(512, 128, 1), (256, 300, 1), (257, 129, 2), (700, 1000, 3), (1536, 2048, 2), (4096, 4096, 4)])
+@pytest.mark.parametrize("L,Lk,H", [(512, 2048, 1), (256, 2100, 1), (257, 1921, 2), (700, 2500, 3), (1536, 2048, 2), (4096, 4096, 4)])
 def test_pair_kernel_dense_shapes(h, L, Lk, H):
     q, k, v = bf16_inputs(L, H, 900 + L + Lk, Lk)
     ref, ref_lse = O.attention(q.float(), k.float(), v.float(), return_lse=True)
@@ -479,7 +479,7 @@ def test_pair_kernel_dense_shapes(h, L, Lk, H):
 
 @pytest.mark.parametrize("L,H", [(512, 2), (1000, 2), (130, 1)])
 def test_pair_kernel_fp8(h, L, H):
-    q, k, v = bf16_inputs(L, H, 950 + L)
+    q, k, v = bf16_inputs(L, H, 950 + L, 2304 - L % 7)
     qq, sq = O.quantize_e4m3_blocks(q.float())
     kq, sk = O.quantize_e4m3_blocks(k.float())
     ref = O.attention(O.dequantize_blocks(qq, sq), O.dequantize_blocks(kq, sk), v.float())
@@ -500,13 +500,13 @@ def test_pair_kernel_agrees_with_single_cta_kernel(h, tmp_path):
         "import sys, torch; sys.path.insert(0, %r)\n"
         "import pika_h3_flex_b200 as h\n"
         "g = torch.Generator().manual_seed(77)\n"
-        "q, k, v = (torch.randn(1100, 3, 128, generator=g).bfloat16().cuda() for _ in range(3))\n"
+        "q, k, v = (torch.randn(2200, 3, 128, generator=g).bfloat16().cuda() for _ in range(3))\n"
         "torch.save(h.attn_fwd(q, k, v, logit_bound=%r).cpu(), %r)\n" % (root, PAIR_BOUND, str(path))
     )
     env = dict(os.environ, H3A_PAIR="0")
     subprocess.run([sys.executable, "-c", code], check=True, env=env, timeout=300)
     g = torch.Generator().manual_seed(77)
-    q, k, v = (torch.randn(1100, 3, 128, generator=g).bfloat16().cuda() for _ in range(3))
+    q, k, v = (torch.randn(2200, 3, 128, generator=g).bfloat16().cuda() for _ in range(3))
     out = h.attn_fwd(q, k, v, logit_bound=PAIR_BOUND).cpu()
     single = torch.load(path)
     assert float((out.float() - single.float()).abs().max()) <= 1e-3
@@ -516,7 +516,7 @@ def test_pair_kernel_agrees_with_single_cta_kernel(h, tmp_path):
 def test_pair_kernel_skips_work_when_the_status_word_is_already_set(h):
     """A launch whose status word already holds an error does nothing: every pair reads rank 0's verdict,
     passes both cluster barriers and returns without touching TMEM or the output."""
-    q, k, v = bf16_inputs(1024, 2, 970)
+    q, k, v = bf16_inputs(1024, 2, 970, 2048)
     st = torch.full((1,), 0x105, dtype=torch.int32, device="cuda")
     out = torch.full((1024, 2, 128), 7.0, dtype=torch.bfloat16, device="cuda")
     h.attn_fwd(dev(q), dev(k), dev(v), out=out, logit_bound=PAIR_BOUND, status_word=st)
@@ -542,11 +542,22 @@ def test_pair_kernel_repeated_launches_are_bit_identical(h):
     check(first, O.attention(q.float(), k.float(), v.float()))
 
 
+def _ring_rows(n, width, empty, long_row=None):
+    """n query tiles over n key tiles: tile i keeps `width` key tiles starting at 3 i (mod n); the tiles in `empty`
+    keep none; `long_row` keeps every second key tile."""
+    rows = [sorted({(3 * i + j) % n for j in range(width)}) for i in range(n)]
+    for i in empty:
+        rows[i] = []
+    if long_row is not None:
+        rows[long_row] = list(range(0, n, 2))
+    return rows
+
+
 @pytest.mark.parametrize("rows", [
-    # a query tile with no key tile whose partner in the MMA (the adjacent tile) has some; uneven lists
-    [[0, 1, 2, 3], [1, 2], [], [0, 4, 5, 6, 7], [0, 5], [], [3], []],
+    # query tiles with no key tile whose partner in the MMA (the adjacent tile) has some; uneven lists
+    _ring_rows(16, 3, empty=(2, 5, 7), long_row=3),
     # four consecutive query tiles (one CTA pair) with no key tile at all, ragged last tile
-    [[0, 1, 2, 3, 4, 5], [1, 7, 8], [2, 3], [0, 9], [], [], [], [], [0, 1, 2, 3, 4, 5, 6, 7, 8, 9], [5, 6, 7]],
+    _ring_rows(18, 4, empty=(4, 5, 6, 7, 13), long_row=16),
 ])
 def test_pair_kernel_block_sparse_structures(h, rows):
     """Block-sparse launches above 12 % density run on CTA pairs with one merged plan per four query tiles."""
@@ -575,7 +586,7 @@ def test_pair_kernel_block_sparse_structures(h, rows):
     assert float((lse.cpu().t()[~empty] - ref_lse[~empty]).abs().max()) < 2e-3
 
 
-@pytest.mark.parametrize("L,Lk,H,fp8", [(1000, 1500, 3, False), (4096, 4096, 4, False), (2100, 8192, 5, False), (1536, 4096, 3, True)])
+@pytest.mark.parametrize("L,Lk,H,fp8", [(1000, 2200, 3, False), (4096, 4096, 4, False), (2100, 8192, 5, False), (1536, 4096, 3, True)])
 def test_pair_kernel_split_last_wave(h, L, Lk, H, fp8):
     """With the optional workspace the pairs of the last, partly filled wave each walk a share of the key tiles and a
     second kernel adds the shares; without it nothing is split.  Both must give the oracle's rows (and each other's,

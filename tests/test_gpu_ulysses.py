@@ -77,7 +77,8 @@ for mode_name in ("dense", "fp8_qk", "block_sparse"):
     elif mode_name == "fp8_qk":
         mode = h.MODE_FP8_QK
     ref = O.joint_attention(q.float(), k.float(), v.float(), pos, mode_name, csr=csr)[sl]
-    for groups in (1, 2):
+    hp = (H + world - 1) // world
+    for groups in (1, 2, [1] * hp):  # one launch, the automatic choice, and one exchange + launch per head slot
         ua = UlyssesAttention(None, mode, bi, head_groups=groups)
         out = ua(q[sl].cuda(), k[sl].cuda(), v[sl].cuda(), h.rope_table(pos[sl].cuda()))
         st = O.error_stats(out.float().cpu(), ref)
