@@ -84,7 +84,9 @@ typedef struct h3a_attn_params {
   const int32_t* col_idx; /* BLOCK_SPARSE: [nnz] device int32, ascending inside each row */
   int32_t nnz;            /* BLOCK_SPARSE: number of kept tiles (host value of row_ptr[last]) */
   float* lse;             /* optional [H, Lq] fp32 natural-log-sum-exp out, or NULL */
-  void* workspace;        /* device scratch of h3a_attn_workspace_bytes() bytes (BLOCK_SPARSE only) */
+  void* workspace;        /* device scratch of h3a_attn_workspace_bytes() bytes: required for BLOCK_SPARSE
+                             (merged tile plan); optional for the dense modes (partial sums of a split last
+                             wave of CTAs: without it, or when it is too small, the launch simply does not split) */
   size_t workspace_bytes;
   int32_t* status_word;   /* optional device int32; a kernel that gives up a bounded wait writes a
                              non-zero code here and returns; must be 0 on entry */
@@ -128,7 +130,10 @@ int32_t h3a_version(int32_t* major, int32_t* minor);
 /* Human-readable name of a status code (static storage). */
 const char* h3a_status_string(int32_t status);
 
-/* Bytes of device scratch h3a_attn_fwd needs for these params (0 for the dense modes). */
+/* Bytes of device scratch for these params on the current device.  BLOCK_SPARSE: what h3a_attn_fwd needs.
+ * Dense modes: what lets the launch split its last wave of CTAs over the key range (0 when that does not pay:
+ * no logit bound, short key range, or a CTA count that already fills whole waves); needs Lq, Lk, H, mode and
+ * logit_bound only. */
 int32_t h3a_attn_workspace_bytes(const h3a_attn_params* p, size_t* bytes);
 
 /* Launch the attention forward on `stream` (a cudaStream_t passed as void*). */
