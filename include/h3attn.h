@@ -209,6 +209,41 @@ int32_t h3a_static_scratch_capacity(size_t* plan_entries);
  */
 int32_t h3a_selftest_wait_timeout(int32_t* status_word, int64_t wait_limit_ns, void* stream);
 
+/*
+ * Projection with the attention preparation fused into its epilogue.  Replaces, for one of Q / K / V, the module
+ * call `attn.to_q(hidden_states)` on a LoRA-wrapped Linear (reference: src/pika_h3/core/loader.py:9 names the
+ * wrapped projections, :20-49 applies rank-128 LoRA with alpha = rank, src/pika_h3/pipeline.py:34) followed by
+ * the per-head RMSNorm + rotation that h3a_qk_prep does as a separate pass:
+ *   Y[l, n] = sum_k x[l, k] w[n, k]  +  sum_r lora_t[l, r] lora_bs[n, r]  +  bias[n]
+ * x [L, K] and w [N, K] (nn.Linear layout) are bf16 with K contiguous; N = heads * 128.  The LoRA term is optional:
+ * lora_t = x A^T [L, R] (the caller computes this thin product) and lora_bs = (alpha / rank) * B [N, R].
+ * epilogue H3A_PROJ_STORE writes Y as bf16; H3A_PROJ_PREP applies RMSNorm over each head's 128 columns (times
+ * norm_weight when given), then the rotation by `rope` ([L, 64, 2] fp32, optional), then writes bf16.  Output
+ * element (l, head, c) goes to out[l * out_stride_l + head * out_stride_h + c] (strides in elements).
+ * Runs on CTA pairs (256 tokens x 256 columns per pair); needs compute capability 10.x.
+ */
+#define H3A_PROJ_STORE 0
+#define H3A_PROJ_PREP 1
+typedef struct h3a_proj_params {
+  const void* x;          /* [L, K] bf16 */
+  const void* w;          /* [N, K] bf16 */
+  const void* lora_t;     /* [L, R] bf16 or NULL */
+  const void* lora_bs;    /* [N, R] bf16 or NULL */
+  const float* bias;      /* [N] fp32 or NULL */
+  const float* rope;      /* H3A_PROJ_PREP: [L, 64, 2] fp32 (cos, sin) or NULL */
+  const float* norm_weight; /* H3A_PROJ_PREP: [128] fp32 or NULL (unit weights) */
+  void* out;              /* bf16 */
+  int64_t x_stride_l, w_stride_n, lora_t_stride_l, lora_bs_stride_n; /* row strides in elements, multiples of 8 */
+  int64_t out_stride_l, out_stride_h;
+  int32_t L, K, N, R;
+  int32_t epilogue;       /* H3A_PROJ_* */
+  int32_t rope_mode;      /* H3A_ROPE_* */
+  float eps;              /* <= 0 selects 1e-6 */
+  int32_t* status_word;   /* as in h3a_attn_params */
+  int64_t wait_limit_ns;
+} h3a_proj_params;
+int32_t h3a_proj_fwd(const h3a_proj_params* p, void* stream);
+
 /* Copy the device status word to the host after synchronising `stream`; maps non-zero to H3A_ERR_TIMEOUT. */
 int32_t h3a_read_device_status(const int32_t* status_word, void* stream, int32_t* raw);
 

@@ -19,6 +19,7 @@ from .ops import (
     static_scratch_capacity,
     build_block_index,
     joint_attention,
+    proj_fwd,
     qk_prep,
     read_status,
     rope_table,
@@ -27,6 +28,6 @@ from .ops import (
 
 __all__ = [
     "_lib", "H3AError", "MODE_DENSE_BF16", "MODE_FP8_QK", "MODE_BLOCK_SPARSE",
-    "BlockIndex", "attn_fwd", "attn_fwd_sparse_static", "static_scratch_capacity", "build_block_index", "joint_attention", "qk_prep",
+    "BlockIndex", "attn_fwd", "attn_fwd_sparse_static", "static_scratch_capacity", "build_block_index", "joint_attention", "proj_fwd", "qk_prep",
     "read_status", "rope_table", "rope_table_from_cos_sin", "position_grid", "HostJointAttention",
 ]

@@ -34,6 +34,7 @@ EXPORTS = (
     "h3a_static_scratch_capacity",
     "h3a_memcpy2d_async",
     "h3a_selftest_wait_timeout",
+    "h3a_proj_fwd",
 )
 
 
@@ -62,6 +63,21 @@ class PrepParams(C.Structure):
         ("q_rope", C.c_void_p), ("k_rope", C.c_void_p), ("q_weight", C.c_void_p), ("k_weight", C.c_void_p),
         ("eps", C.c_float), ("rope_mode", C.c_int32), ("flags", C.c_uint32),
     ]
+
+
+class ProjParams(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("w", C.c_void_p), ("lora_t", C.c_void_p), ("lora_bs", C.c_void_p),
+        ("bias", C.c_void_p), ("rope", C.c_void_p), ("norm_weight", C.c_void_p), ("out", C.c_void_p),
+        ("x_stride_l", C.c_int64), ("w_stride_n", C.c_int64), ("lora_t_stride_l", C.c_int64), ("lora_bs_stride_n", C.c_int64),
+        ("out_stride_l", C.c_int64), ("out_stride_h", C.c_int64),
+        ("L", C.c_int32), ("K", C.c_int32), ("N", C.c_int32), ("R", C.c_int32),
+        ("epilogue", C.c_int32), ("rope_mode", C.c_int32), ("eps", C.c_float),
+        ("status_word", C.c_void_p), ("wait_limit_ns", C.c_int64),
+    ]
+
+
+PROJ_STORE, PROJ_PREP = 0, 1
 
 
 class H3AError(RuntimeError):
@@ -108,6 +124,8 @@ def load() -> C.CDLL:
     lib.h3a_memcpy2d_async.restype = C.c_int32
     lib.h3a_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
     lib.h3a_selftest_wait_timeout.restype = C.c_int32
+    lib.h3a_proj_fwd.argtypes = [C.POINTER(ProjParams), C.c_void_p]
+    lib.h3a_proj_fwd.restype = C.c_int32
     _lib = lib
     return lib
 

@@ -15,6 +15,7 @@
 #include "attn_fwd.cuh"
 #include "attn_fwd_pair.cuh"
 #include "qk_prep.cuh"
+#include "qkv_proj.cuh"
 
 namespace {
 
@@ -54,6 +55,22 @@ int32_t make_map(CUtensorMap* m, const void* ptr, bool fp8, int64_t L, int64_t H
   CUresult r = enc(m, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims,
                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? H3A_OK : H3A_ERR_LAUNCH;
+}
+
+// m[r * stride + c], c < inner (contiguous), r < rows: box = 64 columns x 128 rows of bf16, 128-byte swizzle.
+int32_t make_map2d(CUtensorMap* m, const void* ptr, int64_t inner, int64_t rows, int64_t stride) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return H3A_ERR_DRIVER;
+  if (!aligned16(ptr) || (stride * 2) % 16 != 0) return H3A_ERR_ALIGN;
+  if (stride < inner || inner <= 0 || rows <= 0) return H3A_ERR_ARG;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(stride * 2)};
+  cuuint32_t box[2] = {64u, 128u};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? H3A_OK : H3A_ERR_LAUNCH;
 }
 
@@ -525,6 +542,58 @@ int32_t h3a_debug_set_trace(void* dev_buffer) {
   return cudaMemcpyToSymbol(h3a::g_trace, &dev_buffer, sizeof(void*)) == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
 }
 #endif
+
+int32_t h3a_proj_fwd(const h3a_proj_params* p, void* stream) {
+  if (!p || !p->x || !p->w || !p->out) return H3A_ERR_ARG;
+  if (p->L <= 0 || p->K <= 0 || p->N <= 0 || p->N % 128 != 0 || p->R < 0) return H3A_ERR_SHAPE;
+  if (p->epilogue != H3A_PROJ_STORE && p->epilogue != H3A_PROJ_PREP) return H3A_ERR_ARG;
+  if (p->rope_mode != H3A_ROPE_INTERLEAVED && p->rope_mode != H3A_ROPE_HALF) return H3A_ERR_ARG;
+  const bool lora = p->R > 0;
+  if (lora && (!p->lora_t || !p->lora_bs)) return H3A_ERR_ARG;
+  if (!aligned16(p->out) || (p->out_stride_l % 8) || (p->out_stride_h % 8) || p->out_stride_l <= 0 || p->out_stride_h <= 0) return H3A_ERR_ALIGN;
+  if ((p->bias && !aligned16(p->bias)) || (p->rope && !aligned16(p->rope)) || (p->norm_weight && !aligned16(p->norm_weight))) return H3A_ERR_ALIGN;
+  int32_t rc = check_arch();
+  if (rc != H3A_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap mx, mw, mt, mb;
+  if ((rc = make_map2d(&mx, p->x, p->K, p->L, p->x_stride_l)) != H3A_OK) return rc;
+  if ((rc = make_map2d(&mw, p->w, p->K, p->N, p->w_stride_n)) != H3A_OK) return rc;
+  if (lora) {
+    if ((rc = make_map2d(&mt, p->lora_t, p->R, p->L, p->lora_t_stride_l)) != H3A_OK) return rc;
+    if ((rc = make_map2d(&mb, p->lora_bs, p->R, p->N, p->lora_bs_stride_n)) != H3A_OK) return rc;
+  } else {
+    mt = mx;
+    mb = mw;
+  }
+  h3a::ProjArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.wait.status = p->status_word;
+  a.wait.wait_ns = p->wait_limit_ns > 0 ? p->wait_limit_ns : 2000000000ll;
+  a.L = p->L; a.N = p->N;
+  a.n_tiles_n = (p->N + 255) / 256;
+  a.kb_main = (p->K + 63) / 64;
+  a.kb_lora = lora ? (p->R + 63) / 64 : 0;
+  a.epilogue = p->epilogue;
+  a.bias = p->bias; a.rope = p->rope; a.norm_weight = p->norm_weight;
+  a.eps = p->eps > 0.f ? p->eps : 1e-6f;
+  a.rope_half = p->rope_mode == H3A_ROPE_HALF;
+  a.out = static_cast<__nv_bfloat16*>(p->out);
+  a.out_stride_l = p->out_stride_l; a.out_stride_h = p->out_stride_h;
+
+  static std::once_flag once[kMaxDevices];
+  static cudaError_t attr_err[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return H3A_ERR_LAUNCH;
+  std::call_once(once[dev], [dev] {
+    attr_err[dev] = cudaFuncSetAttribute(h3a::qkv_proj_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h3a::kProjSmemBytes);
+  });
+  if (attr_err[dev] != cudaSuccess) return H3A_ERR_LAUNCH;
+  a.n_tiles = ((p->L + 255) / 256) * a.n_tiles_n;
+  const int sms = sm_count_of_current_device();
+  const unsigned pairs = static_cast<unsigned>(std::min(a.n_tiles, std::max(1, sms / 2)));  // persistent: one pair per two SMs
+  h3a::qkv_proj_kernel<<<2u * pairs, h3a::kProjThreads, h3a::kProjSmemBytes, st>>>(mx, mw, mt, mb, a);
+  return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
+}
 
 int32_t h3a_read_device_status(const int32_t* status_word, void* stream, int32_t* raw) {
   if (!status_word) return H3A_ERR_ARG;

@@ -273,6 +273,13 @@ __device__ __forceinline__ void tma_load_3d_pair_if(uint32_t pred, uint32_t dst,
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(pred)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_2d_pair_if(uint32_t pred, uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+      "@q cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n\t}"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(pred)
+      : "memory");
+}
 // TMEM allocation for the pair: the same warp of BOTH CTAs executes each of these.
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t slot_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(ncols) : "memory");

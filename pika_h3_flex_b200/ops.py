@@ -265,6 +265,72 @@ def split_workspace_bytes(Lq: int, Lk: int, H: int, mode: int = _lib.MODE_DENSE_
     return int(need.value)
 
 
+def proj_fwd(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    lora_t: Optional[torch.Tensor] = None,
+    lora_bs: Optional[torch.Tensor] = None,
+    prep: bool = False,
+    rope: Optional[torch.Tensor] = None,
+    norm_weight: Optional[torch.Tensor] = None,
+    eps: float = 1e-6,
+    rope_half: bool = False,
+    status_word: Optional[torch.Tensor] = None,
+    wait_limit_ns: int = 0,
+):
+    """One of the Q / K / V projections through ``h3a_proj_fwd``: ``x [L, K]`` bf16 times ``weight [N, K]`` bf16
+    (``nn.Linear`` layout, N = heads x 128), plus ``lora_t [L, R] @ lora_bs [N, R]^T`` and ``bias [N]`` when given;
+    with ``prep`` the per-head RMSNorm (x ``norm_weight``) and the rotation by ``rope [L, 64, 2]`` run in the
+    epilogue.  Returns a logical ``[L, heads, 128]`` bf16 view of head-major storage, like :func:`qk_prep`."""
+    _require_cuda(x, weight)
+    lib = _lib.load()
+    if x.dim() != 2 or weight.dim() != 2 or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise ValueError("x [L, K] and weight [N, K] must be 2-D bf16")
+    L, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K or N % HEAD_DIM or x.stride(1) != 1 or weight.stride(1) != 1:
+        raise ValueError("weight must be [N, K] with N a multiple of 128; K must be contiguous in both")
+    p = _lib.ProjParams()
+    keep = []
+    p.x, p.w = x.data_ptr(), weight.data_ptr()
+    p.x_stride_l, p.w_stride_n = x.stride(0), weight.stride(0)
+    p.L, p.K, p.N = L, K, N
+    if (lora_t is None) != (lora_bs is None):
+        raise ValueError("lora_t and lora_bs go together")
+    if lora_t is not None:
+        if lora_t.shape[0] != L or lora_bs.shape[0] != N or lora_t.shape[1] != lora_bs.shape[1]:
+            raise ValueError("lora_t must be [L, R] and lora_bs [N, R]")
+        lora_t, lora_bs = lora_t.to(torch.bfloat16).contiguous(), lora_bs.to(torch.bfloat16).contiguous()
+        keep += [lora_t, lora_bs]
+        p.lora_t, p.lora_bs, p.R = lora_t.data_ptr(), lora_bs.data_ptr(), lora_t.shape[1]
+        p.lora_t_stride_l, p.lora_bs_stride_n = lora_t.stride(0), lora_bs.stride(0)
+    if bias is not None:
+        bias = bias.to(torch.float32).contiguous()
+        keep.append(bias)
+        p.bias = bias.data_ptr()
+    p.epilogue = _lib.PROJ_PREP if prep else _lib.PROJ_STORE
+    if prep:
+        if rope is not None:
+            if rope.shape != (L, 64, 2) or rope.dtype != torch.float32 or not rope.is_contiguous():
+                raise ValueError("rope must be a contiguous fp32 [L, 64, 2] table")
+            p.rope = rope.data_ptr()
+        if norm_weight is not None:
+            norm_weight = norm_weight.to(torch.float32).contiguous()
+            keep.append(norm_weight)
+            p.norm_weight = norm_weight.data_ptr()
+    p.eps = float(eps)
+    p.rope_mode = _lib.ROPE_HALF if rope_half else _lib.ROPE_INTERLEAVED
+    H = N // HEAD_DIM
+    out = torch.empty(H, L, HEAD_DIM, dtype=torch.bfloat16, device=x.device)
+    p.out, p.out_stride_l, p.out_stride_h = out.data_ptr(), HEAD_DIM, L * HEAD_DIM
+    if status_word is not None:
+        p.status_word = status_word.data_ptr()
+    p.wait_limit_ns = int(wait_limit_ns)
+    check(lib.h3a_proj_fwd(C.byref(p), _stream()), "h3a_proj_fwd")
+    return out.permute(1, 0, 2)
+
+
 def static_scratch_capacity() -> int:
     """Plan entries (int32) the library's built-in scratch holds: the limit on ``nnz + ceil(Lq/256)`` for
     :func:`attn_fwd_sparse_static`."""

@@ -63,6 +63,41 @@ def _norm_params(mod):
     return w, eps
 
 
+def _linear_parts(mod):
+    """``(weight, bias, lora_a, lora_b, scale)`` of a plain ``nn.Linear`` or of a LoRA-wrapped one, or None when
+    the module is not one this function can take apart (the processor then simply calls the module).  Recognised
+    wrappers: PEFT's ``lora.Linear`` (``base_layer`` + ``lora_A`` / ``lora_B`` ModuleDicts + ``scaling``, one
+    active adapter, not merged, no dropout in effect) as the reference's ``apply_lora`` builds them
+    (src/pika_h3/core/loader.py:20-49), and a bare ``base`` + ``A`` + ``B`` triple of Linears."""
+    nn = torch.nn
+    if isinstance(mod, nn.Linear):
+        return mod.weight, mod.bias, None, None, 1.0
+    base = getattr(mod, "base_layer", None)
+    if isinstance(base, nn.Linear) and hasattr(mod, "lora_A") and hasattr(mod, "lora_B"):
+        if getattr(mod, "merged", False):
+            return base.weight, base.bias, None, None, 1.0
+        if getattr(mod, "disable_adapters", False):
+            return base.weight, base.bias, None, None, 1.0
+        names = list(getattr(mod, "active_adapters", None) or mod.lora_A.keys())
+        names = [n for n in names if n in mod.lora_A]
+        if len(names) != 1:
+            return None
+        n = names[0]
+        drop = getattr(mod, "lora_dropout", {})
+        d = drop[n] if n in drop else None
+        if d is not None and not isinstance(d, nn.Identity) and (mod.training and getattr(d, "p", 0.0) > 0):
+            return None
+        a, b = mod.lora_A[n], mod.lora_B[n]
+        if not isinstance(a, nn.Linear) or not isinstance(b, nn.Linear) or a.bias is not None or b.bias is not None:
+            return None
+        return base.weight, base.bias, a.weight, b.weight, float(mod.scaling[n])
+    base = getattr(mod, "base", None)
+    a, b = getattr(mod, "A", None), getattr(mod, "B", None)
+    if isinstance(base, nn.Linear) and isinstance(a, nn.Linear) and isinstance(b, nn.Linear) and a.bias is None and b.bias is None:
+        return base.weight, base.bias, a.weight, b.weight, float(getattr(mod, "scale", 1.0))
+    return None
+
+
 class B200AttnProcessor:
     """Drop-in processor: ``processor(attn, hidden_states, encoder_hidden_states=None, ...)``.
 
@@ -75,11 +110,14 @@ class B200AttnProcessor:
                   tokens ``[r*S/P, (r+1)*S/P)``; rotary inputs are the rows of the same shard) and so is the result.
                   The projections stay token-local; the exchange of Q runs under the K projection and that of K
                   under the V projection.  Cross-attention needs no exchange (keys and values are replicated).
+    fused_projection  run to_q / to_k / to_v through the library's own GEMM with the norm + rotation in its epilogue
+                  (bf16 modes; plain or LoRA-wrapped Linears that ``_linear_parts`` recognises, bf16 weights and
+                  activations).  Anything else goes through the module call and the separate preparation kernel.
     """
 
     def __init__(self, mode: str = "dense_bf16", block_index: Optional[ops.BlockIndex] = None, rope_half: bool = False,
                  rope_split=ops.ROPE_SPLIT, rope_theta: float = 10000.0, qk_norm: bool = True, eps: float = 1e-6,
-                 group=None, sequence_parallel: bool = False):
+                 group=None, sequence_parallel: bool = False, fused_projection: bool = False):
         if mode not in MODES:
             raise ValueError(f"mode must be one of {sorted(MODES)}")
         if mode == "block_sparse" and block_index is None:
@@ -94,6 +132,8 @@ class B200AttnProcessor:
         self.eps = eps
         self._rope_cache = RopeCache()
         self._bounds = {}
+        self.fused_projection = fused_projection
+        self._scaled_b = {}
         self._ulysses = None
         if group is not None or sequence_parallel:  # sequence_parallel=True with group=None: the default group
             from .ulysses import UlyssesAttention
@@ -153,11 +193,55 @@ class B200AttnProcessor:
         qw, kw, eps, bound = self._norm_and_bound(attn, mode)
         return ops.joint_attention(q, k, v, None if cross else rope, mode, bi, qw, kw, eps, self.rope_half, logit_bound=bound)
 
+    # ---- fused projections
+    def _fusable(self, attn, x, ctx):
+        if not self.fused_projection or MODES[self.mode] == _lib.MODE_FP8_QK:
+            return None
+        if x.dtype != torch.bfloat16 or ctx.dtype != torch.bfloat16:
+            return None
+        parts = [_linear_parts(m) for m in (attn.to_q, attn.to_k, attn.to_v)]
+        if any(p is None or p[0].dtype != torch.bfloat16 for p in parts):
+            return None
+        return parts
+
+    def _fused(self, mod, parts, x2d, prep, rope, norm_w, eps):
+        """One projection through the library's GEMM; the thin LoRA product ``x A^T`` stays a torch matmul."""
+        w, bias, a, b, scale = parts
+        t = bs = None
+        if a is not None:
+            t = torch.nn.functional.linear(x2d, a.to(torch.bfloat16))
+            key = (id(mod), b.data_ptr(), scale)
+            bs = self._scaled_b.get(key)
+            if bs is None:  # (alpha / rank) * B, static at inference: scaled once per module
+                bs = self._scaled_b[key] = (b.float() * scale).to(torch.bfloat16).contiguous()
+        return ops.proj_fwd(x2d, w, bias, t, bs, prep=prep, rope=rope, norm_weight=norm_w, eps=eps, rope_half=self.rope_half)
+
+    def attention_fused(self, attn, parts, hidden_states, ctx, rope, cross: bool):
+        """Projections with the preparation in their epilogue, then attention (one GPU)."""
+        mode = MODES[self.mode]
+        bi = self.block_index
+        if cross and mode == _lib.MODE_BLOCK_SPARSE:
+            mode, bi = _lib.MODE_DENSE_BF16, None
+        qw, kw, eps, bound = self._norm_and_bound(attn, mode)
+        x2d, c2d = hidden_states[0], ctx[0]
+        q = self._fused(attn.to_q, parts[0], x2d, True, None if cross else rope, qw, eps)
+        k = self._fused(attn.to_k, parts[1], c2d, True, None if cross else rope, kw, eps)
+        v = self._fused(attn.to_v, parts[2], c2d, False, None, None, eps)
+        return ops.attn_fwd(q, k, v, mode, None, None, bi, logit_bound=bound)
+
     def attention_sequence_parallel(self, attn, hidden_states, rope):
         """Self-attention with the sequence sharded over the group: each projection is computed when the previous
         tensor's exchange is already on its way."""
         H = attn.heads
         qw, kw, eps, bound = self._norm_and_bound(attn, MODES[self.mode])
+        parts = self._fusable(attn, hidden_states, hidden_states)
+        if parts is not None:
+            x2d = hidden_states[0]
+            return self._ulysses.run(
+                lambda: self._fused(attn.to_q, parts[0], x2d, True, rope, qw, eps),
+                lambda: self._fused(attn.to_k, parts[1], x2d, True, rope, kw, eps),
+                lambda: self._fused(attn.to_v, parts[2], x2d, False, None, None, eps),
+                None, logit_bound=bound, prepared=True)
 
         def proj(lin):
             def f():
@@ -180,8 +264,14 @@ class B200AttnProcessor:
         S = hidden_states.shape[1]
         cross = encoder_hidden_states is not None
         rope = None if cross else self._rope(S, image_rotary_emb, kwargs)
+        ctx = hidden_states if encoder_hidden_states is None else encoder_hidden_states
+        parts = None if (self._ulysses is not None and not cross) else self._fusable(attn, hidden_states, ctx)
         if self._ulysses is not None and not cross:
             o = self.attention_sequence_parallel(attn, hidden_states, rope)
+        elif parts is not None:
+            if ctx.dim() != 3 or ctx.shape[0] != 1:
+                raise ValueError("encoder_hidden_states must be [1, T, D]")
+            o = self.attention_fused(attn, parts, hidden_states, ctx, rope, cross)
         else:
             q, k, v = self.project(attn, hidden_states, encoder_hidden_states)
             o = self.attention(attn, q, k, v, rope, cross)

@@ -232,13 +232,19 @@ class UlyssesAttention:
 
     def run(self, q_fn: Callable, k_fn: Callable, v_fn: Callable, rope: Optional[torch.Tensor],
             q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
-            rope_half: bool = False, logit_bound: Optional[float] = None) -> torch.Tensor:
+            rope_half: bool = False, logit_bound: Optional[float] = None, prepared: bool = False) -> torch.Tensor:
         """``q_fn() / k_fn() / v_fn()`` return this rank's ``[L/P, H, 128]`` bf16 projections; they are called in
-        that order, each after the previous tensor's exchange has been started."""
+        that order, each after the previous tensor's exchange has been started.  ``prepared``: Q and K arrive
+        normalised and rotated already (the fused projection does that in its epilogue), bf16 modes only."""
         world = dist.get_world_size(self.group)
         fp8 = self.mode == _lib.MODE_FP8_QK
 
+        if prepared and fp8:
+            raise ValueError("prepared operands are bf16: FP8-QK needs the quantising preparation")
+
         def prep(x, which):  # token-local work first: the wire then carries final operands
+            if prepared:
+                return x, None
             a, b = (x, None) if which == 0 else (None, x)
             ra, rb = (rope, None) if which == 0 else (None, rope)
             if self.prep_fn is not None:

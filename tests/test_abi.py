@@ -40,6 +40,42 @@ def test_struct_sizes_match_header(lib):
     # natural-alignment sizes of the two parameter structs as a C compiler lays them out
     assert C.sizeof(_lib.AttnParams) == 216
     assert C.sizeof(_lib.PrepParams) == 144
+    assert C.sizeof(_lib.ProjParams) == 160
+
+
+def test_struct_sizes_match_a_c_compiler(tmp_path):
+    """The same three sizes from the header itself, through gcc."""
+    import os
+    import shutil
+    import subprocess
+
+    if shutil.which("gcc") is None:
+        pytest.skip("no gcc")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = tmp_path / "sz.c"
+    src.write_text('#include <stdio.h>\n#include "h3attn.h"\nint main(void) { printf("%zu %zu %zu\\n", sizeof(h3a_attn_params), '
+                   'sizeof(h3a_prep_params), sizeof(h3a_proj_params)); return 0; }\n')
+    exe = tmp_path / "sz"
+    subprocess.run(["gcc", "-I", os.path.join(root, "include"), "-o", str(exe), str(src)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert [int(v) for v in out] == [C.sizeof(_lib.AttnParams), C.sizeof(_lib.PrepParams), C.sizeof(_lib.ProjParams)]
+
+
+def test_proj_argument_validation_without_a_device(lib):
+    p = _lib.ProjParams()
+    assert lib.h3a_proj_fwd(C.byref(p), None) == _lib.H3A_ERR_ARG  # null pointers
+    buf = (C.c_char * 4096)()
+    base = (C.addressof(buf) + 255) & ~255
+    p.x = p.w = p.out = base
+    p.L, p.K, p.N = 128, 64, 130
+    assert lib.h3a_proj_fwd(C.byref(p), None) == _lib.H3A_ERR_SHAPE  # N not a multiple of 128
+    p.N, p.epilogue = 128, 5
+    assert lib.h3a_proj_fwd(C.byref(p), None) == _lib.H3A_ERR_ARG  # epilogue
+    p.epilogue, p.R = _lib.PROJ_STORE, 64
+    assert lib.h3a_proj_fwd(C.byref(p), None) == _lib.H3A_ERR_ARG  # LoRA operands missing
+    p.R = 0
+    p.out_stride_l, p.out_stride_h = 100, 128
+    assert lib.h3a_proj_fwd(C.byref(p), None) == _lib.H3A_ERR_ALIGN  # output stride
 
 
 def test_attn_argument_validation_without_a_device(lib):

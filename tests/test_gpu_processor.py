@@ -133,6 +133,81 @@ def test_processor_rejects_what_it_cannot_do(setup):
         B200AttnProcessor("block_sparse")
 
 
+class PeftLikeLinear(nn.Module):
+    """The attribute layout of PEFT's lora.Linear: base_layer, lora_A / lora_B ModuleDicts keyed by adapter name,
+    a scaling dict, lora_dropout, merged / disable_adapters flags."""
+
+    def __init__(self, din, dout, r=16, alpha=8.0):
+        super().__init__()
+        self.base_layer = nn.Linear(din, dout, bias=True)
+        self.lora_A = nn.ModuleDict({"default": nn.Linear(din, r, bias=False)})
+        self.lora_B = nn.ModuleDict({"default": nn.Linear(r, dout, bias=False)})
+        self.lora_dropout = nn.ModuleDict({"default": nn.Identity()})
+        self.scaling = {"default": alpha / r}
+        self.active_adapters = ["default"]
+        self.merged = False
+        self.disable_adapters = False
+
+    def forward(self, x):
+        return self.base_layer(x) + self.scaling["default"] * self.lora_B["default"](self.lora_A["default"](x))
+
+
+@torch.no_grad()
+@pytest.mark.parametrize("wrapper", ["stub", "peft_like", "plain"])
+def test_fused_projection_matches_module_calls(setup, wrapper):
+    """fused_projection=True: to_q / to_k / to_v run through the library's GEMM with norm + rotation in its epilogue;
+    the result must match the processor that calls the modules (and the oracle)."""
+    from pika_h3_flex_b200 import build_block_index
+    from pika_h3_flex_b200.processor import B200AttnProcessor, _linear_parts
+
+    attn0, x, pos, grid, n_audio = setup
+    torch.manual_seed(11)
+    attn = StubAttention(256, 2).cuda().bfloat16()
+    if wrapper != "stub":
+        mk = (lambda i, o: PeftLikeLinear(i, o)) if wrapper == "peft_like" else (lambda i, o: nn.Linear(i, o))
+        attn.to_q, attn.to_k, attn.to_v = (mk(256, 256).cuda().bfloat16() for _ in range(3))
+    assert all(_linear_parts(m) is not None for m in (attn.to_q, attn.to_k, attn.to_v))
+    ref = oracle_forward(attn, x, None, pos)
+    y_mod = B200AttnProcessor()(attn, x, position_ids=pos.cuda())
+    y_fused = B200AttnProcessor(fused_projection=True)(attn, x, position_ids=pos.cuda())
+    assert float((y_fused.float() - ref.float()).abs().max()) < 3e-2
+    assert float((y_fused.float() - y_mod.float()).abs().max()) < 3e-2
+    bi = build_block_index(grid, n_audio, (1, 2, 2))
+    ys = B200AttnProcessor("block_sparse", bi.to("cuda"), fused_projection=True, rope_half=True)(attn, x, position_ids=pos.cuda())
+    ym = B200AttnProcessor("block_sparse", bi.to("cuda"), rope_half=True)(attn, x, position_ids=pos.cuda())
+    assert float((ys.float() - ym.float()).abs().max()) < 3e-2
+    # FP8-QK keeps the separate (quantising) preparation even when fusion is asked for
+    y8 = B200AttnProcessor("fp8_qk", fused_projection=True)(attn, x, position_ids=pos.cuda())
+    assert float(((y8.float() - ref.float()).norm() / ref.float().norm())) < 8e-2
+
+
+@torch.no_grad()
+def test_fused_projection_cross_attention(setup):
+    from pika_h3_flex_b200.processor import B200AttnProcessor
+
+    _, x, _, _, _ = setup
+    torch.manual_seed(4)
+    attn = StubAttention(256, 2, ctx_dim=512).cuda().bfloat16()
+    text = torch.randn(1, 77, 512, device="cuda").bfloat16()
+    y = B200AttnProcessor(fused_projection=True)(attn, x, encoder_hidden_states=text)
+    ref = oracle_forward(attn, x, text, None)
+    assert float((y.float() - ref.float()).abs().max()) < 3e-2
+
+
+def test_unrecognised_projection_modules_fall_back_to_the_module_call(setup):
+    from pika_h3_flex_b200.processor import _linear_parts
+
+    assert _linear_parts(nn.Sequential(nn.Linear(8, 8))) is None
+    two = PeftLikeLinear(8, 8)
+    two.lora_A["other"] = nn.Linear(8, 16, bias=False)
+    two.lora_B["other"] = nn.Linear(16, 8, bias=False)
+    two.active_adapters = ["default", "other"]
+    assert _linear_parts(two) is None  # two active adapters: not taken apart
+    merged = PeftLikeLinear(8, 8)
+    merged.merged = True
+    assert _linear_parts(merged)[2] is None  # merged: the base weight already holds the update
+
+
 _SP_CHILD = r"""
 import os, sys, importlib.util, torch, torch.distributed as dist
 sys.path.insert(0, {root!r})
@@ -163,6 +238,11 @@ with torch.no_grad():
         err = float((shard.float() - whole[:, sl].float()).abs().max())
         print(rank, mode, err, flush=True)
         ok = ok and tuple(shard.shape) == (1, Ss, 256) and err < (6e-2 if mode == "fp8_qk" else 2e-2)
+        if mode != "fp8_qk":  # projections through the library's GEMM, prepared operands on the wire
+            fused = B200AttnProcessor(mode, idx, sequence_parallel=True, fused_projection=True)(attn, x[:, sl].contiguous(), position_ids=pos[sl].cuda())
+            errf = float((fused.float() - whole[:, sl].float()).abs().max())
+            print(rank, mode, "fused", errf, flush=True)
+            ok = ok and errf < 3e-2
     text = torch.randn(1, 77, 256, device="cuda").bfloat16()
     c_whole = B200AttnProcessor()(attn, x, encoder_hidden_states=text)
     c_shard = B200AttnProcessor(sequence_parallel=True)(attn, x[:, sl].contiguous(), encoder_hidden_states=text)

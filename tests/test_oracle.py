@@ -142,3 +142,18 @@ def test_seeded_inputs_are_reproducible():
     b = O.seeded_qkv(16, 2, seed=1000)
     assert all(torch.equal(x, y) for x, y in zip(a, b))
     assert abs(float(a[0].std()) - 1.0) < 0.05
+
+
+def test_lora_linear_and_fused_preparation_oracle():
+    g = torch.Generator().manual_seed(9)
+    x, w = torch.randn(50, 96, generator=g), torch.randn(256, 96, generator=g)
+    a, b = torch.randn(8, 96, generator=g), torch.randn(256, 8, generator=g)
+    bias = torch.randn(256, generator=g)
+    y = O.lora_linear(x, w, bias, a, b, scale=0.5)
+    assert torch.allclose(y, x @ (w + 0.5 * b @ a).t() + bias, atol=1e-4)  # LoRA = a low-rank update of the weight
+    assert torch.equal(O.lora_linear(x, w), x @ w.t())
+    cos, sin = O.rope_table(O.make_positions((3, 4, 4), 2))
+    p = O.project_and_prepare(x, w, 2, bias, a, b, 0.5, cos, sin)
+    assert p.shape == (50, 2, 128)
+    assert torch.allclose(p.pow(2).mean(-1), torch.ones(50, 2), atol=1e-3)  # unit RMS per head; the rotation keeps it
+    assert torch.allclose(p, O.apply_rope(O.rms_norm(y.view(50, 2, 128)), cos, sin))
