@@ -408,19 +408,132 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------------ projection workloads
+# The Q/K/V projections feeding the attention (section "next" of the scope: LoRA-wrapped Linears with the
+# preparation fused into the GEMM epilogue).  Not the headline metric: a side workload with its own roofline line.
+PROJ_WORKLOADS = {
+    # name: (tokens, model width, heads, LoRA rank)
+    "cfg1_qkv_proj": (49384, 5120, 40, 128),
+    "prof_qkv_proj": (8192, 5120, 40, 128),
+}
+
+
+def run_projection(args):
+    import torch
+
+    import pika_h3_flex_b200 as h3
+    from oracle import oracle as O
+
+    L, D, H, R = PROJ_WORKLOADS[args.workload]
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(3001)
+    x = torch.randn(L, D, device=dev, generator=g).bfloat16()
+    ws = [(torch.randn(H * 128, D, device=dev, generator=g) / D ** 0.5).bfloat16() for _ in range(3)]
+    las = [(torch.randn(R, D, device=dev, generator=g) / D ** 0.5).bfloat16() for _ in range(3)]
+    lbs = [(0.5 * torch.randn(H * 128, R, device=dev, generator=g) / R ** 0.5).bfloat16() for _ in range(3)]
+    # positions: config 1's grid when L is its length, otherwise frames of 8 x 8 tokens plus audio
+    if L == 31 * 30 * 52 + 1024:
+        pos = O.make_positions((31, 30, 52), 1024)
+    else:
+        frames = (L - 1024) // 64
+        pos = O.make_positions((frames, 8, 8), L - frames * 64)
+    rope = h3.rope_table(pos.to(dev))
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    events = []
+
+    def step(record=False):
+        outs = []
+        for i in range(3):
+            t = torch.nn.functional.linear(x, las[i])  # the thin LoRA product x A^T (torch / cuBLAS)
+            if record:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            outs.append(h3.proj_fwd(x, ws[i], None, t, lbs[i], prep=(i < 2), rope=rope if i < 2 else None, status_word=status))
+            if record:
+                e1.record()
+                events.append((e0, e1))
+        return outs
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for _ in range(args.steps):
+        step(record=True)
+    e_stop.record()
+    torch.cuda.synchronize()
+    elapsed_ms = e_start.elapsed_time(e_stop)
+    ms_per_step = elapsed_ms / args.steps
+    extra = 0
+    if elapsed_ms < 1000.0:
+        extra = int(1500.0 / max(ms_per_step, 1e-3)) + 1
+        for _ in range(extra):
+            step()
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    if extra:
+        clocks["note"] = f"timed region {elapsed_ms:.0f} ms: sampling continued over {extra} identical untimed steps"
+    if h3.read_status(status) != 0:
+        raise SystemExit(f"device wait gave up: status 0x{h3.read_status(status):x}")
+    flops_kernel = 3 * 2.0 * L * (H * 128) * (D + R)       # the library's GEMMs (main + LoRA columns)
+    flops_step = flops_kernel + 3 * 2.0 * L * D * R        # + the thin products done by torch
+    kernel_ms = sum(a.elapsed_time(b) for a, b in events) / len(events)
+    burst, sustained, src = measured_peaks()
+    achieved = (flops_kernel / 3) / (kernel_ms * 1e-3) / 1e12
+    # torch reference of the same step on the same box: Linear + LoRA update + the separate preparation kernel
+    def torch_step():
+        for i in range(3):
+            y = torch.nn.functional.linear(x, ws[i]) + torch.nn.functional.linear(torch.nn.functional.linear(x, las[i]), lbs[i])
+            y = y.view(L, H, 128)
+            if i < 2:
+                h3.qk_prep(y if i == 0 else None, y if i == 1 else None, rope if i == 0 else None, rope if i == 1 else None)
+            else:
+                y.permute(1, 0, 2).contiguous()
+    for _ in range(3):
+        torch_step()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(5):
+        torch_step()
+    t1.record()
+    torch.cuda.synchronize()
+    line = {
+        "metric": "qkv_projection_tflops", "value": flops_step / (ms_per_step * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "L": L, "D": D, "H": H, "lora_rank": R,
+                   "step": "to_q, to_k (LoRA + RMSNorm + RoPE in the epilogue) and to_v (LoRA, head-major store)",
+                   "flops_per_step": flops_step, "l2": "X + W + out = %.0f MB per projection exceed the 126 MB L2; no flush" % ((2 * L * D * 2 + D * D * 2) / 1e6)},
+        "roofline": {"bound": "tensor", "kernel": "qkv_proj_kernel", "achieved": achieved, "peak": burst, "unit": "TFLOP/s",
+                     "frac": achieved / burst, "peak_source": f"bf16 burst, of {src}", "frac_of_sustained": achieved / sustained,
+                     "kernel_ms": kernel_ms, "traffic": None},
+        "torch_same_step_ms": t0.elapsed_time(t1) / 5, "cpu_baseline": None, "e2e": None, "clocks": clocks,
+        "gpu_launches": 3 * args.steps,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="cfg1_dense")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(PROJ_WORKLOADS), default="cfg1_dense")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the cpu_baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--head-groups", type=int, default=2, help="N > 1: head groups the exchanges are pipelined over (1 = no overlap)")
     ap.add_argument("--online-max", action="store_true", help="use the running-maximum kernel instead of the fixed logit bound")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload in PROJ_WORKLOADS:
+        if args.impl == "reference" or args.gpus != 1:
+            raise SystemExit("projection workloads run on one GPU with --impl ours")
+        run_projection(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
