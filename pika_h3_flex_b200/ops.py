@@ -278,11 +278,13 @@ def proj_fwd(
     rope_half: bool = False,
     status_word: Optional[torch.Tensor] = None,
     wait_limit_ns: int = 0,
+    token_major: bool = False,
 ):
-    """One of the Q / K / V projections through ``h3a_proj_fwd``: ``x [L, K]`` bf16 times ``weight [N, K]`` bf16
+    """One of the Q / K / V (or, with ``token_major``, the output) projections through ``h3a_proj_fwd``: ``x [L, K]`` bf16 times ``weight [N, K]`` bf16
     (``nn.Linear`` layout, N = heads x 128), plus ``lora_t [L, R] @ lora_bs [N, R]^T`` and ``bias [N]`` when given;
     with ``prep`` the per-head RMSNorm (x ``norm_weight``) and the rotation by ``rope [L, 64, 2]`` run in the
-    epilogue.  Returns a logical ``[L, heads, 128]`` bf16 view of head-major storage, like :func:`qk_prep`."""
+    epilogue.  Returns a logical ``[L, heads, 128]`` bf16 view of head-major storage, like :func:`qk_prep`; with
+    ``token_major`` a plain contiguous ``[L, N]`` tensor (what ``to_out`` produces)."""
     _require_cuda(x, weight)
     lib = _lib.load()
     if x.dim() != 2 or weight.dim() != 2 or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
@@ -322,13 +324,17 @@ def proj_fwd(
     p.eps = float(eps)
     p.rope_mode = _lib.ROPE_HALF if rope_half else _lib.ROPE_INTERLEAVED
     H = N // HEAD_DIM
-    out = torch.empty(H, L, HEAD_DIM, dtype=torch.bfloat16, device=x.device)
-    p.out, p.out_stride_l, p.out_stride_h = out.data_ptr(), HEAD_DIM, L * HEAD_DIM
+    if token_major:
+        out = torch.empty(L, N, dtype=torch.bfloat16, device=x.device)
+        p.out, p.out_stride_l, p.out_stride_h = out.data_ptr(), N, HEAD_DIM
+    else:
+        out = torch.empty(H, L, HEAD_DIM, dtype=torch.bfloat16, device=x.device)
+        p.out, p.out_stride_l, p.out_stride_h = out.data_ptr(), HEAD_DIM, L * HEAD_DIM
     if status_word is not None:
         p.status_word = status_word.data_ptr()
     p.wait_limit_ns = int(wait_limit_ns)
     check(lib.h3a_proj_fwd(C.byref(p), _stream()), "h3a_proj_fwd")
-    return out.permute(1, 0, 2)
+    return out if token_major else out.permute(1, 0, 2)
 
 
 def static_scratch_capacity() -> int:

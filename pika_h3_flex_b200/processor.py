@@ -277,7 +277,20 @@ class B200AttnProcessor:
             o = self.attention(attn, q, k, v, rope, cross)
         o = o.reshape(1, S, -1).to(hidden_states.dtype)
         to_out = attn.to_out
-        o = to_out[0](o)
+        out_parts = _linear_parts(to_out[0]) if (self.fused_projection and o.dtype == torch.bfloat16) else None
+        if out_parts is not None and out_parts[0].dtype == torch.bfloat16 and out_parts[0].shape[0] % ops.HEAD_DIM == 0:
+            # the output projection through the same GEMM (plain epilogue, token-major rows)
+            w, bias, a, b, scale = out_parts
+            t = bs = None
+            if a is not None:
+                t = torch.nn.functional.linear(o[0], a.to(torch.bfloat16))
+                key = (id(to_out[0]), b.data_ptr(), scale)
+                bs = self._scaled_b.get(key)
+                if bs is None:
+                    bs = self._scaled_b[key] = (b.float() * scale).to(torch.bfloat16).contiguous()
+            o = ops.proj_fwd(o[0].contiguous(), w, bias, t, bs, token_major=True)[None]
+        else:
+            o = to_out[0](o)
         if len(to_out) > 1:
             o = to_out[1](o)
         return o

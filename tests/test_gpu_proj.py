@@ -88,3 +88,15 @@ def test_projection_rejects_bad_arguments(h):
         h.proj_fwd(x, w, lora_t=torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda"))  # LoRA halves go together
     with pytest.raises(ValueError):
         h.proj_fwd(x.float(), w)
+
+
+def test_projection_token_major_output(h):
+    """The output projection (to_out): same GEMM, rows written token-major [L, N]."""
+    L, K, H = 900, 384, 3
+    x, w, b, a, bm = _inputs(L, K, H, 64, True, 77)
+    t = _lora_t(x, a)
+    ref = O.lora_linear(x, w, b, None, None) + t.float() @ bm.float().t()
+    out = h.proj_fwd(x.cuda(), w.cuda(), b.cuda(), t.cuda(), bm.cuda(), token_major=True)
+    assert out.shape == (L, H * 128) and out.is_contiguous()
+    s = O.error_stats(out.float().cpu(), ref)
+    assert s["rel_l2"] <= 5e-3 and s["max_abs"] <= 3e-2, s
