@@ -46,7 +46,7 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention-kernel launch, from the ncu captures summarised
 # under profiles/ (None until a capture of that workload exists)
 NCU_TRAFFIC_BYTES = {
-    "prof_dense": 250.9e6,           # measured (profiles/attn_fwd_dense_bf16_prof_dense.md)
+    "prof_dense": 250.9e6,           # measured: the ncu capture of this workload summarised under profiles/
     "cfg1_dense": 250.9e6 * 7.535,   # the same capture scaled by the units per launch (L*H: 49,384*40 / 16,384*16)
 }
 
