@@ -244,6 +244,30 @@ typedef struct h3a_proj_params {
 } h3a_proj_params;
 int32_t h3a_proj_fwd(const h3a_proj_params* p, void* stream);
 
+/*
+ * Pre-attention adaptive layer norm: y = norm(x) * (1 + scale[idx[l]]) + shift[idx[l]] per token row l.  Replaces the
+ * reference's patched `self.norm(hidden_states)` followed by `hidden_states * (1.0 + scale.index_select(0,
+ * timestep_indices)) + shift.index_select(0, timestep_indices)` (patches/0001-h3-adaln-fp32.patch:36-40; the
+ * modulation tables come from the fp32-SiLU Linear of the same patch, :14-26).  x, y [L, D] bf16 (D a multiple of
+ * 8, at most 8192), scale / shift [T, D] bf16 with their own row strides (they may be the two halves of one
+ * [T, 2 D] tensor), idx [L] int64 or NULL (every token uses row 0).  norm is LayerNorm (rms = 0) or RMSNorm
+ * (rms = 1) over D in fp32, with optional fp32 weight / bias [D].  HBM-bound: one read and one write of the rows.
+ */
+typedef struct h3a_adaln_params {
+  const void* x;
+  void* y;
+  const void* scale;
+  const void* shift;
+  const int64_t* idx;
+  const float* weight;
+  const float* bias;
+  int64_t x_stride, y_stride, scale_stride, shift_stride; /* row strides in elements, multiples of 8 */
+  int32_t L, D, T;
+  int32_t rms;
+  float eps; /* <= 0 selects 1e-6 */
+} h3a_adaln_params;
+int32_t h3a_adaln_norm(const h3a_adaln_params* p, void* stream);
+
 /* Copy the device status word to the host after synchronising `stream`; maps non-zero to H3A_ERR_TIMEOUT. */
 int32_t h3a_read_device_status(const int32_t* status_word, void* stream, int32_t* raw);
 

@@ -301,6 +301,27 @@ def project_and_prepare(x, weight, heads: int, bias=None, lora_a=None, lora_b=No
     return y
 
 
+def adaln_modulate(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, idx: Optional[torch.Tensor] = None,
+                   eps: float = 1e-6, rms: bool = False, weight: Optional[torch.Tensor] = None,
+                   bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``norm(x) * (1 + scale[idx]) + shift[idx]`` in fp32: the reference's patched adaptive layer norm
+    (patches/0001-h3-adaln-fp32.patch:36-40: ``self.norm(hidden_states)`` then the modulation with
+    ``index_select(0, timestep_indices)``).  ``x [L, D]``, ``scale`` / ``shift`` ``[T, D]``, ``idx [L]``."""
+    x = x.float()
+    if rms:
+        n = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+    else:
+        mu = x.mean(-1, keepdim=True)
+        n = (x - mu) * torch.rsqrt((x - mu).pow(2).mean(-1, keepdim=True) + eps)
+    if weight is not None:
+        n = n * weight.float()
+    if bias is not None:
+        n = n + bias.float()
+    if idx is None:
+        idx = torch.zeros(x.shape[0], dtype=torch.long)
+    return n * (1.0 + scale.float().index_select(0, idx)) + shift.float().index_select(0, idx)
+
+
 def ulysses_simulate(q_shards, k_shards, v_shards, attn_fn, n_heads: int):
     """Sequence-parallel attention over ``P = len(q_shards)`` simulated ranks.
 

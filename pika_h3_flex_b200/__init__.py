@@ -14,6 +14,7 @@ from .host_path import HostJointAttention
 from .layout import position_grid
 from .ops import (
     BlockIndex,
+    adaln_norm,
     attn_fwd,
     attn_fwd_sparse_static,
     static_scratch_capacity,
@@ -28,6 +29,6 @@ from .ops import (
 
 __all__ = [
     "_lib", "H3AError", "MODE_DENSE_BF16", "MODE_FP8_QK", "MODE_BLOCK_SPARSE",
-    "BlockIndex", "attn_fwd", "attn_fwd_sparse_static", "static_scratch_capacity", "build_block_index", "joint_attention", "proj_fwd", "qk_prep",
+    "BlockIndex", "adaln_norm", "attn_fwd", "attn_fwd_sparse_static", "static_scratch_capacity", "build_block_index", "joint_attention", "proj_fwd", "qk_prep",
     "read_status", "rope_table", "rope_table_from_cos_sin", "position_grid", "HostJointAttention",
 ]

@@ -35,6 +35,7 @@ EXPORTS = (
     "h3a_memcpy2d_async",
     "h3a_selftest_wait_timeout",
     "h3a_proj_fwd",
+    "h3a_adaln_norm",
 )
 
 
@@ -78,6 +79,15 @@ class ProjParams(C.Structure):
 
 
 PROJ_STORE, PROJ_PREP = 0, 1
+
+
+class AdaLnParams(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("y", C.c_void_p), ("scale", C.c_void_p), ("shift", C.c_void_p),
+        ("idx", C.c_void_p), ("weight", C.c_void_p), ("bias", C.c_void_p),
+        ("x_stride", C.c_int64), ("y_stride", C.c_int64), ("scale_stride", C.c_int64), ("shift_stride", C.c_int64),
+        ("L", C.c_int32), ("D", C.c_int32), ("T", C.c_int32), ("rms", C.c_int32), ("eps", C.c_float),
+    ]
 
 
 class H3AError(RuntimeError):
@@ -126,6 +136,8 @@ def load() -> C.CDLL:
     lib.h3a_selftest_wait_timeout.restype = C.c_int32
     lib.h3a_proj_fwd.argtypes = [C.POINTER(ProjParams), C.c_void_p]
     lib.h3a_proj_fwd.restype = C.c_int32
+    lib.h3a_adaln_norm.argtypes = [C.POINTER(AdaLnParams), C.c_void_p]
+    lib.h3a_adaln_norm.restype = C.c_int32
     _lib = lib
     return lib
 

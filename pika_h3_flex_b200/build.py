@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "csrc", "h3attn_api.cu")
 OUT = os.path.join(HERE, "libh3attn.so")
-DEPS = [SRC] + [os.path.join(HERE, "csrc", f) for f in ("attn_fwd.cuh", "attn_fwd_pair.cuh", "qk_prep.cuh", "qkv_proj.cuh", "ptx.cuh")] + [
+DEPS = [SRC] + [os.path.join(HERE, "csrc", f) for f in ("attn_fwd.cuh", "attn_fwd_pair.cuh", "qk_prep.cuh", "qkv_proj.cuh", "adaln.cuh", "ptx.cuh")] + [
     os.path.join(HERE, "..", "include", "h3attn.h")
 ]
 

@@ -16,6 +16,7 @@
 #include "attn_fwd_pair.cuh"
 #include "qk_prep.cuh"
 #include "qkv_proj.cuh"
+#include "adaln.cuh"
 
 namespace {
 
@@ -592,6 +593,40 @@ int32_t h3a_proj_fwd(const h3a_proj_params* p, void* stream) {
   const int sms = sm_count_of_current_device();
   const unsigned pairs = static_cast<unsigned>(std::min(a.n_tiles, std::max(1, sms / 2)));  // persistent: one pair per two SMs
   h3a::qkv_proj_kernel<<<2u * pairs, h3a::kProjThreads, h3a::kProjSmemBytes, st>>>(mx, mw, mt, mb, a);
+  return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
+}
+
+int32_t h3a_adaln_norm(const h3a_adaln_params* p, void* stream) {
+  if (!p || !p->x || !p->y || !p->scale || !p->shift) return H3A_ERR_ARG;
+  if (p->L <= 0 || p->T <= 0 || p->D <= 0 || p->D % 8 != 0 || p->D > 8 * h3a::kAdaThreads * h3a::kAdaMaxChunks) return H3A_ERR_SHAPE;
+  if (p->rms != 0 && p->rms != 1) return H3A_ERR_ARG;
+  if (!aligned16(p->x) || !aligned16(p->y) || !aligned16(p->scale) || !aligned16(p->shift)) return H3A_ERR_ALIGN;
+  if ((p->x_stride % 8) || (p->y_stride % 8) || (p->scale_stride % 8) || (p->shift_stride % 8)) return H3A_ERR_ALIGN;
+  if (p->x_stride < p->D || p->y_stride < p->D || p->scale_stride < p->D || p->shift_stride < p->D) return H3A_ERR_ARG;
+  h3a::AdaLnArgs a;
+  a.x = static_cast<const __nv_bfloat16*>(p->x);
+  a.y = static_cast<__nv_bfloat16*>(p->y);
+  a.x_stride = p->x_stride; a.y_stride = p->y_stride;
+  a.scale = static_cast<const __nv_bfloat16*>(p->scale);
+  a.shift = static_cast<const __nv_bfloat16*>(p->shift);
+  a.scale_stride = p->scale_stride; a.shift_stride = p->shift_stride;
+  a.idx = reinterpret_cast<const long long*>(p->idx);
+  a.weight = p->weight; a.bias = p->bias;
+  a.L = p->L; a.D = p->D; a.T = p->T;
+  a.eps = p->eps > 0.f ? p->eps : 1e-6f;
+  a.rms = p->rms;
+  const unsigned grid = static_cast<unsigned>(p->L);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch ((p->D / 8 + h3a::kAdaThreads - 1) / h3a::kAdaThreads) {  // 16-byte chunks per thread
+    case 1: h3a::adaln_norm_kernel<1><<<grid, h3a::kAdaThreads, 0, st>>>(a); break;
+    case 2: h3a::adaln_norm_kernel<2><<<grid, h3a::kAdaThreads, 0, st>>>(a); break;
+    case 3: h3a::adaln_norm_kernel<3><<<grid, h3a::kAdaThreads, 0, st>>>(a); break;
+    case 4: h3a::adaln_norm_kernel<4><<<grid, h3a::kAdaThreads, 0, st>>>(a); break;
+    case 5: h3a::adaln_norm_kernel<5><<<grid, h3a::kAdaThreads, 0, st>>>(a); break;
+    case 6: h3a::adaln_norm_kernel<6><<<grid, h3a::kAdaThreads, 0, st>>>(a); break;
+    case 7: h3a::adaln_norm_kernel<7><<<grid, h3a::kAdaThreads, 0, st>>>(a); break;
+    default: h3a::adaln_norm_kernel<8><<<grid, h3a::kAdaThreads, 0, st>>>(a); break;
+  }
   return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
 }
 

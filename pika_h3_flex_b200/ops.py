@@ -337,6 +337,41 @@ def proj_fwd(
     return out if token_major else out.permute(1, 0, 2)
 
 
+def adaln_norm(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, idx: Optional[torch.Tensor] = None,
+               eps: float = 1e-6, rms: bool = False, weight: Optional[torch.Tensor] = None,
+               bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``norm(x) * (1 + scale[idx]) + shift[idx]`` per token row through ``h3a_adaln_norm``: ``x [L, D]`` bf16,
+    ``scale`` / ``shift`` ``[T, D]`` bf16 (views with their own row stride are fine, e.g. the two chunks of one
+    ``[T, 2 D]`` projection), ``idx [L]`` int64 table row per token (None: row 0 for every token)."""
+    _require_cuda(x, scale, shift)
+    if x.dim() != 2 or scale.dim() != 2 or shift.dim() != 2 or x.dtype != torch.bfloat16 or scale.dtype != torch.bfloat16 or shift.dtype != torch.bfloat16:
+        raise ValueError("x [L, D], scale [T, D] and shift [T, D] must be 2-D bf16")
+    L, D = x.shape
+    if scale.shape != shift.shape or scale.shape[1] != D or x.stride(1) != 1 or scale.stride(1) != 1 or shift.stride(1) != 1:
+        raise ValueError("scale and shift must be [T, D] with contiguous rows")
+    p = _lib.AdaLnParams()
+    keep = []
+    if out is None:
+        out = torch.empty(L, D, dtype=torch.bfloat16, device=x.device)
+    p.x, p.y, p.scale, p.shift = x.data_ptr(), out.data_ptr(), scale.data_ptr(), shift.data_ptr()
+    p.x_stride, p.y_stride, p.scale_stride, p.shift_stride = x.stride(0), out.stride(0), scale.stride(0), shift.stride(0)
+    p.L, p.D, p.T = L, D, scale.shape[0]
+    if idx is not None:
+        if idx.shape != (L,) or idx.dtype != torch.int64 or not idx.is_cuda:
+            raise ValueError("idx must be an int64 [L] device tensor")
+        idx = idx.contiguous()
+        keep.append(idx)
+        p.idx = idx.data_ptr()
+    for name, t in (("weight", weight), ("bias", bias)):
+        if t is not None:
+            t = t.to(torch.float32).contiguous()
+            keep.append(t)
+            setattr(p, name, t.data_ptr())
+    p.rms, p.eps = int(bool(rms)), float(eps)
+    check(_lib.load().h3a_adaln_norm(C.byref(p), _stream()), "h3a_adaln_norm")
+    return out
+
+
 def static_scratch_capacity() -> int:
     """Plan entries (int32) the library's built-in scratch holds: the limit on ``nnz + ceil(Lq/256)`` for
     :func:`attn_fwd_sparse_static`."""

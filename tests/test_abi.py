@@ -41,6 +41,7 @@ def test_struct_sizes_match_header(lib):
     assert C.sizeof(_lib.AttnParams) == 216
     assert C.sizeof(_lib.PrepParams) == 144
     assert C.sizeof(_lib.ProjParams) == 160
+    assert C.sizeof(_lib.AdaLnParams) == 112
 
 
 def test_struct_sizes_match_a_c_compiler(tmp_path):
@@ -53,12 +54,13 @@ def test_struct_sizes_match_a_c_compiler(tmp_path):
         pytest.skip("no gcc")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     src = tmp_path / "sz.c"
-    src.write_text('#include <stdio.h>\n#include "h3attn.h"\nint main(void) { printf("%zu %zu %zu\\n", sizeof(h3a_attn_params), '
-                   'sizeof(h3a_prep_params), sizeof(h3a_proj_params)); return 0; }\n')
+    src.write_text('#include <stdio.h>\n#include "h3attn.h"\nint main(void) { printf("%zu %zu %zu %zu\\n", sizeof(h3a_attn_params), '
+                   'sizeof(h3a_prep_params), sizeof(h3a_proj_params), sizeof(h3a_adaln_params)); return 0; }\n')
     exe = tmp_path / "sz"
     subprocess.run(["gcc", "-I", os.path.join(root, "include"), "-o", str(exe), str(src)], check=True)
     out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
-    assert [int(v) for v in out] == [C.sizeof(_lib.AttnParams), C.sizeof(_lib.PrepParams), C.sizeof(_lib.ProjParams)]
+    assert [int(v) for v in out] == [C.sizeof(_lib.AttnParams), C.sizeof(_lib.PrepParams), C.sizeof(_lib.ProjParams),
+                                     C.sizeof(_lib.AdaLnParams)]
 
 
 def test_proj_argument_validation_without_a_device(lib):

@@ -157,3 +157,14 @@ def test_lora_linear_and_fused_preparation_oracle():
     assert p.shape == (50, 2, 128)
     assert torch.allclose(p.pow(2).mean(-1), torch.ones(50, 2), atol=1e-3)  # unit RMS per head; the rotation keeps it
     assert torch.allclose(p, O.apply_rope(O.rms_norm(y.view(50, 2, 128)), cos, sin))
+
+
+def test_adaln_oracle_against_torch_layer_norm():
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(20, 64, generator=g)
+    scale, shift = 0.2 * torch.randn(3, 64, generator=g), 0.2 * torch.randn(3, 64, generator=g)
+    idx = torch.tensor([0, 1, 2, 1] * 5)
+    ref = torch.nn.functional.layer_norm(x, (64,), eps=1e-6) * (1.0 + scale.index_select(0, idx)) + shift.index_select(0, idx)
+    assert torch.allclose(O.adaln_modulate(x, scale, shift, idx), ref, atol=1e-5)
+    r = O.adaln_modulate(x, torch.zeros(1, 64), torch.zeros(1, 64), None, rms=True)
+    assert torch.allclose(r.pow(2).mean(-1), torch.ones(20), atol=1e-4)
