@@ -218,12 +218,14 @@ int32_t h3a_selftest_wait_timeout(int32_t* status_word, int64_t wait_limit_ns, v
  * x [L, K] and w [N, K] (nn.Linear layout) are bf16 with K contiguous; N = heads * 128.  The LoRA term is optional:
  * lora_t = x A^T [L, R] (the caller computes this thin product) and lora_bs = (alpha / rank) * B [N, R].
  * epilogue H3A_PROJ_STORE writes Y as bf16; H3A_PROJ_PREP applies RMSNorm over each head's 128 columns (times
- * norm_weight when given), then the rotation by `rope` ([L, 64, 2] fp32, optional), then writes bf16.  Output
+ * norm_weight when given), then the rotation by `rope` ([L, 64, 2] fp32, optional), then writes bf16;
+ * H3A_PROJ_PREP_FP8 additionally quantises to e4m3 exactly as h3a_qk_prep does with H3A_PREP_FP8.  Output
  * element (l, head, c) goes to out[l * out_stride_l + head * out_stride_h + c] (strides in elements).
  * Runs on CTA pairs (256 tokens x 256 columns per pair); needs compute capability 10.x.
  */
 #define H3A_PROJ_STORE 0
 #define H3A_PROJ_PREP 1
+#define H3A_PROJ_PREP_FP8 2 /* as PREP, then e4m3 bytes + one absmax / 448 scale per (head, 128-token block) */
 typedef struct h3a_proj_params {
   const void* x;          /* [L, K] bf16 */
   const void* w;          /* [N, K] bf16 */
@@ -232,7 +234,8 @@ typedef struct h3a_proj_params {
   const float* bias;      /* [N] fp32 or NULL */
   const float* rope;      /* H3A_PROJ_PREP: [L, 64, 2] fp32 (cos, sin) or NULL */
   const float* norm_weight; /* H3A_PROJ_PREP: [128] fp32 or NULL (unit weights) */
-  void* out;              /* bf16 */
+  void* out;              /* bf16; H3A_PROJ_PREP_FP8: e4m3 bytes (strides then count bytes) */
+  float* out_scale;       /* H3A_PROJ_PREP_FP8: [N / 128, ceil(L / 128)] fp32, else NULL */
   int64_t x_stride_l, w_stride_n, lora_t_stride_l, lora_bs_stride_n; /* row strides in elements, multiples of 8 */
   int64_t out_stride_l, out_stride_h;
   int32_t L, K, N, R;

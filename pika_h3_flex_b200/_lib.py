@@ -69,7 +69,7 @@ class PrepParams(C.Structure):
 class ProjParams(C.Structure):
     _fields_ = [
         ("x", C.c_void_p), ("w", C.c_void_p), ("lora_t", C.c_void_p), ("lora_bs", C.c_void_p),
-        ("bias", C.c_void_p), ("rope", C.c_void_p), ("norm_weight", C.c_void_p), ("out", C.c_void_p),
+        ("bias", C.c_void_p), ("rope", C.c_void_p), ("norm_weight", C.c_void_p), ("out", C.c_void_p), ("out_scale", C.c_void_p),
         ("x_stride_l", C.c_int64), ("w_stride_n", C.c_int64), ("lora_t_stride_l", C.c_int64), ("lora_bs_stride_n", C.c_int64),
         ("out_stride_l", C.c_int64), ("out_stride_h", C.c_int64),
         ("L", C.c_int32), ("K", C.c_int32), ("N", C.c_int32), ("R", C.c_int32),
@@ -78,7 +78,7 @@ class ProjParams(C.Structure):
     ]
 
 
-PROJ_STORE, PROJ_PREP = 0, 1
+PROJ_STORE, PROJ_PREP, PROJ_PREP_FP8 = 0, 1, 2
 
 
 class AdaLnParams(C.Structure):

@@ -547,11 +547,13 @@ int32_t h3a_debug_set_trace(void* dev_buffer) {
 int32_t h3a_proj_fwd(const h3a_proj_params* p, void* stream) {
   if (!p || !p->x || !p->w || !p->out) return H3A_ERR_ARG;
   if (p->L <= 0 || p->K <= 0 || p->N <= 0 || p->N % 128 != 0 || p->R < 0) return H3A_ERR_SHAPE;
-  if (p->epilogue != H3A_PROJ_STORE && p->epilogue != H3A_PROJ_PREP) return H3A_ERR_ARG;
+  if (p->epilogue != H3A_PROJ_STORE && p->epilogue != H3A_PROJ_PREP && p->epilogue != H3A_PROJ_PREP_FP8) return H3A_ERR_ARG;
+  if (p->epilogue == H3A_PROJ_PREP_FP8 && !p->out_scale) return H3A_ERR_ARG;
   if (p->rope_mode != H3A_ROPE_INTERLEAVED && p->rope_mode != H3A_ROPE_HALF) return H3A_ERR_ARG;
   const bool lora = p->R > 0;
   if (lora && (!p->lora_t || !p->lora_bs)) return H3A_ERR_ARG;
-  if (!aligned16(p->out) || (p->out_stride_l % 8) || (p->out_stride_h % 8) || p->out_stride_l <= 0 || p->out_stride_h <= 0) return H3A_ERR_ALIGN;
+  const int64_t out_unit = p->epilogue == H3A_PROJ_PREP_FP8 ? 16 : 8;  // 16-byte stores
+  if (!aligned16(p->out) || (p->out_stride_l % out_unit) || (p->out_stride_h % out_unit) || p->out_stride_l <= 0 || p->out_stride_h <= 0) return H3A_ERR_ALIGN;
   if ((p->bias && !aligned16(p->bias)) || (p->rope && !aligned16(p->rope)) || (p->norm_weight && !aligned16(p->norm_weight))) return H3A_ERR_ALIGN;
   int32_t rc = check_arch();
   if (rc != H3A_OK) return rc;
@@ -578,8 +580,10 @@ int32_t h3a_proj_fwd(const h3a_proj_params* p, void* stream) {
   a.bias = p->bias; a.rope = p->rope; a.norm_weight = p->norm_weight;
   a.eps = p->eps > 0.f ? p->eps : 1e-6f;
   a.rope_half = p->rope_mode == H3A_ROPE_HALF;
-  a.out = static_cast<__nv_bfloat16*>(p->out);
+  a.out = p->out;
   a.out_stride_l = p->out_stride_l; a.out_stride_h = p->out_stride_h;
+  a.out_scale = p->out_scale;
+  a.nblk = (p->L + 127) / 128;
 
   static std::once_flag once[kMaxDevices];
   static cudaError_t attr_err[kMaxDevices];

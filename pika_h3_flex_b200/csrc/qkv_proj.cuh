@@ -5,6 +5,7 @@
 // R more columns of the contraction.  Epilogue per head (128 output columns of one token, fp32):
 //   kProjStore : bf16 store, head-major [head][token][128]                                    (V)
 //   kProjPrep  : RMSNorm over the 128 columns (x weight), rotation by the (cos, sin) table, store   (Q, K)
+//   kProjPrepFp8: the same, then e4m3 with one absmax / 448 scale per (head, 128-token block)       (Q, K of FP8-QK)
 // so the projection output never makes a round trip through HBM before the preparation.
 //
 // One CTA PAIR (cluster of two, tcgen05 cta_group::2) computes tiles of 256 tokens x 256 output columns: each CTA
@@ -19,6 +20,8 @@
 // The pair protocol (cluster barriers around set-up and tear-down, bounded waits, abort flag raised in the peer
 // too) is the one of the attention kernel on CTA pairs.
 #pragma once
+#include <cuda_fp8.h>
+
 #include "attn_fwd.cuh"
 
 namespace h3a {
@@ -28,8 +31,8 @@ constexpr int kProjStageBytes = 32768;  // 16 KB of X rows + 16 KB of W rows
 constexpr int kProjThreads = 320;
 constexpr int kProjSmemBytes = kProjStages * kProjStageBytes + 1024 + 256;
 
-enum : int { kProjStore = 0, kProjPrep = 1 };
-enum : int { kWaitProjEmpty = 16, kWaitProjFull = 17, kWaitProjAcc = 18, kWaitProjDrain = 19, kWaitProjAccEmpty = 20 };
+enum : int { kProjStore = 0, kProjPrep = 1, kProjPrepFp8 = 2 };
+enum : int { kWaitProjEmpty = 16, kWaitProjFull = 17, kWaitProjAcc = 18, kWaitProjDrain = 19, kWaitProjAccEmpty = 20, kWaitProjMax = 21 };
 
 struct ProjBars {
   uint64_t full[kProjStages];   // rank 0: bytes of both CTAs
@@ -37,6 +40,8 @@ struct ProjBars {
   uint64_t acc_full[2];         // both CTAs: accumulator buffer b is complete
   uint64_t acc_empty[2];        // rank 0: all 16 epilogue warps of the pair have read buffer b
   uint64_t drain;               // rank 0
+  uint64_t qmax[2];             // e4m3 epilogue: the 4 warps of warpgroup h have posted their maxima (one phase per tile)
+  float wmax[2][2][4];          // [tile parity][warpgroup][warp]
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
   uint32_t early_exit;
@@ -53,8 +58,10 @@ struct ProjArgs {
   const float* norm_weight;    // [128] or null
   float eps;
   int rope_half;
-  __nv_bfloat16* out;          // [N / 128][L][128] by strides
+  void* out;                   // bf16 (or e4m3 bytes) [N / 128][L][128] by strides
   long long out_stride_l, out_stride_h;
+  float* out_scale;            // kProjPrepFp8: [N / 128][nblk] absmax / 448 per (head, 128-token block)
+  int nblk;
 };
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kProjThreads, 1)
@@ -85,6 +92,8 @@ qkv_proj_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
       mbar_init(smem_u32(&bars->acc_empty[b]), 16);
     }
     mbar_init(smem_u32(&bars->drain), 1);
+    mbar_init(smem_u32(&bars->qmax[0]), 4);
+    mbar_init(smem_u32(&bars->qmax[1]), 4);
     bars->abort_flag = 0;
     bars->early_exit = (args.wait.status != nullptr && *reinterpret_cast<volatile int*>(args.wait.status) != 0) ? 1u : 0u;
     fence_mbar_init();
@@ -183,22 +192,31 @@ qkv_proj_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
       const int quarter = warp & 3, hsel = warp >> 2;
       const int row = quarter * 32 + lane;
       const uint32_t empty_bar0 = at0(&bars->acc_empty[0]);
+      const bool prep = args.epilogue != kProjStore;
       bool ok = true;
       int it = 0;
       for (int tile = pair; ok && tile < args.n_tiles; tile += n_pairs, ++it) {
-      const int buf = it & 1;
-      const int l = tile_m0(tile) + row;
-      const int n_head0 = tile_n0(tile) + 128 * hsel;  // first output column of this thread's head
-      const uint32_t t_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + 256 * buf + 128 * hsel;
-      ok = warp_wait(wc, smem_u32(&bars->acc_full[buf]), (it >> 1) & 1, kWaitProjAcc);
-      if (ok) {
+        const int buf = it & 1;
+        const int l = tile_m0(tile) + row;
+        const int n_head0 = tile_n0(tile) + 128 * hsel;  // first output column of this thread's head
+        const uint32_t t_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + 256 * buf + 128 * hsel;
+        ok = warp_wait(wc, smem_u32(&bars->acc_full[buf]), (it >> 1) & 1, kWaitProjAcc);
+        if (!ok) break;
         tc_fence_after_sync();
         const bool live = l < args.L && n_head0 < args.N;
         const float4* b4 = reinterpret_cast<const float4*>(args.bias + (args.bias ? n_head0 : 0));
-        // pass 1 (kProjPrep): the row's sum of squares; the accumulator is read again in pass 2, which keeps only
-        // 64 of the 128 columns in registers at a time
+        const float4* w4 = reinterpret_cast<const float4*>(args.norm_weight);
+        const float4* t4 = reinterpret_cast<const float4*>(args.rope + (args.rope ? static_cast<long long>(min(l, args.L - 1)) * 128 : 0));
+        // this warp has read all it needs of the accumulator buffer: hand it back (before the stores)
+        auto release = [&]() {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(empty_bar0 + 8 * buf);
+        };
+        // pass 1 (with normalisation): the row's sum of squares; later passes read the accumulator again and keep
+        // only 64 of the 128 columns in registers at a time
         float rinv = 1.0f;
-        if (args.epilogue == kProjPrep) {
+        if (prep) {
           float ss = 0.f;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -216,22 +234,13 @@ qkv_proj_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
           }
           rinv = rsqrtf(ss * (1.0f / 128.0f) + args.eps);
         }
-        // pass 2: columns [32 g, +32) and [64 + 32 g, +32) together (both rotary pair conventions stay inside)
-        __nv_bfloat16* dst = args.out + static_cast<long long>(n_head0 / 128) * args.out_stride_h + static_cast<long long>(l) * args.out_stride_l;
-        const float4* w4 = reinterpret_cast<const float4*>(args.norm_weight);
-        const float4* t4 = reinterpret_cast<const float4*>(args.rope + (args.rope ? static_cast<long long>(min(l, args.L - 1)) * 128 : 0));
-#pragma unroll
-        for (int g = 0; g < 2; ++g) {
+        // columns [32 g, +32) -> lo and [64 + 32 g, +32) -> hi, finished (bias, norm, weight, rotation): both rotary
+        // pair conventions stay inside one call
+        auto prepare = [&](int g, float (&lo)[32], float (&hi)[32]) {
           uint32_t ra[32], rb[32];
           tmem_ld32(t_addr + 32 * g, ra);
           tmem_ld32(t_addr + 64 + 32 * g, rb);
           tmem_wait_ld();
-          if (g == 1) {  // this warp has read all it needs of the buffer: hand it back before the stores
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(empty_bar0 + 8 * buf);
-          }
-          float lo[32], hi[32];
 #pragma unroll
           for (int c = 0; c < 32; c += 4) {
             float4 ba = make_float4(0.f, 0.f, 0.f, 0.f), bb = ba;
@@ -240,7 +249,7 @@ qkv_proj_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
               bb = b4[(64 + 32 * g + c) >> 2];
             }
             float4 wa = make_float4(1.f, 1.f, 1.f, 1.f), wb = wa;
-            if (args.epilogue == kProjPrep && args.norm_weight) {
+            if (prep && args.norm_weight) {
               wa = w4[(32 * g + c) >> 2];
               wb = w4[(64 + 32 * g + c) >> 2];
             }
@@ -253,7 +262,7 @@ qkv_proj_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
             hi[c + 2] = (__uint_as_float(rb[c + 2]) + bb.z) * rinv * wb.z;
             hi[c + 3] = (__uint_as_float(rb[c + 3]) + bb.w) * rinv * wb.w;
           }
-          if (args.epilogue == kProjPrep && args.rope && live) {
+          if (prep && args.rope && live) {
             if (args.rope_half) {
               // pair e = (e, e + 64), e = 32 g + c: table entries 32 g .. 32 g + 31
 #pragma unroll
@@ -276,20 +285,81 @@ qkv_proj_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
               }
             }
           }
-          if (live) {
+        };
+        const long long out_off = static_cast<long long>(n_head0 / 128) * args.out_stride_h + static_cast<long long>(l) * args.out_stride_l;
+        if (args.epilogue != kProjPrepFp8) {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(args.out) + out_off;
 #pragma unroll
-            for (int c = 0; c < 32; c += 8) {
-              uint4 w;
-              w.x = pack_bf16x2(lo[c], lo[c + 1]); w.y = pack_bf16x2(lo[c + 2], lo[c + 3]);
-              w.z = pack_bf16x2(lo[c + 4], lo[c + 5]); w.w = pack_bf16x2(lo[c + 6], lo[c + 7]);
-              *reinterpret_cast<uint4*>(dst + 32 * g + c) = w;
-              w.x = pack_bf16x2(hi[c], hi[c + 1]); w.y = pack_bf16x2(hi[c + 2], hi[c + 3]);
-              w.z = pack_bf16x2(hi[c + 4], hi[c + 5]); w.w = pack_bf16x2(hi[c + 6], hi[c + 7]);
-              *reinterpret_cast<uint4*>(dst + 64 + 32 * g + c) = w;
+          for (int g = 0; g < 2; ++g) {
+            float lo[32], hi[32];
+            prepare(g, lo, hi);
+            if (g == 1) release();
+            if (live) {
+#pragma unroll
+              for (int c = 0; c < 32; c += 8) {
+                uint4 w;
+                w.x = pack_bf16x2(lo[c], lo[c + 1]); w.y = pack_bf16x2(lo[c + 2], lo[c + 3]);
+                w.z = pack_bf16x2(lo[c + 4], lo[c + 5]); w.w = pack_bf16x2(lo[c + 6], lo[c + 7]);
+                *reinterpret_cast<uint4*>(dst + 32 * g + c) = w;
+                w.x = pack_bf16x2(hi[c], hi[c + 1]); w.y = pack_bf16x2(hi[c + 2], hi[c + 3]);
+                w.z = pack_bf16x2(hi[c + 4], hi[c + 5]); w.w = pack_bf16x2(hi[c + 6], hi[c + 7]);
+                *reinterpret_cast<uint4*>(dst + 64 + 32 * g + c) = w;
+              }
+            }
+          }
+        } else {
+          // e4m3 with one absmax scale per (head, 128-token block) = this warpgroup's 128 rows x 128 columns: a pass
+          // for the block maximum (4 warps meet through shared memory and a bounded mbarrier), a pass to quantise
+          float amax = 0.f;
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            float lo[32], hi[32];
+            prepare(g, lo, hi);
+            if (live) {
+#pragma unroll
+              for (int c = 0; c < 32; ++c) amax = fmaxf(amax, fmaxf(fabsf(lo[c]), fabsf(hi[c])));
+            }
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+          if (lane == 0) {
+            bars->wmax[it & 1][hsel][quarter] = amax;
+            mbar_arrive(smem_u32(&bars->qmax[hsel]));
+          }
+          ok = warp_wait(wc, smem_u32(&bars->qmax[hsel]), it & 1, kWaitProjMax);
+          if (!ok) break;
+          const float bm = fmaxf(fmaxf(bars->wmax[it & 1][hsel][0], bars->wmax[it & 1][hsel][1]),
+                                 fmaxf(bars->wmax[it & 1][hsel][2], bars->wmax[it & 1][hsel][3]));
+          const float scale = bm > 0.f ? bm / 448.0f : 1.0f;
+          const float inv = 1.0f / scale;
+          if (row == 0 && n_head0 < args.N && tile_m0(tile) < args.L)
+            args.out_scale[static_cast<long long>(n_head0 / 128) * args.nblk + tile_m0(tile) / 128] = scale;
+          uint8_t* dst = static_cast<uint8_t*>(args.out) + out_off;
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            float lo[32], hi[32];
+            prepare(g, lo, hi);
+            if (g == 1) release();
+            if (live) {
+#pragma unroll
+              for (int c = 0; c < 32; c += 16) {
+                uint32_t wl[4], wh[4];
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                  const int e = c + 4 * x;
+                  const auto q2 = [&](float a, float b) {
+                    return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(
+                        make_float2(fminf(fmaxf(a * inv, -448.f), 448.f), fminf(fmaxf(b * inv, -448.f), 448.f)), __NV_SATFINITE, __NV_E4M3));
+                  };
+                  wl[x] = q2(lo[e], lo[e + 1]) | (q2(lo[e + 2], lo[e + 3]) << 16);
+                  wh[x] = q2(hi[e], hi[e + 1]) | (q2(hi[e + 2], hi[e + 3]) << 16);
+                }
+                *reinterpret_cast<uint4*>(dst + 32 * g + c) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+                *reinterpret_cast<uint4*>(dst + 64 + 32 * g + c) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+              }
             }
           }
         }
-      }
       }  // tiles
     }
   }

@@ -279,12 +279,14 @@ def proj_fwd(
     status_word: Optional[torch.Tensor] = None,
     wait_limit_ns: int = 0,
     token_major: bool = False,
+    fp8: bool = False,
 ):
     """One of the Q / K / V (or, with ``token_major``, the output) projections through ``h3a_proj_fwd``: ``x [L, K]`` bf16 times ``weight [N, K]`` bf16
     (``nn.Linear`` layout, N = heads x 128), plus ``lora_t [L, R] @ lora_bs [N, R]^T`` and ``bias [N]`` when given;
     with ``prep`` the per-head RMSNorm (x ``norm_weight``) and the rotation by ``rope [L, 64, 2]`` run in the
     epilogue.  Returns a logical ``[L, heads, 128]`` bf16 view of head-major storage, like :func:`qk_prep`; with
-    ``token_major`` a plain contiguous ``[L, N]`` tensor (what ``to_out`` produces)."""
+    ``token_major`` a plain contiguous ``[L, N]`` tensor (what ``to_out`` produces).  ``fp8`` (with ``prep``):
+    e4m3 bytes plus per-(head, 128-token block) scales, returned as ``(out_uint8, scale [heads, ceil(L/128)])``."""
     _require_cuda(x, weight)
     lib = _lib.load()
     if x.dim() != 2 or weight.dim() != 2 or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
@@ -311,7 +313,9 @@ def proj_fwd(
         bias = bias.to(torch.float32).contiguous()
         keep.append(bias)
         p.bias = bias.data_ptr()
-    p.epilogue = _lib.PROJ_PREP if prep else _lib.PROJ_STORE
+    if fp8 and (not prep or token_major):
+        raise ValueError("fp8 output is the quantised preparation: needs prep=True and head-major output")
+    p.epilogue = (_lib.PROJ_PREP_FP8 if fp8 else _lib.PROJ_PREP) if prep else _lib.PROJ_STORE
     if prep:
         if rope is not None:
             if rope.shape != (L, 64, 2) or rope.dtype != torch.float32 or not rope.is_contiguous():
@@ -328,12 +332,18 @@ def proj_fwd(
         out = torch.empty(L, N, dtype=torch.bfloat16, device=x.device)
         p.out, p.out_stride_l, p.out_stride_h = out.data_ptr(), N, HEAD_DIM
     else:
-        out = torch.empty(H, L, HEAD_DIM, dtype=torch.bfloat16, device=x.device)
+        out = torch.empty(H, L, HEAD_DIM, dtype=torch.uint8 if fp8 else torch.bfloat16, device=x.device)
         p.out, p.out_stride_l, p.out_stride_h = out.data_ptr(), HEAD_DIM, L * HEAD_DIM
+    scale = None
+    if fp8:
+        scale = torch.empty(H, (L + TILE - 1) // TILE, dtype=torch.float32, device=x.device)
+        p.out_scale = scale.data_ptr()
     if status_word is not None:
         p.status_word = status_word.data_ptr()
     p.wait_limit_ns = int(wait_limit_ns)
     check(lib.h3a_proj_fwd(C.byref(p), _stream()), "h3a_proj_fwd")
+    if fp8:
+        return out.permute(1, 0, 2), scale
     return out if token_major else out.permute(1, 0, 2)
 
 

@@ -110,9 +110,10 @@ class B200AttnProcessor:
                   tokens ``[r*S/P, (r+1)*S/P)``; rotary inputs are the rows of the same shard) and so is the result.
                   The projections stay token-local; the exchange of Q runs under the K projection and that of K
                   under the V projection.  Cross-attention needs no exchange (keys and values are replicated).
-    fused_projection  run to_q / to_k / to_v through the library's own GEMM with the norm + rotation in its epilogue
-                  (bf16 modes; plain or LoRA-wrapped Linears that ``_linear_parts`` recognises, bf16 weights and
-                  activations).  Anything else goes through the module call and the separate preparation kernel.
+    fused_projection  run to_q / to_k / to_v (and to_out.0) through the library's own GEMM with the norm + rotation
+                  (+ e4m3 quantisation in FP8-QK mode) in its epilogue: plain or LoRA-wrapped Linears that
+                  ``_linear_parts`` recognises, bf16 weights and activations.  Anything else goes through the module
+                  call and the separate preparation kernel.
     """
 
     def __init__(self, mode: str = "dense_bf16", block_index: Optional[ops.BlockIndex] = None, rope_half: bool = False,
@@ -195,7 +196,7 @@ class B200AttnProcessor:
 
     # ---- fused projections
     def _fusable(self, attn, x, ctx):
-        if not self.fused_projection or MODES[self.mode] == _lib.MODE_FP8_QK:
+        if not self.fused_projection:
             return None
         if x.dtype != torch.bfloat16 or ctx.dtype != torch.bfloat16:
             return None
@@ -204,8 +205,9 @@ class B200AttnProcessor:
             return None
         return parts
 
-    def _fused(self, mod, parts, x2d, prep, rope, norm_w, eps):
-        """One projection through the library's GEMM; the thin LoRA product ``x A^T`` stays a torch matmul."""
+    def _fused(self, mod, parts, x2d, prep, rope, norm_w, eps, fp8=False):
+        """One projection through the library's GEMM; the thin LoRA product ``x A^T`` stays a torch matmul.
+        ``fp8``: returns ``(e4m3 bytes, block scales)``."""
         w, bias, a, b, scale = parts
         t = bs = None
         if a is not None:
@@ -214,7 +216,7 @@ class B200AttnProcessor:
             bs = self._scaled_b.get(key)
             if bs is None:  # (alpha / rank) * B, static at inference: scaled once per module
                 bs = self._scaled_b[key] = (b.float() * scale).to(torch.bfloat16).contiguous()
-        return ops.proj_fwd(x2d, w, bias, t, bs, prep=prep, rope=rope, norm_weight=norm_w, eps=eps, rope_half=self.rope_half)
+        return ops.proj_fwd(x2d, w, bias, t, bs, prep=prep, rope=rope, norm_weight=norm_w, eps=eps, rope_half=self.rope_half, fp8=fp8)
 
     def attention_fused(self, attn, parts, hidden_states, ctx, rope, cross: bool):
         """Projections with the preparation in their epilogue, then attention (one GPU)."""
@@ -224,10 +226,12 @@ class B200AttnProcessor:
             mode, bi = _lib.MODE_DENSE_BF16, None
         qw, kw, eps, bound = self._norm_and_bound(attn, mode)
         x2d, c2d = hidden_states[0], ctx[0]
-        q = self._fused(attn.to_q, parts[0], x2d, True, None if cross else rope, qw, eps)
-        k = self._fused(attn.to_k, parts[1], c2d, True, None if cross else rope, kw, eps)
+        fp8 = mode == _lib.MODE_FP8_QK
+        q = self._fused(attn.to_q, parts[0], x2d, True, None if cross else rope, qw, eps, fp8)
+        k = self._fused(attn.to_k, parts[1], c2d, True, None if cross else rope, kw, eps, fp8)
         v = self._fused(attn.to_v, parts[2], c2d, False, None, None, eps)
-        return ops.attn_fwd(q, k, v, mode, None, None, bi, logit_bound=bound)
+        (q, qs), (k, ks) = (q, k) if fp8 else ((q, None), (k, None))
+        return ops.attn_fwd(q, k, v, mode, qs, ks, bi, logit_bound=bound)
 
     def attention_sequence_parallel(self, attn, hidden_states, rope):
         """Self-attention with the sequence sharded over the group: each projection is computed when the previous
@@ -237,9 +241,10 @@ class B200AttnProcessor:
         parts = self._fusable(attn, hidden_states, hidden_states)
         if parts is not None:
             x2d = hidden_states[0]
+            fp8 = MODES[self.mode] == _lib.MODE_FP8_QK
             return self._ulysses.run(
-                lambda: self._fused(attn.to_q, parts[0], x2d, True, rope, qw, eps),
-                lambda: self._fused(attn.to_k, parts[1], x2d, True, rope, kw, eps),
+                lambda: self._fused(attn.to_q, parts[0], x2d, True, rope, qw, eps, fp8),
+                lambda: self._fused(attn.to_k, parts[1], x2d, True, rope, kw, eps, fp8),
                 lambda: self._fused(attn.to_v, parts[2], x2d, False, None, None, eps),
                 None, logit_bound=bound, prepared=True)
 

@@ -235,16 +235,17 @@ class UlyssesAttention:
             rope_half: bool = False, logit_bound: Optional[float] = None, prepared: bool = False) -> torch.Tensor:
         """``q_fn() / k_fn() / v_fn()`` return this rank's ``[L/P, H, 128]`` bf16 projections; they are called in
         that order, each after the previous tensor's exchange has been started.  ``prepared``: Q and K arrive
-        normalised and rotated already (the fused projection does that in its epilogue), bf16 modes only."""
+        normalised and rotated already (the fused projection does that in its epilogue); in FP8-QK mode the two
+        callables return ``(e4m3 bytes, block scales)``."""
         world = dist.get_world_size(self.group)
         fp8 = self.mode == _lib.MODE_FP8_QK
 
-        if prepared and fp8:
-            raise ValueError("prepared operands are bf16: FP8-QK needs the quantising preparation")
-
         def prep(x, which):  # token-local work first: the wire then carries final operands
-            if prepared:
-                return x, None
+            if prepared:  # FP8-QK: the callable returned (e4m3 bytes, block scales)
+                xp, xs = x if isinstance(x, tuple) else (x, None)
+                if fp8 and xs is None:
+                    raise ValueError("prepared FP8-QK operands come with their block scales")
+                return xp, xs
             a, b = (x, None) if which == 0 else (None, x)
             ra, rb = (rope, None) if which == 0 else (None, rope)
             if self.prep_fn is not None:
@@ -254,20 +255,20 @@ class UlyssesAttention:
             return (r[0], r[2]) if which == 0 else (r[1], r[3])
 
         q = q_fn()
-        Ls, H, _ = q.shape
+        Ls, H, _ = (q[0] if isinstance(q, tuple) else q).shape
         if fp8 and Ls % ops.TILE:
             raise ValueError("FP8 mode under Ulysses needs the local sequence length to be a multiple of 128")
         Hp = padded_heads(H, world)
         hp = Hp // world
         # The local head slots are handled in groups: while one group is in attention the next group's operands
         # are arriving and the previous group's output is leaving.
-        groups = self._head_slot_groups(hp, world * Ls, q)
+        groups = self._head_slot_groups(hp, world * Ls, q[0] if isinstance(q, tuple) else q)
         inbound = [[] for _ in groups]
         scale_fetch = [None, None]
         heads = [None, None, None]
         for which, fn in enumerate((None, k_fn, v_fn)):
             x = q if which == 0 else fn()
-            if tuple(x.shape) != (Ls, H, ops.HEAD_DIM):
+            if tuple((x[0] if isinstance(x, tuple) else x).shape) != (Ls, H, ops.HEAD_DIM):
                 raise ValueError("q, k, v must be [L/P, H, 128] shards of the same shape")
             if which < 2:
                 xp, xs = prep(x, which)

@@ -40,7 +40,7 @@ def test_struct_sizes_match_header(lib):
     # natural-alignment sizes of the two parameter structs as a C compiler lays them out
     assert C.sizeof(_lib.AttnParams) == 216
     assert C.sizeof(_lib.PrepParams) == 144
-    assert C.sizeof(_lib.ProjParams) == 160
+    assert C.sizeof(_lib.ProjParams) == 168
     assert C.sizeof(_lib.AdaLnParams) == 112
 
 

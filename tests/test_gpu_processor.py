@@ -176,7 +176,7 @@ def test_fused_projection_matches_module_calls(setup, wrapper):
     ys = B200AttnProcessor("block_sparse", bi.to("cuda"), fused_projection=True, rope_half=True)(attn, x, position_ids=pos.cuda())
     ym = B200AttnProcessor("block_sparse", bi.to("cuda"), rope_half=True)(attn, x, position_ids=pos.cuda())
     assert float((ys.float() - ym.float()).abs().max()) < 3e-2
-    # FP8-QK keeps the separate (quantising) preparation even when fusion is asked for
+    # FP8-QK: the quantisation runs in the GEMM epilogue too
     y8 = B200AttnProcessor("fp8_qk", fused_projection=True)(attn, x, position_ids=pos.cuda())
     assert float(((y8.float() - ref.float()).norm() / ref.float().norm())) < 8e-2
 
@@ -238,11 +238,11 @@ with torch.no_grad():
         err = float((shard.float() - whole[:, sl].float()).abs().max())
         print(rank, mode, err, flush=True)
         ok = ok and tuple(shard.shape) == (1, Ss, 256) and err < (6e-2 if mode == "fp8_qk" else 2e-2)
-        if mode != "fp8_qk":  # projections through the library's GEMM, prepared operands on the wire
-            fused = B200AttnProcessor(mode, idx, sequence_parallel=True, fused_projection=True)(attn, x[:, sl].contiguous(), position_ids=pos[sl].cuda())
-            errf = float((fused.float() - whole[:, sl].float()).abs().max())
-            print(rank, mode, "fused", errf, flush=True)
-            ok = ok and errf < 3e-2
+        # projections through the library's GEMM, prepared operands on the wire
+        fused = B200AttnProcessor(mode, idx, sequence_parallel=True, fused_projection=True)(attn, x[:, sl].contiguous(), position_ids=pos[sl].cuda())
+        errf = float((fused.float() - whole[:, sl].float()).abs().max())
+        print(rank, mode, "fused", errf, flush=True)
+        ok = ok and errf < (8e-2 if mode == "fp8_qk" else 3e-2)
     text = torch.randn(1, 77, 256, device="cuda").bfloat16()
     c_whole = B200AttnProcessor()(attn, x, encoder_hidden_states=text)
     c_shard = B200AttnProcessor(sequence_parallel=True)(attn, x[:, sl].contiguous(), encoder_hidden_states=text)

@@ -100,3 +100,27 @@ def test_projection_token_major_output(h):
     assert out.shape == (L, H * 128) and out.is_contiguous()
     s = O.error_stats(out.float().cpu(), ref)
     assert s["rel_l2"] <= 5e-3 and s["max_abs"] <= 3e-2, s
+
+
+@pytest.mark.parametrize("L,K,H", [(700, 512, 3), (4100, 320, 20)])
+def test_projection_with_fused_fp8_quantisation(h, L, K, H):
+    """Epilogue H3A_PROJ_PREP_FP8: the prepared rows as e4m3 with per-(head, 128-token block) absmax scales, the
+    layout h3a_qk_prep produces; dequantised they must match the oracle's preparation within e4m3 resolution, and
+    the scales must be the block maxima / 448."""
+    x, w, b, a, bm = _inputs(L, K, H, 64, True, 90 + L)
+    t = _lora_t(x, a)
+    frames = max(1, (L - 40) // 16)
+    pos = O.make_positions((frames, 4, 4), L - frames * 16)
+    cos, sin = O.rope_table(pos)
+    y = O.lora_linear(x, w, b, None, None) + t.float() @ bm.float().t()
+    ref = O.apply_rope(O.rms_norm(y.view(L, H, 128)), cos, sin, True)
+    rope = torch.stack([cos, sin], dim=-1).float().contiguous().cuda()
+    out, scale = h.proj_fwd(x.cuda(), w.cuda(), b.cuda(), t.cuda(), bm.cuda(), prep=True, rope=rope, fp8=True)
+    assert out.dtype == torch.uint8 and out.shape == (L, H, 128) and scale.shape == (H, (L + 127) // 128)
+    deq = O.dequantize_blocks(out.cpu().view(torch.float8_e4m3fn).float(), scale.cpu())
+    s = O.error_stats(deq, ref)
+    assert s["rel_l2"] <= 4e-2 and s["max_abs"] <= 0.3, s  # e4m3: 3 mantissa bits, values up to ~5
+    nb = (L + 127) // 128
+    pad = torch.zeros(nb * 128 - L, H, 128)
+    blockmax = torch.cat([ref, pad]).abs().view(nb, 128, H, 128).amax(dim=(1, 3)).t()  # [H, nb]
+    assert torch.allclose(scale.cpu(), blockmax / 448.0, rtol=2e-2, atol=1e-6)
