@@ -1,4 +1,4 @@
-// Dense forward attention on CTA PAIRS: two CTAs on neighbouring SMs (a cluster of two) run every MMA
+// Forward attention on CTA PAIRS (fixed softmax reference): two CTAs on neighbouring SMs (a cluster of two) run every MMA
 // together (tcgen05 cta_group::2, M = 256 = 128 query rows in each CTA), so each CTA stages only HALF of every
 // K and V tile in its shared memory and fetches half of the B operand per MMA.  The single-CTA kernel is bound by
 // shared-memory bandwidth (operand fetch plus TMA writes); the pair moves 30 % fewer bytes through each SM's
@@ -27,6 +27,9 @@
 //   V stage       : [128 keys][64 dims]                       - this CTA's half of the output columns
 // TMEM: as in the single-CTA kernel, at the same addresses in both CTAs.
 //
+// Dense launches may split the key range for the pairs of the last, partly filled wave (AttnArgs::split_begin):
+// those pairs store un-normalised partial rows and combine_partials_kernel adds the shares.
+//
 // Cluster protocol.  A cluster barrier after the mbarrier set-up (no remote arrive or TMA completion may reach
 // an uninitialised barrier) and one before TMEM is freed (no CTA leaves while its peer may still signal its
 // barriers or the pair's MMAs may still run).  Every thread reaches both on every path; all other waits are
@@ -36,7 +39,10 @@
 
 namespace h3a {
 
-constexpr int kPairStages = 8;
+#ifndef H3A_PAIR_STAGES
+#define H3A_PAIR_STAGES 8
+#endif
+constexpr int kPairStages = H3A_PAIR_STAGES;
 constexpr int kPairStageBytes = 16384;
 constexpr int kPairThreads = AttnLayout<true>::kThreads;
 

@@ -26,7 +26,10 @@
 
 namespace h3a {
 
-constexpr int kProjStages = 6;
+#ifndef H3A_PROJ_STAGES
+#define H3A_PROJ_STAGES 6
+#endif
+constexpr int kProjStages = H3A_PROJ_STAGES;
 constexpr int kProjStageBytes = 32768;  // 16 KB of X rows + 16 KB of W rows
 constexpr int kProjThreads = 320;
 constexpr int kProjSmemBytes = kProjStages * kProjStageBytes + 1024 + 256;
