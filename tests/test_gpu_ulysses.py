@@ -122,3 +122,74 @@ def test_ulysses_multi_gpu_exchange_matches_oracle(world, heads, tmp_path):
             o, _ = p.communicate()
         outs.append(o.decode(errors="replace"))
     assert all(p.returncode == 0 for p in procs), "\n".join(x[-2000:] for x in outs)
+
+
+_HOST_CHILD = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, {root!r})
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+import pika_h3_flex_b200 as h
+from pika_h3_flex_b200.host_path import HostUlyssesAttention
+from oracle import oracle as O
+grid, n_audio, H = (4, 8, 12), 128, {heads}
+pos = O.make_positions(grid, n_audio)
+L = pos.shape[0]
+Ls = L // world
+sl = slice(rank * Ls, (rank + 1) * Ls)
+rope = h.rope_table(pos[sl].cuda())
+ok = True
+for mode_name in ("dense", "block_sparse"):
+    csr, bi, mode = None, None, h.MODE_DENSE_BF16
+    if mode_name == "block_sparse":
+        bih = h.build_block_index(grid, n_audio, (1, 2, 2))
+        csr, bi, mode = (bih.row_ptr.numpy(), bih.col_idx.numpy()), bih.to("cuda"), h.MODE_BLOCK_SPARSE
+    ha = HostUlyssesAttention(Ls, H, mode, bi, slot_groups={groups!r})
+    for seed in (35, 36):  # twice through the same staging buffers, different values
+        q, k, v = (t.bfloat16() for t in O.seeded_qkv(L, H, seed=seed))
+        ref = O.joint_attention(q.float(), k.float(), v.float(), pos, mode_name, csr=csr)[sl]
+        hq, hk, hv = (t[sl].contiguous().pin_memory() for t in (q, k, v))
+        ho = torch.full((Ls, H, 128), float("nan"), dtype=torch.bfloat16).pin_memory()
+        ha(hq, hk, hv, rope, ho)
+        torch.cuda.synchronize()
+        st = O.error_stats(ho.float(), ref)
+        print(rank, mode_name, seed, st, flush=True)
+        ok = ok and bool(torch.isfinite(ho.float()).all()) and st["rel_l2"] <= 1e-2
+flag = torch.tensor([1 if ok else 0], device="cuda")
+dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+dist.destroy_process_group()
+sys.exit(0 if int(flag.item()) == 1 else 1)
+"""
+
+
+@pytest.mark.parametrize("world,heads,groups", [(2, 6, [1, 2]), (2, 5, [1, 1, 1]), (4, 6, None)])
+def test_host_buffer_path_under_ulysses(world, heads, groups, tmp_path):
+    """Ranks as child processes: pinned host shards in, pinned host shard out, pipelined over head-slot groups with
+    round-robin head assignment (5 heads on 2 ranks and 6 on 4 pad); every rank must get the oracle's rows."""
+    import subprocess
+    import sys
+
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "child.py"
+    script.write_text(_HOST_CHILD.format(root=root, heads=heads, groups=groups))
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                   NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT))
+    outs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o, _ = p.communicate()
+        outs.append(o.decode(errors="replace"))
+    assert all(p.returncode == 0 for p in procs), "\n".join(x[-2000:] for x in outs)
