@@ -115,3 +115,38 @@ def test_ulysses_block_sparse(tmp_path):
 
 def test_ulysses_rejects_bad_shapes():
     assert padded_heads(40, 8) == 40 and padded_heads(6, 4) == 8 and padded_heads(1, 8) == 8
+
+
+def test_round_robin_head_assignment_of_the_host_path_simulated():
+    """The index arithmetic of the host-buffer Ulysses pipeline (heads dealt round-robin, blocks packed per peer,
+    placed per source rank, unpacked per owner) with all ranks simulated in one process: after the inbound
+    exchange rank p must hold heads j*P + p over ALL tokens, and the outbound exchange must restore every rank's
+    token shard of every head.  5 heads on 2 ranks and 6 on 4 pad."""
+    for P, H in ((2, 6), (2, 5), (4, 6), (3, 7)):
+        Ls, Cc = 4, 2
+        hp = (H + P - 1) // P
+        full = torch.arange(P * Ls * H * Cc, dtype=torch.float32).view(P * Ls, H, Cc)  # [token, head, c]
+        shards = [full[r * Ls : (r + 1) * Ls] for r in range(P)]
+        for j0, n in ((0, 1), (1, hp - 1)) if hp > 1 else ((0, 1),):
+            h0, h1 = j0 * P, min((j0 + n) * P, H)
+
+            def pack(x_hm):  # HostUlyssesAttention._pack
+                if x_hm.shape[0] < n * P:
+                    x_hm = torch.cat([x_hm, x_hm.new_zeros(n * P - x_hm.shape[0], Ls, Cc)], dim=0)
+                return x_hm.view(n, P, Ls, Cc).permute(1, 0, 2, 3).contiguous()
+
+            sends = [pack(shards[r][:, h0:h1].permute(1, 0, 2).contiguous()) for r in range(P)]
+            # all_to_all: rank p receives sends[src][p] from every src
+            recvs = [torch.stack([sends[src][p] for src in range(P)]) for p in range(P)]
+            outs_send = []
+            for p in range(P):
+                got = recvs[p].permute(1, 0, 2, 3).reshape(n, P * Ls, Cc)  # [slot, all tokens, c]
+                for j in range(n):
+                    h = (j0 + j) * P + p
+                    want = full[:, h] if h < H else torch.zeros(P * Ls, Cc)
+                    assert torch.equal(got[j], want), (P, H, p, j)
+                outs_send.append(got.view(n, P, Ls, Cc).permute(1, 0, 2, 3).contiguous())  # [dest rank, slot, its tokens, c]
+            for r in range(P):
+                back = torch.stack([outs_send[p][r] for p in range(P)])  # [owner p, slot j, my tokens, c]
+                heads = back.permute(1, 0, 2, 3).reshape(n * P, Ls, Cc)[: h1 - h0]
+                assert torch.equal(heads.permute(1, 0, 2), shards[r][:, h0:h1]), (P, H, r)
