@@ -383,35 +383,39 @@ def run_ours(args):
         e2e = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                "note": "the multi-GPU host-buffer path covers the dense bf16 and block-sparse self-attention workloads"}
     else:
-        # every rank's shard comes from its own pinned host buffers and goes back to one
-        from pika_h3_flex_b200.host_path import HostUlyssesAttention
+        try:
+            # every rank's shard comes from its own pinned host buffers and goes back to one
+            from pika_h3_flex_b200.host_path import HostUlyssesAttention
 
-        hq, hk, hv = (torch.empty(Ls, H, 128, dtype=torch.bfloat16).pin_memory() for _ in range(3))
-        for dst, src_t in ((hq, q), (hk, k), (hv, v)):
-            dst.copy_(src_t)
-        ho = torch.empty(Ls, H, 128, dtype=torch.bfloat16).pin_memory()
-        host_attn = HostUlyssesAttention(Ls, H, mode, bi)
-        barrier()
-        n_e2e = max(2, min(args.steps, 5))
-        for _ in range(2):
-            host_attn(hq, hk, hv, rope, ho)
-        barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(n_e2e):
-            host_attn(hq, hk, hv, rope, ho)
-        b.record()
-        barrier()
-        t = torch.tensor([a.elapsed_time(b) / n_e2e], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-        nbytes = L * H * 128 * 2  # over all ranks
-        e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": 3 * nbytes,
-               "d2h_bytes_per_step": nbytes, "ms_per_step": e2e_ms, "steps": n_e2e,
-               "api": "HostUlyssesAttention: per rank, H2D of its shard, prep, exchanges, attention and D2H pipelined over head-slot groups %s"
-                      % host_attn.slot_groups}
-        if h3.read_status(status) != 0:
-            raise SystemExit(f"device wait gave up: status 0x{h3.read_status(status):x}")
+            hq, hk, hv = (torch.empty(Ls, H, 128, dtype=torch.bfloat16).pin_memory() for _ in range(3))
+            for dst, src_t in ((hq, q), (hk, k), (hv, v)):
+                dst.copy_(src_t)
+            ho = torch.empty(Ls, H, 128, dtype=torch.bfloat16).pin_memory()
+            host_attn = HostUlyssesAttention(Ls, H, mode, bi)
+            barrier()
+            n_e2e = max(2, min(args.steps, 5))
+            for _ in range(2):
+                host_attn(hq, hk, hv, rope, ho)
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n_e2e):
+                host_attn(hq, hk, hv, rope, ho)
+            b.record()
+            barrier()
+            t = torch.tensor([a.elapsed_time(b) / n_e2e], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+            nbytes = L * H * 128 * 2  # over all ranks
+            e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": 3 * nbytes,
+                   "d2h_bytes_per_step": nbytes, "ms_per_step": e2e_ms, "steps": n_e2e,
+                   "api": "HostUlyssesAttention: per rank, H2D of its shard, prep, exchanges, attention and D2H pipelined over head-slot groups %s"
+                          % host_attn.slot_groups}
+            if h3.read_status(status) != 0:
+                raise SystemExit(f"device wait gave up: status 0x{h3.read_status(status):x}")
+        except (RuntimeError, ValueError, TypeError, AttributeError, NotImplementedError) as exc:  # keep the kernel-side line
+            e2e = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                   "note": "multi-GPU host-buffer path failed: %r" % (exc,)}
 
     if world > 1:
         dist.barrier()
