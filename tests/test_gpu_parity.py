@@ -252,15 +252,20 @@ def _full_inputs(name, H):
     return grid, n_audio, L, q, k, v
 
 
-def test_config1_full_length_properties(h):
-    """480p-like length (49,384 tokens, tail tile of 104), 8 of the 40 heads to bound host time."""
+@pytest.mark.parametrize("bounded", [False, True])
+def test_config1_full_length_properties(h, bounded):
+    """480p-like length (49,384 tokens, tail tile of 104), 8 of the 40 heads to bound host time: with the running
+    maximum (single-CTA kernel) and with the logit bound of the normalised operands (CTA pairs, split last wave)."""
+    from pika_h3_flex_b200.ops import normed_logit_bound
+
     H = 8
+    bound = normed_logit_bound() if bounded else 0.0
     grid, n_audio, L, q, k, v = _full_inputs("cfg1", H)
     pos = O.make_positions(grid, n_audio)
     tab = h.rope_table(dev(pos))
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     qp, kp, _, _ = h.qk_prep(q, k, tab, tab)
-    out, lse = h.attn_fwd(qp, kp, v, return_lse=True, status_word=status)
+    out, lse = h.attn_fwd(qp, kp, v, return_lse=True, status_word=status, logit_bound=bound)
     assert h.read_status(status) == 0
     # (1) sampled query rows against the fp64 oracle
     rows = torch.cat([torch.arange(0, L, 997), torch.tensor([L - 1, L - 104, L - 105, 1023, 1024])])
@@ -270,36 +275,42 @@ def test_config1_full_length_properties(h):
     check(out[rows][:, hs], ref.float())
     # (2) softmax rows sum to one: with V = 1 every output element is 1
     ones = torch.ones_like(v)
-    o1 = h.attn_fwd(qp, kp, ones)
+    o1 = h.attn_fwd(qp, kp, ones, logit_bound=bound)
     assert float((o1.float() - 1).abs().max()) <= 8e-3
     # (3) key order does not matter: permute K and V rows together
     perm = torch.randperm(L, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
     kperm = kp.permute(1, 0, 2)[:, perm].contiguous().permute(1, 0, 2)
-    o2, lse2 = h.attn_fwd(qp, kperm, v[perm].contiguous(), return_lse=True)
+    o2, lse2 = h.attn_fwd(qp, kperm, v[perm].contiguous(), return_lse=True, logit_bound=bound)
     assert float((o2.float() - out.float()).abs().max()) <= 4e-3
     assert float((lse2 - lse).abs().max()) <= 1e-3
     # (4) linear in V
-    o3 = h.attn_fwd(qp, kp, (2 * v).contiguous())
+    o3 = h.attn_fwd(qp, kp, (2 * v).contiguous(), logit_bound=bound)
     assert float((o3.float() - 2 * out.float()).abs().max()) <= 8e-3
 
 
-def test_config3_full_length_block_sparse_properties(h):
-    """768p-like length (126,016 tokens), literal neighbourhood rule (7.2 % of tiles), 2 heads."""
+@pytest.mark.parametrize("window,bounded", [((2, 8, 8), False), ((2, 8, 8), True), ((3, 48, 84), True)])
+def test_config3_full_length_block_sparse_properties(h, window, bounded):
+    """768p-like length (126,016 tokens), 2 heads: the literal neighbourhood rule (7.2 % of tiles) with the running
+    maximum and with the logit bound (single-CTA kernels), and the +-3 frames x whole frame rule (22.7 %) with the
+    bound (CTA pairs, merged plans per four query tiles)."""
+    from pika_h3_flex_b200.ops import normed_logit_bound
+
     H = 2
+    bound = normed_logit_bound() if bounded else 0.0
     grid, n_audio, L, q, k, v = _full_inputs("cfg3", H)
-    bi = h.build_block_index(grid, n_audio, (2, 8, 8))
+    bi = h.build_block_index(grid, n_audio, window)
     bid = bi.to("cuda")
     pos = O.make_positions(grid, n_audio)
     tab = h.rope_table(dev(pos))
     qp, kp, _, _ = h.qk_prep(q, k, tab, tab)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    out = h.attn_fwd(qp, kp, v, h.MODE_BLOCK_SPARSE, block_index=bid, status_word=status)
+    out = h.attn_fwd(qp, kp, v, h.MODE_BLOCK_SPARSE, block_index=bid, status_word=status, logit_bound=bound)
     assert h.read_status(status) == 0
     rows = torch.cat([torch.arange(0, L, 4099), torch.tensor([L - 1, 1023, 1024, 1151, 1152])])
     qo, ko = O.qk_prep(q.cpu().double(), k.cpu().double(), *O.rope_table(pos))
     ref = O.attention(qo, ko, v.cpu().double(), csr=(bi.row_ptr.numpy(), bi.col_idx.numpy()), q_rows=rows)
     check(out[rows], ref.float(), mx=3e-2, mean=3e-3)
-    o1 = h.attn_fwd(qp, kp, torch.ones_like(v), h.MODE_BLOCK_SPARSE, block_index=bid)
+    o1 = h.attn_fwd(qp, kp, torch.ones_like(v), h.MODE_BLOCK_SPARSE, block_index=bid, logit_bound=bound)
     assert float((o1.float() - 1).abs().max()) <= 8e-3
 
 
