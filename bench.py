@@ -9,7 +9,17 @@ rotation [+ e4m3 quantisation]) followed by the attention forward, on the 480p-l
 `value` counts 4*Lq*Lk*d*H*density FLOPs per step; inputs are resident in HBM when the timed region
 starts.  `e2e` is the same step driven from pinned HOST buffers (H2D of Q, K, V and D2H of the output
 inside the timed region).  With N > 1 (launched by torchrun, one rank per GPU) the same total work is
-split Ulysses-style: each rank holds L/N tokens, two all-to-all exchanges bracket the local attention.
+split Ulysses-style: each rank holds L/N tokens of one global seeded tensor, the operands are resharded
+sequence -> heads before the local attention and the output heads -> sequence after it.
+
+Besides the contract keys the line carries
+  parity     sampled query rows of THIS run's outputs (every rank's own shard; device-resident path and
+             host-buffer path) against the fp64 CPU oracle on the same global seeded tensors, computed outside the
+             timed region, worst rank reported;
+  roofline   the attention kernel alone (CUDA events around its launches, max over ranks);
+  ms_per_step_sustained / ms_x_mhz   the same steps continued for about two seconds with the SM clock
+             sampled over exactly that stretch (the part runs under a 1 kW power cap);
+  also       (N = 1) short runs of the other configurations, each with its own kernel time and parity verdict.
 `--impl reference` times the CPU oracle (the restatement of the reference's attention, all host threads)
 on a bounded sample of the same workload.
 """
@@ -17,7 +27,6 @@ from __future__ import annotations
 
 import argparse
 import json
-import math
 import os
 import subprocess
 import sys
@@ -42,12 +51,18 @@ WORKLOADS = {
     "prof_dense": ((15, 32, 32), 1024, 16, "dense_bf16", None, 2001),
     "prof_fp8": ((15, 32, 32), 1024, 16, "fp8_qk", None, 2001),
     "prof_sparse": ((31, 32, 32), 1024, 16, "block_sparse", (3, 32, 32), 2003),
+    "prof_sparse7": ((31, 32, 48), 1024, 16, "block_sparse", (2, 8, 8), 2003),
+    "prof_cross": ((15, 32, 32), 1024, 16, "cross_bf16", None, 2004),
 }
-# dram__bytes_read.sum + dram__bytes_write.sum of one attention-kernel launch, from the ncu captures summarised
-# under profiles/ (None until a capture of that workload exists)
-NCU_TRAFFIC_BYTES = {
-    "prof_dense": 250.9e6,           # measured: the ncu capture of this workload summarised under profiles/
-    "cfg1_dense": 250.9e6 * 7.535,   # the same capture scaled by the units per launch (L*H: 49,384*40 / 16,384*16)
+ALSO = ("cfg2_fp8", "cfg3_sparse", "cfg3_sparse20", "cfg4_cross")  # N = 1: short runs next to the headline workload
+
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the dominant kernel, from the ncu
+# capture summarised in the named file under profiles/.  An entry is (kernel the capture is of, bytes per launch of
+# the CAPTURED workload, L * H of the captured workload, file).  The figure is scaled to the benchmarked workload by
+# the units per launch (L * H: traffic is Q, K, V, O once per head) and reported only when the kernel that ran is the
+# captured one; otherwise `traffic` is null.
+NCU_TRAFFIC = {
+    "dense_bf16": ("attn_fwd_pair_kernel", 250.9e6, 16384 * 16, "profiles/attn_fwd_dense_bf16_prof_dense.md"),
 }
 
 
@@ -61,7 +76,8 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms; `mark()` returns a position in the record so that
+    a summary can cover one stretch of the run."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -85,23 +101,31 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def mark(self) -> int:
+        return len(self.lines)
+
     def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+
+    def summary(self, lo: int = 0, hi: int | None = None):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        for ln in self.lines[lo:hi]:
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 9:
                 continue
             try:
                 sm.append(float(parts[1]))
                 mx.append(float(parts[2]))
+                pw.append(float(parts[3]))
             except ValueError:
                 continue
             for name, val in zip(names, parts[5:9]):
@@ -109,7 +133,7 @@ class ClockSampler:
                     reasons.add(name)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "power_w_max": max(pw) if pw else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
 def workload_dims(name):
@@ -193,12 +217,19 @@ def run_reference(args):
             vals.append(tf)
             times.append(dt)
     value = sum(vals) / len(vals)
+    density = 1.0
+    if mode == "block_sparse":
+        import pika_h3_flex_b200 as h3
+
+        density = h3.build_block_index(grid, n_audio, window).density
     line = {
         "impl": "reference", "metric": "attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "L": L, "Lk": Lk, "H": H, "d": 128, "mode": mode,
-                   "note": "CPU restatement of the reference attention (oracle); each step is a bounded sample"},
+        "config": {"workload": name, "L": L, "Lk": Lk, "H": H, "d": 128, "mode": mode, "density": density,
+                   "flops_per_step": 4.0 * L * Lk * 128 * H * density,
+                   "note": "CPU restatement of the reference attention (oracle); each step is a bounded sample of the workload "
+                           "(ms_per_step is the sample's time, value its TFLOP/s)"},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -207,12 +238,253 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
+PARITY_HEADS = 2
+BOUNDS = {"bf16": (2e-2, 2e-3, 1e-2), "fp8": (3e-2, 3e-3, 6e-2)}  # max-abs, mean-abs, rel-L2 (as in tests/test_gpu_parity.py)
+
+
+class Case:
+    """One workload on this rank: its shard of the global seeded operands on the device, what the oracle needs to
+    rebuild sampled rows of the result on the host, and the step that runs it."""
+
+
+def make_case(name, world, rank, dev, online_max=False):
+    import pika_h3_flex_b200 as h3
+    from pika_h3_flex_b200 import _lib
+    from pika_h3_flex_b200.layout import position_grid
+    from pika_h3_flex_b200.ops import normed_logit_bound
+
+    c = Case()
+    c.name = name
+    grid, n_audio, L, H, mode_name, window, seed = workload_dims(name)
+    c.grid, c.n_audio, c.L, c.H, c.mode_name, c.window = grid, n_audio, L, H, mode_name, window
+    c.mode = {"dense_bf16": _lib.MODE_DENSE_BF16, "fp8_qk": _lib.MODE_FP8_QK, "block_sparse": _lib.MODE_BLOCK_SPARSE,
+              "cross_bf16": _lib.MODE_DENSE_BF16}[mode_name]
+    c.cross = mode_name == "cross_bf16"
+    c.fp8 = c.mode == _lib.MODE_FP8_QK
+    if L % world:
+        raise SystemExit(f"sequence length {L} does not split over {world} ranks")
+    c.Ls = Ls = L // world
+    c.Lk = 512 if c.cross else L
+    c.lo = rank * Ls
+    c.heads = sorted({0, H - 1})[:PARITY_HEADS]
+    # ONE global tensor per operand, the same on every rank (same seed, same generator, same draw order): a rank
+    # keeps its token shard on the device and, for the parity check, the full keys / values of two heads on the host
+    g = torch.Generator(device=dev).manual_seed(seed)
+    shard = slice(c.lo, c.lo + Ls)
+    full = torch.randn(L, H, 128, device=dev, generator=g).bfloat16()
+    c.q = full[shard].clone()
+    full = torch.randn(L, H, 128, device=dev, generator=g).bfloat16()
+    c.k = full[: c.Lk].clone() if c.cross else full[shard].clone()
+    c.k_host = full[: c.Lk][:, c.heads].cpu()
+    full = torch.randn(L, H, 128, device=dev, generator=g).bfloat16()
+    c.v = full[: c.Lk].clone() if c.cross else full[shard].clone()
+    c.v_host = full[: c.Lk][:, c.heads].cpu()
+    del full
+    c.pos = position_grid(grid, n_audio)  # the whole sequence, fp32 on the host
+    c.rope = None if c.cross else h3.rope_table(c.pos[shard].to(dev))
+    c.bi = c.bi_host = None
+    c.density = 1.0
+    if c.mode == _lib.MODE_BLOCK_SPARSE:
+        c.bi_host = h3.build_block_index(grid, n_audio, window)
+        c.density = c.bi_host.density
+        c.bi = c.bi_host.to(dev)
+    c.flops = 4.0 * L * c.Lk * 128 * H * c.density
+    c.bound = 0.0 if online_max else normed_logit_bound(fp8=c.fp8)  # unit-weight QK-RMSNorm
+    return c
+
+
+def kernel_name(c, online_max):
+    """Which attention kernel the library picks for this case: CTA pairs with a logit bound, from 16 key tiles and
+    (block-sparse) 12 % density up."""
+    pair = (not online_max and os.environ.get("H3A_PAIR", "1")[:1] != "0" and (c.Lk + 127) // 128 >= 16
+            and (c.mode_name != "block_sparse" or c.density >= 0.12))
+    return "attn_fwd_pair_kernel" if pair else "attn_fwd_kernel"
+
+
+def single_gpu_step(c, status):
+    """(step, events, launches per step) for one GPU: preparation + attention through the C ABI wrappers."""
+    import pika_h3_flex_b200 as h3
+    from pika_h3_flex_b200.ops import split_workspace_bytes
+
+    dev = c.q.device
+    out = torch.empty(c.L, c.H, 128, dtype=torch.bfloat16, device=dev)
+    if c.bi is not None:
+        ws = torch.empty((c.bi.nnz + (c.L + 255) // 256) * 4 + 16, dtype=torch.uint8, device=dev)
+        split_bytes = 0
+    else:  # optional scratch: the CTA pairs of the last, partly filled wave split the key range
+        split_bytes = split_workspace_bytes(c.L, c.Lk, c.H, c.mode, c.bound)
+        ws = torch.empty(max(16, split_bytes), dtype=torch.uint8, device=dev)
+    events = {"prep": [], "attention": []}
+
+    def step(record=False):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
+        if record:
+            ev[0].record()
+        qp, kp, qs, ks = h3.qk_prep(c.q, c.k, c.rope, c.rope, fp8=c.fp8)
+        if record:
+            ev[1].record()
+        h3.attn_fwd(qp, kp, c.v, c.mode, qs, ks, c.bi, out=out, status_word=status, workspace=ws, logit_bound=c.bound)
+        if record:
+            ev[2].record()
+            events["prep"].append((ev[0], ev[1]))
+            events["attention"].append((ev[1], ev[2]))
+        return out
+
+    # prep (2) + attention (1) [+ plan | + combine of the split last wave]; V is used where it lies
+    launches = 3 + (1 if c.bi is not None else 0) + (1 if split_bytes else 0)
+    return step, events, launches
+
+
+def sample_rows(c, n=40):
+    """Global indices of the query rows of THIS rank's shard that the parity check looks at: evenly spread plus the
+    shard's edges, the last (partial) tile and the audio / video border when the shard holds them."""
+    lo, hi = c.lo, c.lo + c.Ls
+    rows = set(torch.linspace(lo, hi - 1, n).long().tolist()) | {lo, hi - 1}
+    for r in (c.L - 1, c.L - 104, c.L - 105, c.n_audio - 1, c.n_audio, 127, 128):
+        if lo <= r < hi:
+            rows.add(r)
+    return torch.tensor(sorted(rows), dtype=torch.int64)
+
+
+def parity_of(c, out_shard, world, dev):
+    """Compare sampled rows of this rank's output shard (`out_shard [Ls, H, 128]`, device or pinned host) with the
+    fp64 oracle evaluated on the global seeded operands of two heads; the worst rank's figures are returned."""
+    import torch.distributed as dist
+
+    from oracle import oracle as O
+
+    rows = sample_rows(c)
+    local = rows - c.lo
+    hs = c.heads
+    got = out_shard[local][:, hs].float().cpu()
+    q = c.q[local][:, hs].cpu().double()
+    k, v = c.k_host.double(), c.v_host.double()
+    if c.cross:
+        qn, kn = O.rms_norm(q), O.rms_norm(k)
+        csr = None
+    else:
+        cos, sin = O.rope_table(c.pos.double())
+        qn = O.apply_rope(O.rms_norm(q), cos[rows], sin[rows])
+        kn = O.apply_rope(O.rms_norm(k), cos, sin)
+        csr = None if c.bi_host is None else (c.bi_host.row_ptr.numpy(), c.bi_host.col_idx.numpy())
+    if csr is None:
+        ref = O.attention(qn, kn, v, chunk=64)
+    else:  # the masked oracle looks the tile row up by the global row index
+        full_q = torch.zeros(c.L, len(hs), 128, dtype=torch.float64)
+        full_q[rows] = qn
+        ref = O.attention(full_q, kn, v, csr=csr, q_rows=rows, chunk=64)
+    st = O.error_stats(got, ref.float())
+    finite = bool(torch.isfinite(got).all())
+    mx, mean, rel = BOUNDS["fp8" if c.fp8 else "bf16"]
+    ok = finite and st["max_abs"] <= mx and st["mean_abs"] <= mean and st["rel_l2"] <= rel
+    t = torch.tensor([st["max_abs"], st["mean_abs"], st["rel_l2"], 0.0 if ok else 1.0], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"ok": bool(t[3].item() == 0.0), "max_abs": float(t[0]), "mean_abs": float(t[1]), "rel_l2": float(t[2]),
+            "rows": int(rows.numel()) * world, "heads": hs, "bounds": {"max_abs": mx, "mean_abs": mean, "rel_l2": rel},
+            "against": "fp64 CPU oracle (RMSNorm + rotation + exact softmax attention%s) on the same global seeded operands; worst rank"
+                       % (", unquantised" if c.fp8 else "")}
+
+
+def copy_floor(hq, hk, hv, ho, dev, barrier, rank_max):
+    """What the host link allows: this rank's Q, K, V shards host -> device and an output shard device -> host with
+    plain asynchronous copies, every rank copying at once.  Returns (ms with both directions together, H2D GB/s alone,
+    D2H GB/s alone), each the slowest rank's."""
+    dq, dk, dv, do = (torch.empty_like(t, device=dev) for t in (hq, hk, hv, ho))
+    s1, s2 = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def run(h2d, d2h):
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        cur = torch.cuda.current_stream(dev)
+        a.record(cur)
+        s1.wait_stream(cur)
+        s2.wait_stream(cur)
+        if h2d:
+            with torch.cuda.stream(s1):
+                for d, h in ((dq, hq), (dk, hk), (dv, hv)):
+                    d.copy_(h, non_blocking=True)
+        if d2h:
+            with torch.cuda.stream(s2):
+                ho.copy_(do, non_blocking=True)
+        cur.wait_stream(s1)
+        cur.wait_stream(s2)
+        b.record(cur)
+        barrier()
+        return rank_max(a.elapsed_time(b))
+
+    run(True, True)
+    both = min(run(True, True) for _ in range(3))
+    t_in = min(run(True, False) for _ in range(2))
+    t_out = min(run(False, True) for _ in range(2))
+    nb = hq.numel() * 2
+    return both, 3 * nb / (t_in * 1e-3) / 1e9, nb / (t_out * 1e-3) / 1e9
+
+
+def mean_ms(pairs):
+    return sum(a.elapsed_time(b) for a, b in pairs) / max(1, len(pairs))
+
+
+def roofline_of(c, attn_ms, online_max, world=1):
+    """Roofline entry of the attention kernel: `attn_ms` = its launches of one step on one GPU, which computes
+    1/world of the step's FLOPs; `achieved` and the fractions are per GPU (fractions of ONE GPU's peak)."""
+    burst, sustained, src = measured_peaks()
+    achieved = c.flops / world / (attn_ms * 1e-3) / 1e12
+    kern = kernel_name(c, online_max)
+    traffic, traffic_src = None, None
+    cap = NCU_TRAFFIC.get(c.mode_name)
+    if cap is not None and cap[0] == kern:
+        traffic = cap[1] * (c.L * c.H / world) / cap[2]
+        traffic_src = f"{cap[3]} (captured workload scaled by L*H per launch)"
+    r = {"bound": "tensor", "kernel": kern, "achieved": achieved, "peak": burst, "unit": "TFLOP/s", "frac": achieved / burst,
+         "peak_source": f"bf16 burst, of {src}", "frac_of_sustained": achieved / sustained, "frac_of_spec_2250": achieved / 2250.0,
+         "kernel_ms": attn_ms, "traffic": traffic, "traffic_source": traffic_src}
+    if world > 1:
+        r["whole_job_tflops"] = achieved * world
+        r["note"] = "per GPU: kernel_ms = attention launches of one step on one rank (max over ranks), 1/%d of the step's FLOPs" % world
+    if c.fp8:
+        r["frac_of_fp8_spec_4500"] = achieved / 4500.0
+        r["frac_of_blended_3000"] = achieved / 3000.0
+    return r
+
+
+def run_also(name, dev, online_max=False):
+    """A short run (3 warm-up + 5 timed steps) of another configuration on this GPU, with its parity verdict."""
+    import pika_h3_flex_b200 as h3
+
+    c = make_case(name, 1, 0, dev, online_max)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    step, events, _ = single_gpu_step(c, status)
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(5):
+        out = step(record=True)
+    b.record()
+    torch.cuda.synchronize()
+    if h3.read_status(status) != 0:
+        return {"workload": name, "error": f"device status 0x{h3.read_status(status):x}"}
+    ms = a.elapsed_time(b) / 5
+    attn_ms = mean_ms(events["attention"])
+    roof = roofline_of(c, attn_ms, online_max)
+    par = parity_of(c, out, 1, dev)
+    res = {"workload": name + ("_online_max" if online_max else ""), "value": c.flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+           "ms_per_step": ms, "kernel_ms": attn_ms, "kernel": roof["kernel"], "kernel_tflops": roof["achieved"], "frac": roof["frac"],
+           "frac_of_spec_2250": roof["frac_of_spec_2250"], "density": c.density, "steps": 5,
+           "parity": {k: par[k] for k in ("ok", "max_abs", "mean_abs", "rel_l2", "rows")}}
+    if c.fp8:
+        res["frac_of_fp8_spec_4500"] = roof["frac_of_fp8_spec_4500"]
+        res["frac_of_blended_3000"] = roof["frac_of_blended_3000"]
+    return res
+
+
 def run_ours(args):
     import torch.distributed as dist
 
     import pika_h3_flex_b200 as h3
     from pika_h3_flex_b200 import _lib
-    from pika_h3_flex_b200.ulysses import UlyssesAttention
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -223,222 +495,200 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(minutes=10))
     torch.backends.cuda.matmul.allow_tf32 = False
 
     name = args.workload
-    grid, n_audio, L, H, mode_name, window, seed = workload_dims(name)
-    mode = {"dense_bf16": _lib.MODE_DENSE_BF16, "fp8_qk": _lib.MODE_FP8_QK, "block_sparse": _lib.MODE_BLOCK_SPARSE,
-            "cross_bf16": _lib.MODE_DENSE_BF16}[mode_name]
-    if L % world:
-        raise SystemExit(f"sequence length {L} does not split over {world} ranks")
-    Ls = L // world
-    from pika_h3_flex_b200.layout import position_grid
-
-    pos = position_grid(grid, n_audio)[rank * Ls : (rank + 1) * Ls]
-    g = torch.Generator(device=dev).manual_seed(seed + rank)
-    q = torch.randn(Ls, H, 128, device=dev, generator=g).bfloat16()
-    k = torch.randn(Ls, H, 128, device=dev, generator=g).bfloat16()
-    v = torch.randn(Ls, H, 128, device=dev, generator=g).bfloat16()
-    rope = h3.rope_table(pos.to(dev))
-    bi = None
-    density = 1.0
-    if mode == _lib.MODE_BLOCK_SPARSE:
-        bi_host = h3.build_block_index(grid, n_audio, window)
-        density = bi_host.density
-        bi = bi_host.to(dev)
-    cross = mode_name == "cross_bf16"
-    Lk = 512 if cross else L
-    if cross and world > 1:
+    c = make_case(name, world, rank, dev, args.online_max)
+    if c.cross and world > 1:
         raise SystemExit("cross-attention needs no exchange: run it per rank with --gpus 1")
-    flops = 4.0 * L * Lk * 128 * H * density
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
-    attn_events = []
-
-    from pika_h3_flex_b200.ops import normed_logit_bound
-
-    bound = 0.0 if args.online_max else normed_logit_bound(fp8=(mode == _lib.MODE_FP8_QK))  # unit-weight QK-RMSNorm
+    L, Ls, H = c.L, c.Ls, c.H
+    status = h3.StatusWord(dev)
+    ua = None
     if world == 1:
-        out = torch.empty(L, H, 128, dtype=torch.bfloat16, device=dev)
-        if bi is not None:
-            ws = torch.empty((bi.nnz + (L + 255) // 256) * 4 + 16, dtype=torch.uint8, device=dev)
-            split_bytes = 0
-        else:  # optional scratch: the CTA pairs of the last, partly filled wave split the key range
-            from pika_h3_flex_b200.ops import split_workspace_bytes
-            split_bytes = split_workspace_bytes(L, Lk, H, mode, bound)
-            ws = torch.empty(max(16, split_bytes), dtype=torch.uint8, device=dev)
-
-        if cross:  # keys and values are the text tokens; QK-RMSNorm without rotation
-            k = k[:Lk].contiguous()
-            v = v[:Lk].contiguous()
-
-        def step(record=False):
-            qp, kp, qs, ks = h3.qk_prep(q, k, None if cross else rope, None if cross else rope, fp8=(mode == _lib.MODE_FP8_QK))
-            if record:
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-            h3.attn_fwd(qp, kp, v, mode, qs, ks, bi, out=out, status_word=status, workspace=ws, logit_bound=bound)
-            if record:
-                e1.record()
-                attn_events.append((e0, e1))
-            return out
-
-        # prep (2) + attention (1) [+ plan | + combine of the split last wave]; V is used where it lies
-        launches_per_step = 3 + (1 if bi is not None else 0) + (1 if split_bytes else 0)
+        step, events, launches_per_step = single_gpu_step(c, status.tensor())
     else:
-        ua = UlyssesAttention(None, mode, bi, head_groups=args.head_groups)
+        from pika_h3_flex_b200.ulysses import UlyssesAttention
+
+        ua = UlyssesAttention(None, c.mode, c.bi, head_groups=args.head_groups, status=status, transport=args.transport)
+        timeline = []
 
         def step(record=False):
-            return ua(q, k, v, rope)
+            ua.timeline = timeline if record else None
+            return ua(c.q, c.k, c.v, c.rope, logit_bound=c.bound)
 
-        # prep (2) + V head-major copy (1, torch) + attention (1) [+ plan]; only this library's kernels are counted
-        launches_per_step = 3 + (1 if bi is not None else 0)
+        launches_per_step = ua.launches_per_step(Ls, H)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def rank_max(x):
+        if world == 1:
+            return float(x)
+        t = torch.tensor([float(x)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     for _ in range(max(3, args.warmup)):
         step()
     barrier()
-    if h3.read_status(status) != 0:
-        raise SystemExit(f"device wait gave up during warm-up: status 0x{h3.read_status(status):x}")
+    status.check("warm-up")
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     barrier()
+    m0 = sampler.mark()
     e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_start.record()
     for _ in range(args.steps):
-        step(record=True)
+        out = step(record=True)
     e_stop.record()
     barrier()
-    elapsed_ms = e_start.elapsed_time(e_stop)
-    if world > 1:
-        t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
-    ms_per_step = elapsed_ms / args.steps
-    # nvidia-smi delivers a sample every 200 ms: a timed region shorter than about a second holds too few of them,
-    # so the same steps keep running (untimed, every rank alike) until the record covers 1.5 s of this load
-    extra_steps = 0
-    if elapsed_ms < 1000.0:
-        extra_steps = int(1500.0 / max(ms_per_step, 1e-3)) + 1
-        for _ in range(extra_steps):
-            step()
-        barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    if clocks is not None and extra_steps:
-        clocks["note"] = f"timed region {elapsed_ms:.0f} ms: sampling continued over {extra_steps} identical untimed steps"
-    value = flops / (ms_per_step * 1e-3) / 1e12
-    if h3.read_status(status) != 0:
-        raise SystemExit(f"device wait gave up: status 0x{h3.read_status(status):x}")
+    m1 = sampler.mark()
+    ms_per_step = rank_max(e_start.elapsed_time(e_stop)) / args.steps
+    status.check("timed region")
+    # ---- the same steps continued for about two seconds (every rank alike), timed again, with the clock record of
+    #      exactly this stretch: nvidia-smi delivers a sample every 200 ms, and the power cap needs a second to bite
+    n_sus = max(args.steps, int(2000.0 / max(ms_per_step, 1e-3)) + 1)
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    m2 = sampler.mark()
+    s0.record()
+    for _ in range(n_sus):
+        step()
+    s1.record()
+    barrier()
+    m3 = sampler.mark()
+    ms_sustained = rank_max(s0.elapsed_time(s1)) / n_sus
+    clocks = clocks_sus = None
+    if rank == 0:
+        sampler.stop()
+        clocks = sampler.summary(m0, m1)
+        clocks_sus = sampler.summary(m2, m3)
+        if clocks["samples"] < 3:  # a short timed region holds too few samples: report the record of the whole run
+            clocks = sampler.summary(m0, m3)
+            clocks["note"] = f"timed region {ms_per_step * args.steps:.0f} ms: the record also covers the {n_sus} identical steps that followed"
+    value = c.flops / (ms_per_step * 1e-3) / 1e12
+    status.check("sustained stretch")
 
-    # ---- dominant kernel, timed live with CUDA events on the launching stream
-    roofline = None
-    if attn_events:
-        attn_ms = sum(a.elapsed_time(b) for a, b in attn_events) / len(attn_events)
-        burst, sustained, src = measured_peaks()
-        achieved = flops / (attn_ms * 1e-3) / 1e12
-        # which kernel the library picks: CTA pairs with a logit bound, from 16 key tiles and (sparse) 12 % density up
-        pair = (not args.online_max and os.environ.get("H3A_PAIR", "1")[:1] != "0" and (Lk + 127) // 128 >= 16
-                and (mode_name != "block_sparse" or density >= 0.12))
-        roofline = {"bound": "tensor", "kernel": "attn_fwd_pair_kernel" if pair else "attn_fwd_kernel", "achieved": achieved, "peak": burst, "unit": "TFLOP/s",
-                    "frac": achieved / burst, "peak_source": f"bf16 burst, of {src}", "frac_of_sustained": achieved / sustained,
-                    "frac_of_spec_2250": achieved / 2250.0, "kernel_ms": attn_ms, "traffic": NCU_TRAFFIC_BYTES.get(name)}
+    # ---- dominant kernel and the token-local preparation, timed live with CUDA events on the launching stream
+    if world == 1:
+        attn_ms, prep_ms = mean_ms(events["attention"]), mean_ms(events["prep"])
+    else:
+        attn_ms = sum(sum(a.elapsed_time(b) for a, b in m["attention"]) for m in timeline) / max(1, len(timeline))
+        prep_ms = sum(sum(a.elapsed_time(b) for a, b in m["prep"]) for m in timeline) / max(1, len(timeline))
+    attn_ms, prep_ms = rank_max(attn_ms), rank_max(prep_ms)
+    roofline = roofline_of(c, attn_ms, args.online_max, world)
+
+    # ---- parity of this run's output (outside the timed region)
+    parity = parity_of(c, out if world == 1 else out.contiguous(), world, dev)
+    parity["path"] = "device-resident"
 
     # ---- end to end from host buffers through the public call
     e2e = None
-    if world == 1 and cross:
+    nbytes = L * H * 128 * 2  # over all ranks
+    if c.cross:
         e2e = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                "note": "host-buffer end-to-end is measured on the self-attention workloads"}
-    elif world == 1:
-        hq, hk, hv = (torch.empty(L, H, 128, dtype=torch.bfloat16).pin_memory() for _ in range(3))
-        for dst, src_t in ((hq, q), (hk, k), (hv, v)):
-            dst.copy_(src_t)
-        ho = torch.empty(L, H, 128, dtype=torch.bfloat16).pin_memory()
-        host_attn = h3.HostJointAttention(L, H, mode, bi)  # the public host-buffer call: pipelined over head groups
-        torch.cuda.synchronize()
-
-        def e2e_step():
-            host_attn(hq, hk, hv, rope, ho)
-
-        n_e2e = max(2, min(args.steps, 5))
-        e2e_step()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(n_e2e):
-            e2e_step()
-        b.record()
-        torch.cuda.synchronize()
-        e2e_ms = a.elapsed_time(b) / n_e2e
-        nbytes = L * H * 128 * 2
-        e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": 3 * nbytes,
-               "d2h_bytes_per_step": nbytes, "ms_per_step": e2e_ms, "steps": n_e2e,
-               "api": "HostJointAttention: H2D, prep+attention and D2H pipelined over head groups %s" % host_attn.groups}
-    elif mode == _lib.MODE_FP8_QK or cross:
-        e2e = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-               "note": "the multi-GPU host-buffer path covers the dense bf16 and block-sparse self-attention workloads"}
     else:
         try:
-            # every rank's shard comes from its own pinned host buffers and goes back to one
-            from pika_h3_flex_b200.host_path import HostUlyssesAttention
-
             hq, hk, hv = (torch.empty(Ls, H, 128, dtype=torch.bfloat16).pin_memory() for _ in range(3))
-            for dst, src_t in ((hq, q), (hk, k), (hv, v)):
+            for dst, src_t in ((hq, c.q), (hk, c.k), (hv, c.v)):
                 dst.copy_(src_t)
             ho = torch.empty(Ls, H, 128, dtype=torch.bfloat16).pin_memory()
-            host_attn = HostUlyssesAttention(Ls, H, mode, bi)
+            if world == 1:
+                host_attn = h3.HostJointAttention(L, H, c.mode, c.bi, status=status)
+                api = "HostJointAttention: H2D, prep+attention and D2H pipelined over head groups %s" % host_attn.groups
+            else:
+                from pika_h3_flex_b200.host_path import HostUlyssesAttention
+
+                host_attn = HostUlyssesAttention(Ls, H, c.mode, c.bi, status=status, transport=args.transport)
+                api = "HostUlyssesAttention: per rank, H2D of its shard, prep, reshard, attention, reshard and D2H pipelined over head-slot groups %s" % host_attn.slot_groups
             barrier()
             n_e2e = max(2, min(args.steps, 5))
             for _ in range(2):
-                host_attn(hq, hk, hv, rope, ho)
+                host_attn(hq, hk, hv, c.rope, ho)
             barrier()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             for _ in range(n_e2e):
-                host_attn(hq, hk, hv, rope, ho)
+                host_attn(hq, hk, hv, c.rope, ho)
             b.record()
             barrier()
-            t = torch.tensor([a.elapsed_time(b) / n_e2e], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_ms = float(t.item())
-            nbytes = L * H * 128 * 2  # over all ranks
-            e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": 3 * nbytes,
-                   "d2h_bytes_per_step": nbytes, "ms_per_step": e2e_ms, "steps": n_e2e,
-                   "api": "HostUlyssesAttention: per rank, H2D of its shard, prep, exchanges, attention and D2H pipelined over head-slot groups %s"
-                          % host_attn.slot_groups}
-            if h3.read_status(status) != 0:
-                raise SystemExit(f"device wait gave up: status 0x{h3.read_status(status):x}")
+            e2e_ms = rank_max(a.elapsed_time(b)) / n_e2e
+            status.check("host-buffer path")
+            e2e = {"value": c.flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": 3 * nbytes,
+                   "d2h_bytes_per_step": nbytes, "ms_per_step": e2e_ms, "steps": n_e2e, "api": api}
+            pe = parity_of(c, ho, world, dev)
+            e2e["parity"] = {k: pe[k] for k in ("ok", "max_abs", "mean_abs", "rel_l2", "rows")}
+            floor_ms, h2d_gbs, d2h_gbs = copy_floor(hq, hk, hv, ho, dev, barrier, rank_max)
+            e2e["copy_floor_ms"] = floor_ms
+            e2e["copy_floor"] = ("plain asynchronous copies of the same shards, both directions at once, every rank at once (slowest rank); "
+                                 "per rank H2D alone %.1f GB/s, D2H alone %.1f GB/s" % (h2d_gbs, d2h_gbs))
+            e2e["ms_over_copy_floor"] = e2e_ms / floor_ms
+            stages = getattr(host_attn, "stage_ms", None)
+            if stages is not None:
+                e2e["stages_ms"] = stages()
+            if hasattr(host_attn, "close"):
+                host_attn.close()
+            del host_attn
         except (RuntimeError, ValueError, TypeError, AttributeError, NotImplementedError) as exc:  # keep the kernel-side line
             e2e = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-                   "note": "multi-GPU host-buffer path failed: %r" % (exc,)}
+                   "note": "host-buffer path failed: %r" % (exc,)}
+            parity["ok"] = False
+            parity["note"] = "host-buffer path failed"
+    if e2e is not None and e2e.get("parity") is not None:
+        parity["ok"] = parity["ok"] and e2e["parity"]["ok"]
+
+    also = None
+    if world == 1 and name == "cfg1_dense" and not args.no_also and not args.online_max:
+        also = []
+        for other in ALSO:
+            try:
+                also.append(run_also(other, dev))
+            except (RuntimeError, ValueError) as exc:
+                also.append({"workload": other, "error": repr(exc)})
+            torch.cuda.empty_cache()
+        try:
+            also.append(run_also("cfg1_dense", dev, online_max=True))
+        except (RuntimeError, ValueError) as exc:
+            also.append({"workload": "cfg1_dense_online_max", "error": repr(exc)})
 
     if world > 1:
         dist.barrier()
     if rank == 0:
         cpu_baseline = None
-        if world == 1 and not args.no_cpu_baseline:
+        if not args.no_cpu_baseline:
             tf, cores, sample, _ = cpu_oracle_sample(name, args.cpu_seconds)
             cpu_baseline = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample}
+        sm = clocks_sus["sm_mhz"] if clocks_sus else None
         line = {
             "metric": "attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16" if mode != _lib.MODE_FP8_QK else "e4m3(QK)+bf16(PV)", "data": "synthetic",
-            "config": {"workload": name, "L": L, "Lk": Lk, "H": H, "d": 128, "mode": mode_name, "density": density,
-                       "flops_per_step": flops, "step": "qk_prep(RMSNorm+RoPE) + attention forward",
-                       "softmax_reference": "running row maximum" if bound == 0.0 else "fixed logit bound %.2f from QK-RMSNorm" % bound,
-                       "parallelism": "single GPU" if world == 1 else f"ulysses{world} (seq<->head all-to-all, NCCL)",
+            "vs_baseline": None, "dtype": "bf16" if not c.fp8 else "e4m3(QK)+bf16(PV)", "data": "synthetic",
+            "config": {"workload": name, "L": L, "Lk": c.Lk, "H": H, "d": 128, "mode": c.mode_name, "density": c.density,
+                       "flops_per_step": c.flops, "step": "qk_prep(RMSNorm+RoPE) + attention forward",
+                       "softmax_reference": "running row maximum" if c.bound == 0.0 else "fixed logit bound %.2f from QK-RMSNorm" % c.bound,
+                       "parallelism": "single GPU" if world == 1 else f"ulysses{world} (seq<->head reshard, transport: {ua.transport})",
                        "l2": "inputs (Q,K,V = %.0f MB per rank) exceed the 126 MB L2; no flush" % (3 * Ls * H * 256 / 1e6)},
-            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks, "parity": parity,
+            "ms_per_step_sustained": ms_sustained, "sustained_steps": n_sus, "clocks_sustained": clocks_sus,
+            "ms_x_mhz": None if not sm else ms_sustained * sm,
+            "prep_ms": prep_ms, "exchange_ms_exposed": None if world == 1 else ms_per_step - prep_ms - attn_ms,
             "gpu_launches": launches_per_step * args.steps,
             "attn_ms_per_dit_step_per_layer": ms_per_step,
         }
+        if also is not None:
+            line["also"] = also
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
+        if ua is not None:
+            ua.close()
         dist.destroy_process_group()
 
 
@@ -456,7 +706,7 @@ def run_projection(args):
     import torch
 
     import pika_h3_flex_b200 as h3
-    from oracle import oracle as O
+    from pika_h3_flex_b200.layout import position_grid
 
     L, D, H, R = PROJ_WORKLOADS[args.workload]
     dev = torch.device("cuda", 0)
@@ -468,10 +718,10 @@ def run_projection(args):
     lbs = [(0.5 * torch.randn(H * 128, R, device=dev, generator=g) / R ** 0.5).bfloat16() for _ in range(3)]
     # positions: config 1's grid when L is its length, otherwise frames of 8 x 8 tokens plus audio
     if L == 31 * 30 * 52 + 1024:
-        pos = O.make_positions((31, 30, 52), 1024)
+        pos = position_grid((31, 30, 52), 1024)
     else:
         frames = (L - 1024) // 64
-        pos = O.make_positions((frames, 8, 8), L - frames * 64)
+        pos = position_grid((frames, 8, 8), L - frames * 64)
     rope = h3.rope_table(pos.to(dev))
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     events = []
@@ -508,7 +758,8 @@ def run_projection(args):
         for _ in range(extra):
             step()
         torch.cuda.synchronize()
-    clocks = sampler.stop()
+    sampler.stop()
+    clocks = sampler.summary()
     if extra:
         clocks["note"] = f"timed region {elapsed_ms:.0f} ms: sampling continued over {extra} identical untimed steps"
     if h3.read_status(status) != 0:
@@ -582,7 +833,8 @@ def run_adaln(args):
     for _ in range(extra):
         h3.adaln_norm(x, scale, shift, idx, out=out)
     torch.cuda.synchronize()
-    clocks = sampler.stop()
+    sampler.stop()
+    clocks = sampler.summary()
     clocks["note"] = f"timed region {ms * args.steps:.0f} ms: sampling continued over {extra} identical untimed steps"
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     hbm, src = 6650.0, "fallback"
@@ -620,7 +872,10 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(PROJ_WORKLOADS) + ["cfg1_adaln"], default="cfg1_dense")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the cpu_baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--head-groups", type=int, default=2, help="N > 1: head groups the exchanges are pipelined over (1 = no overlap)")
+    ap.add_argument("--no-also", action="store_true", help="N = 1: skip the short runs of the other configurations")
+    ap.add_argument("--head-groups", type=int, default=2, help="N > 1: head groups the reshard is pipelined over (1 = no overlap)")
+    ap.add_argument("--transport", choices=["auto", "peer", "nccl"], default="auto",
+                    help="N > 1: how operands are resharded: direct stores into the owning rank's memory (peer) or NCCL all-to-all")
     ap.add_argument("--online-max", action="store_true", help="use the running-maximum kernel instead of the fixed logit bound")
     args = ap.parse_args()
     if args.workload == "cfg1_adaln":

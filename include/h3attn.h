@@ -26,7 +26,7 @@ extern "C" {
 #endif
 
 #define H3A_VERSION_MAJOR 0
-#define H3A_VERSION_MINOR 1
+#define H3A_VERSION_MINOR 2
 
 /* status codes */
 enum {
@@ -39,8 +39,11 @@ enum {
   H3A_ERR_TIMEOUT = -6, /* a bounded device-side wait ran out (read back from the status word) */
   H3A_ERR_WORKSPACE = -7, /* workspace missing or too small */
   H3A_ERR_DRIVER = -8,  /* driver entry point for tensor-map encoding not found */
-  H3A_ERR_STATIC_SCRATCH = -9 /* h3a_attn_fwd_sparse_static: block index larger than the built-in scratch */
+  H3A_ERR_STATIC_SCRATCH = -9, /* h3a_attn_fwd_sparse_static: block index larger than the built-in scratch */
+  H3A_ERR_INDEX = -10   /* the device-side check of a block index failed (read back from the status word) */
 };
+
+#define H3A_MAX_RANKS 8 /* GPUs one sequence can be spread over (one NVSwitch domain) */
 
 /* attention modes */
 enum {
@@ -57,6 +60,8 @@ enum {
 
 /* flags for h3a_prep_params.flags */
 #define H3A_PREP_FP8 1u /* write e4m3 Q/K and per-(head, 128-token) scales instead of bf16 */
+#define H3A_PREP_NO_NORM 2u /* skip the RMSNorm; with no rotation table either the call is a plain re-layout to
+                               head-major (what V needs) or, with H3A_PREP_FP8, a quantisation of prepared rows */
 
 /*
  * Forward attention  O = softmax(Q K^T * softmax_scale) V, non-causal, one document (batch 1, as the
@@ -80,16 +85,21 @@ typedef struct h3a_attn_params {
   float softmax_scale;    /* <= 0 selects 1/sqrt(d) */
   const float* q_scale;   /* FP8_QK: [H, ceil(Lq/128)] fp32, else NULL */
   const float* k_scale;   /* FP8_QK: [H, ceil(Lk/128)] fp32, else NULL */
-  const int32_t* row_ptr; /* BLOCK_SPARSE: [ceil(Lq/128)+1] device int32, else NULL */
-  const int32_t* col_idx; /* BLOCK_SPARSE: [nnz] device int32, ascending inside each row */
+  const int32_t* row_ptr; /* BLOCK_SPARSE: [ceil(Lq/128)+1] device int32, non-decreasing, 0 .. nnz, else NULL */
+  const int32_t* col_idx; /* BLOCK_SPARSE: [nnz] device int32 in [0, ceil(Lk/128)), strictly ascending inside each row.
+                             The index is checked on the device: entries that break a rule are left out, nothing is
+                             written outside the workspace, and the status word (when given) receives code 10, after
+                             which the attention launch does nothing (h3a_read_device_status: H3A_ERR_INDEX). */
   int32_t nnz;            /* BLOCK_SPARSE: number of kept tiles (host value of row_ptr[last]) */
   float* lse;             /* optional [H, Lq] fp32 natural-log-sum-exp out, or NULL */
   void* workspace;        /* device scratch of h3a_attn_workspace_bytes() bytes: required for BLOCK_SPARSE
                              (merged tile plan); optional for the dense modes (partial sums of a split last
                              wave of CTAs: without it, or when it is too small, the launch simply does not split) */
   size_t workspace_bytes;
-  int32_t* status_word;   /* optional device int32; a kernel that gives up a bounded wait writes a
-                             non-zero code here and returns; must be 0 on entry */
+  int32_t* status_word;   /* optional device int32; a kernel that gives up a bounded wait (or finds a malformed
+                             block index) writes a non-zero code here and returns; while it is non-zero every
+                             later launch given the same word does nothing, so one word can be shared by all the
+                             calls of a forward pass and read once at its end; zero it before the first use */
   int64_t wait_limit_ns;  /* bound for each device-side wait; <= 0 selects 2 s */
   float logit_bound;      /* optional: a value B with |q.k| * softmax_scale <= B for every query/key pair (with
                              QK-RMSNorm: 128 * max|w_q| * max|w_k| * softmax_scale).  When 0 < B <= 30 the kernel
@@ -101,6 +111,14 @@ typedef struct h3a_attn_params {
                              each) list far more key tiles than the rest (the dense audio rows of the joint
                              sequence); their CTAs of all heads are started first.  0 = no hint.  Never affects
                              results. */
+  /* Sequence parallelism, return trip: when o_n_ranks > 1 the output rows are stored where their token lives instead
+     of in `o`: query row g goes to o_rank_base[g / o_rank_rows] at row g % o_rank_rows, addressed with o_stride_l /
+     o_stride_h like `o` (each base already points at this launch's first head).  The bases are device addresses of
+     this process or of peer GPUs (see h3a_peer_open); they are only ever stored to.  `o` is then unused but must still
+     be a valid aligned pointer (pass o_rank_base[own rank]). */
+  void* o_rank_base[H3A_MAX_RANKS];
+  int32_t o_n_ranks;      /* 0 or 1: everything goes to `o` */
+  int32_t o_rank_rows;    /* tokens per rank */
 } h3a_attn_params;
 
 /*
@@ -141,6 +159,46 @@ int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream);
 
 /* Launch the Q/K preparation on `stream`. */
 int32_t h3a_qk_prep(const h3a_prep_params* p, void* stream);
+
+/*
+ * Sequence parallelism, outbound trip.  (The reference runs one request on one GPU, README.md:115; this is the
+ * multi-GPU path BASELINE's configuration 4 asks for.)  Each rank holds a token shard of every head and each head is
+ * computed by one rank.  h3a_qk_prep_scatter runs the same preparation as h3a_qk_prep on this rank's tokens and
+ * stores every prepared row straight where it is needed: head `h` (counted from `head0` for the first head of the
+ * input) belongs to rank  h / heads_per_rank  (round_robin = 0) or  h % n_ranks  (round_robin = 1), in that rank's
+ * head slot  h % heads_per_rank  or  h / n_ranks, and token l of this shard is row `row_offset + l` of the full
+ * sequence: the row goes to  base[rank] + ((slot * L_total) + row_offset + l) * 128  elements (bf16).  base[p] is rank
+ * p's [heads_per_rank, L_total, 128] buffer: this process's own memory or a peer GPU's, opened with h3a_peer_open;
+ * peer memory is only ever stored to.  q_out / k_out / scales of `p` are ignored and H3A_PREP_FP8 is refused (block
+ * scales need whole 128-token blocks of the FULL sequence: quantise on the owning rank after the exchange, with
+ * H3A_PREP_NO_NORM | H3A_PREP_FP8).  Either of q_to / k_to may be NULL together with its input.  The values for V go
+ * through the same call with H3A_PREP_NO_NORM and no rotation table.  The stores of one call are complete, for every
+ * GPU, when the kernel has finished; the ranks still have to meet (a barrier) before the owners read.
+ */
+typedef struct h3a_head_scatter {
+  void* base[H3A_MAX_RANKS];
+  int32_t n_ranks;        /* 1 .. H3A_MAX_RANKS */
+  int32_t heads_per_rank; /* head slots in every rank's buffer */
+  int32_t round_robin;    /* 0: heads in blocks, 1: dealt round robin */
+  int32_t head0;          /* global index of the input's first head */
+  int32_t row_offset;     /* this shard's first token in the full sequence */
+  int32_t L_total;        /* tokens of the full sequence */
+} h3a_head_scatter;
+int32_t h3a_qk_prep_scatter(const h3a_prep_params* p, const h3a_head_scatter* q_to, const h3a_head_scatter* k_to, void* stream);
+
+/*
+ * Device memory that other processes on the same machine can store to.  (No counterpart in the reference.)  These
+ * four are the only entry points that allocate or map device memory; everything else works on caller-owned buffers.
+ * h3a_peer_alloc: cudaMalloc of `bytes` on the current device plus the 64-byte inter-process handle of the
+ * allocation, to be sent to the other ranks by any host channel.  h3a_peer_open: map another process's allocation
+ * into this one (enables peer access between the two GPUs); the pointer is valid until h3a_peer_close.  The owner
+ * frees with h3a_peer_free after every peer has closed.
+ */
+#define H3A_PEER_HANDLE_BYTES 64
+int32_t h3a_peer_alloc(size_t bytes, void** ptr, uint8_t handle[H3A_PEER_HANDLE_BYTES]);
+int32_t h3a_peer_open(const uint8_t handle[H3A_PEER_HANDLE_BYTES], void** ptr);
+int32_t h3a_peer_close(void* ptr);
+int32_t h3a_peer_free(void* ptr);
 
 /*
  * Build the (cos, sin) table [L, 64, 2] fp32 on the device from a float position grid pos[L,3]
@@ -184,9 +242,12 @@ int32_t h3a_memcpy2d_async(void* dst, size_t dst_pitch, const void* src, size_t 
  * as `workspace`.  Here the scratch for the merged tile plan is a fixed array inside the library:
  * 262144 int32 (1 MiB) of device memory, held by every GPU that loads the library until the process exits.
  *
- * Same arguments and results as h3a_attn_fwd with mode == H3A_MODE_BLOCK_SPARSE (any other mode returns
- * H3A_ERR_ARG); `workspace` and `workspace_bytes` are ignored.  The caller still owns q, k, v, o, the block
- * index, lse and the status word.
+ * Same arguments, same kernel choice (logit_bound, density, sparse_heavy_pairs) and bit-identical results as
+ * h3a_attn_fwd with mode == H3A_MODE_BLOCK_SPARSE (any other mode returns H3A_ERR_ARG); `workspace` and
+ * `workspace_bytes` are ignored.  The caller still owns q, k, v, o, the block index, lse and the status word.
+ *   - The 1 MiB is taken from the device when the library's code is loaded into that device's context, which
+ *     with CUDA's default lazy loading is the first call into the library on that device, not dlopen(): an
+ *     arena that claims "the rest of the GPU" must leave that much free.
  *   - Limit: nnz + ceil(Lq/256) must be <= 262144 (h3a_static_scratch_capacity reports it), otherwise
  *     H3A_ERR_STATIC_SCRATCH and nothing is launched.
  *   - It calls no cudaMalloc, cudaFree or other allocating routine.
@@ -271,7 +332,9 @@ typedef struct h3a_adaln_params {
 } h3a_adaln_params;
 int32_t h3a_adaln_norm(const h3a_adaln_params* p, void* stream);
 
-/* Copy the device status word to the host after synchronising `stream`; maps non-zero to H3A_ERR_TIMEOUT. */
+/* Copy the device status word to the host after synchronising `stream`.  Returns H3A_OK for 0, H3A_ERR_INDEX when a
+ * block index failed its device-side check (low byte 10), H3A_ERR_TIMEOUT for every other non-zero value; *raw (optional)
+ * receives the word: low byte = which wait or check, upper bits = the CTA (waits) or query tile (index check). */
 int32_t h3a_read_device_status(const int32_t* status_word, void* stream, int32_t* raw);
 
 #ifdef __cplusplus

@@ -23,6 +23,8 @@ from .ops import (
     proj_fwd,
     qk_prep,
     read_status,
+    check_status,
+    StatusWord,
     rope_table,
     rope_table_from_cos_sin,
 )
@@ -30,5 +32,5 @@ from .ops import (
 __all__ = [
     "_lib", "H3AError", "MODE_DENSE_BF16", "MODE_FP8_QK", "MODE_BLOCK_SPARSE",
     "BlockIndex", "adaln_norm", "attn_fwd", "attn_fwd_sparse_static", "static_scratch_capacity", "build_block_index", "joint_attention", "proj_fwd", "qk_prep",
-    "read_status", "rope_table", "rope_table_from_cos_sin", "position_grid", "HostJointAttention",
+    "read_status", "check_status", "StatusWord", "rope_table", "rope_table_from_cos_sin", "position_grid", "HostJointAttention",
 ]

@@ -17,9 +17,13 @@ H3A_OK = 0
 H3A_ERR_ARG, H3A_ERR_ALIGN, H3A_ERR_SHAPE, H3A_ERR_ARCH = -1, -2, -3, -4
 H3A_ERR_LAUNCH, H3A_ERR_TIMEOUT, H3A_ERR_WORKSPACE, H3A_ERR_DRIVER = -5, -6, -7, -8
 H3A_ERR_STATIC_SCRATCH = -9
+H3A_ERR_INDEX = -10
 MODE_DENSE_BF16, MODE_FP8_QK, MODE_BLOCK_SPARSE = 0, 1, 2
 ROPE_INTERLEAVED, ROPE_HALF = 0, 1
 PREP_FP8 = 1
+PREP_NO_NORM = 2
+MAX_RANKS = 8
+PEER_HANDLE_BYTES = 64
 
 EXPORTS = (
     "h3a_version",
@@ -36,6 +40,11 @@ EXPORTS = (
     "h3a_selftest_wait_timeout",
     "h3a_proj_fwd",
     "h3a_adaln_norm",
+    "h3a_qk_prep_scatter",
+    "h3a_peer_alloc",
+    "h3a_peer_open",
+    "h3a_peer_close",
+    "h3a_peer_free",
 )
 
 
@@ -52,6 +61,14 @@ class AttnParams(C.Structure):
         ("row_ptr", C.c_void_p), ("col_idx", C.c_void_p), ("nnz", C.c_int32),
         ("lse", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("status_word", C.c_void_p), ("wait_limit_ns", C.c_int64), ("logit_bound", C.c_float), ("sparse_heavy_pairs", C.c_int32),
+        ("o_rank_base", C.c_void_p * MAX_RANKS), ("o_n_ranks", C.c_int32), ("o_rank_rows", C.c_int32),
+    ]
+
+
+class HeadScatter(C.Structure):
+    _fields_ = [
+        ("base", C.c_void_p * MAX_RANKS), ("n_ranks", C.c_int32), ("heads_per_rank", C.c_int32), ("round_robin", C.c_int32),
+        ("head0", C.c_int32), ("row_offset", C.c_int32), ("L_total", C.c_int32),
     ]
 
 
@@ -138,6 +155,16 @@ def load() -> C.CDLL:
     lib.h3a_proj_fwd.restype = C.c_int32
     lib.h3a_adaln_norm.argtypes = [C.POINTER(AdaLnParams), C.c_void_p]
     lib.h3a_adaln_norm.restype = C.c_int32
+    lib.h3a_qk_prep_scatter.argtypes = [C.POINTER(PrepParams), C.POINTER(HeadScatter), C.POINTER(HeadScatter), C.c_void_p]
+    lib.h3a_qk_prep_scatter.restype = C.c_int32
+    lib.h3a_peer_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]
+    lib.h3a_peer_alloc.restype = C.c_int32
+    lib.h3a_peer_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+    lib.h3a_peer_open.restype = C.c_int32
+    lib.h3a_peer_close.argtypes = [C.c_void_p]
+    lib.h3a_peer_close.restype = C.c_int32
+    lib.h3a_peer_free.argtypes = [C.c_void_p]
+    lib.h3a_peer_free.restype = C.c_int32
     _lib = lib
     return lib
 

@@ -100,6 +100,7 @@ struct AttnArgs {
   long long wait_ns;
   float fixed_m;           // fixed softmax reference in log2 units (kFixed kernels)
   int heavy_pairs;         // sparse: leading query-tile pairs whose CTAs (of every head) are scheduled first
+  int nnz;                 // sparse: entries of col_idx = capacity of the plan; plan offsets are clamped to it
   // CTA pairs, dense: pairs numbered split_begin and up (the ones that would form a last, partly empty wave) are
   // each handled by kv_splits CTA pairs, every one over its share of the key tiles; they leave un-normalised
   // partial outputs and row sums in `part`, which combine_partials_kernel adds up (the fixed softmax reference
@@ -107,7 +108,23 @@ struct AttnArgs {
   int split_begin;
   int kv_splits;
   float* part;             // [slot][4 query tiles][128 rows][128 + 1] fp32: O columns, then the row sum
+  // Sequence parallelism: with o_n_ranks > 1 query row g is stored at row g % o_rank_rows of o_rank[g / o_rank_rows]
+  // (the rank that holds token g: its own memory or a peer GPU's, stored to only) instead of in `o`.
+  __nv_bfloat16* o_rank[8];
+  int o_n_ranks, o_rank_rows;
 };
+
+// address of output row `q_row` of (local) head `head`
+__device__ __forceinline__ __nv_bfloat16* out_row_ptr(const AttnArgs& a, int q_row, int head) {
+  __nv_bfloat16* base = a.o;
+  int r = q_row;
+  if (a.o_n_ranks > 1) {
+    const int t = min(q_row / a.o_rank_rows, a.o_n_ranks - 1);
+    base = a.o_rank[t];
+    r = q_row - t * a.o_rank_rows;
+  }
+  return base + static_cast<long long>(r) * a.o_stride_l + static_cast<long long>(head) * a.o_stride_h;
+}
 
 // status word layout: bits [0,8) code, bits [8,32) blockIdx.x (truncated)
 enum : int {
@@ -195,16 +212,40 @@ __global__ void wait_selftest_kernel(const AttnArgs args) {
   bounded_wait(wc, smem_u32(&bars.q_full), 0, kWaitSelfTest);
 }
 
+// The plan kernels do not trust the caller's block index.  Row pointers are clamped into [0, nnz] and must not
+// decrease; column entries must lie in [0, nkb) and ascend strictly inside a row.  What breaks a rule is left out
+// of the plan, never written past the plan's `nnz` entries and reported (once) through the status word as
+// kBadBlockIndex | offending query tile << 8: the attention launch that follows then does nothing, exactly as
+// after a wait that gave up.  Without a status word the launch runs on the entries that passed.
+constexpr int kBadBlockIndex = 10;
+__device__ __forceinline__ int clamp_row_ptr(int v, int nnz) { return max(0, min(v, nnz)); }
+__device__ __forceinline__ void report_bad_index(int* status, int q_tile) {
+  if (status) atomicCAS(status, 0, kBadBlockIndex | ((q_tile & 0x7FFFFF) << 8));
+}
+// begin / end of the key-tile list of query tile r (empty beyond nqb); *bad is raised when row_ptr breaks a rule
+__device__ __forceinline__ void row_range(const int32_t* __restrict__ row_ptr, int r, int nqb, int nnz, int& begin, int& end, bool& bad) {
+  begin = end = 0;
+  if (r >= nqb) return;
+  const int a = row_ptr[r], b = row_ptr[r + 1];
+  begin = clamp_row_ptr(a, nnz);
+  end = clamp_row_ptr(b, nnz);
+  if (a != begin || b != end || b < a) bad = true;
+  if (end < begin) end = begin;
+}
+
 // Merge the sorted key-tile lists of query tiles 2p and 2p+1 into one list with stream flags.
 __global__ void build_pair_plan_kernel(const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ col_idx,
-                                       int nqb, int n_qpairs, int32_t* __restrict__ plan, int32_t* __restrict__ plan_cnt) {
+                                       int nqb, int n_qpairs, int nnz, int nkb, int32_t* __restrict__ plan,
+                                       int32_t* __restrict__ plan_cnt, int* __restrict__ status) {
   int p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= n_qpairs) return;
-  int r0 = 2 * p, r1 = 2 * p + 1;
-  int a = row_ptr[r0], a_end = row_ptr[r0 + 1];
-  int b = (r1 < nqb) ? row_ptr[r1] : 0, b_end = (r1 < nqb) ? row_ptr[r1 + 1] : 0;
-  int32_t* out = plan + row_ptr[r0];
-  int n = 0;
+  bool bad = false;
+  int a, a_end, b, b_end;
+  row_range(row_ptr, 2 * p, nqb, nnz, a, a_end, bad);
+  row_range(row_ptr, 2 * p + 1, nqb, nnz, b, b_end, bad);
+  int32_t* out = plan + a;
+  const int cap = nnz - a;  // the merged list is never longer than the two lists together, which end at or before nnz
+  int n = 0, prev = -1;
   while (a < a_end || b < b_end) {
     int ca = (a < a_end) ? col_idx[a] : 0x7FFFFFFF;
     int cb = (b < b_end) ? col_idx[b] : 0x7FFFFFFF;
@@ -212,9 +253,12 @@ __global__ void build_pair_plan_kernel(const int32_t* __restrict__ row_ptr, cons
     int f = 0;
     if (ca == c) { f |= 1; ++a; }
     if (cb == c) { f |= 2; ++b; }
+    if (c <= prev || c >= nkb || n >= cap) { bad = true; continue; }  // out of range, out of order or duplicate
+    prev = c;
     out[n++] = (c << 2) | f;
   }
   plan_cnt[p] = n;
+  if (bad) report_bad_index(status, 2 * p);
 }
 
 // kFixed: the caller supplied an upper bound of the logits; it is used as the softmax reference for every row, so
@@ -265,7 +309,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int32_t* plan = nullptr;
   int dense_flags = 3;
   if constexpr (kSparse) {
-    plan = args.plan + args.row_ptr[2 * pair];
+    plan = args.plan + clamp_row_ptr(args.row_ptr[2 * pair], args.nnz);
     n_it = args.plan_cnt[pair];
   } else {
     n_it = args.n_kv_tiles;
@@ -555,7 +599,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");
     if (have) tc_fence_after_sync();
     const bool row_valid = q_row < args.Lq;
-    __nv_bfloat16* orow = args.o + static_cast<long long>(q_row) * args.o_stride_l + static_cast<long long>(head) * args.o_stride_h + 64 * hf;
+    __nv_bfloat16* orow = out_row_ptr(args, q_row, head) + 64 * hf;
     if (have) {
       const float l_tot = l_sum + lbuf[(hf ^ 1) * 128 + row];
       const float inv = 1.0f / l_tot;
@@ -776,7 +820,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
     // ---- epilogue: O / l -> bf16 -> global
     const bool row_valid = q_row < args.Lq;
-    __nv_bfloat16* orow = args.o + static_cast<long long>(q_row) * args.o_stride_l + static_cast<long long>(head) * args.o_stride_h;
+    __nv_bfloat16* orow = out_row_ptr(args, q_row, head);
     if (ok && j > 0) {
       ok = warp_wait(wc, smem_u32(&bars->o_full[t][1]), (j - 1) & 1, kWaitOFull);
       if (ok) {
@@ -813,6 +857,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
 
   // ---- tear-down
+  if (args.o_n_ranks > 1) __threadfence_system();  // rows stored into other GPUs' memory
   tc_fence_before_sync();
   __syncthreads();
   if (bars->abort_flag) {

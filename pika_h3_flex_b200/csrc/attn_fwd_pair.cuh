@@ -84,18 +84,18 @@ static_assert(512 * kPairSoftmaxRegs + 128 * kPairHelperRegs <= AttnLayout<true>
               "setmaxnreg budget exceeds the launch allocation");
 
 // Merge the sorted key-tile lists of query tiles 4c .. 4c+3 into one list with a flag bit per query tile.
+// The index is checked as in build_pair_plan_kernel.
 __global__ void build_cluster_plan_kernel(const int32_t* __restrict__ row_ptr, const int32_t* __restrict__ col_idx,
-                                          int nqb, int n_clusters, int32_t* __restrict__ plan, int32_t* __restrict__ plan_cnt) {
+                                          int nqb, int n_clusters, int nnz, int nkb, int32_t* __restrict__ plan,
+                                          int32_t* __restrict__ plan_cnt, int* __restrict__ status) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= n_clusters) return;
+  bool bad = false;
   int pos[4], end[4];
-  for (int i = 0; i < 4; ++i) {
-    const int r = 4 * c + i;
-    pos[i] = (r < nqb) ? row_ptr[r] : 0;
-    end[i] = (r < nqb) ? row_ptr[r + 1] : 0;
-  }
-  int32_t* out = plan + row_ptr[4 * c];  // the merged list is never longer than the four lists together
-  int n = 0;
+  for (int i = 0; i < 4; ++i) row_range(row_ptr, 4 * c + i, nqb, nnz, pos[i], end[i], bad);
+  int32_t* out = plan + pos[0];  // the merged list is never longer than the four lists together
+  const int cap = nnz - pos[0];
+  int n = 0, prev = -1;
   for (;;) {
     int lo = 0x7FFFFFFF;
     for (int i = 0; i < 4; ++i)
@@ -107,9 +107,12 @@ __global__ void build_cluster_plan_kernel(const int32_t* __restrict__ row_ptr, c
         f |= 1 << i;
         ++pos[i];
       }
+    if (lo <= prev || lo >= nkb || n >= cap) { bad = true; continue; }
+    prev = lo;
     out[n++] = (lo << 4) | f;
   }
   plan_cnt[c] = n;
+  if (bad) report_bad_index(status, 4 * c);
 }
 
 // Partial results of the split pairs: `part` holds [slot][4 query tiles][128 rows][128] un-normalised output sums,
@@ -146,10 +149,11 @@ __global__ void combine_partials_kernel(const AttnArgs args, int n_clusters) {
     w.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
     w.z = pack_bf16x2(acc[4] * inv, acc[5] * inv);
     w.w = pack_bf16x2(acc[6] * inv, acc[7] * inv);
-    __nv_bfloat16* orow = args.o + static_cast<long long>(q_row) * args.o_stride_l + static_cast<long long>(head) * args.o_stride_h;
+    __nv_bfloat16* orow = out_row_ptr(args, q_row, head);
     *reinterpret_cast<uint4*>(orow + 8 * sub) = w;
     if (sub == 0 && args.lse) args.lse[static_cast<long long>(head) * args.Lq + q_row] = (args.fixed_m + log2f(l)) * 0.6931471805599453f;
   }
+  if (args.o_n_ranks > 1) __threadfence_system();  // rows stored into other GPUs' memory
 }
 
 template <bool kFp8, bool kSparse>
@@ -205,7 +209,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   int n_it;
   const int32_t* plan = nullptr;
   if constexpr (kSparse) {
-    plan = args.plan + args.row_ptr[min(4 * cl, args.nqb)];
+    plan = args.plan + clamp_row_ptr(args.row_ptr[min(4 * cl, args.nqb)], args.nnz);
     n_it = args.plan_cnt[cl];
   } else {
     n_it = args.n_kv_tiles;
@@ -532,7 +536,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");
     if (have) tc_fence_after_sync();
     const bool row_valid = q_row < args.Lq;
-    __nv_bfloat16* orow = args.o + static_cast<long long>(q_row) * args.o_stride_l + static_cast<long long>(head) * args.o_stride_h + 64 * hf;
+    __nv_bfloat16* orow = out_row_ptr(args, q_row, head) + 64 * hf;
     const float l_tot = l_sum + lbuf[(hf ^ 1) * 128 + row];
     if (!kSparse && part_slot >= 0) {
       // a share of the key tiles: leave the un-normalised sums for the combining kernel
@@ -582,6 +586,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   }  // run
 
   // ---- tear-down
+  if (args.o_n_ranks > 1) __threadfence_system();  // rows stored into other GPUs' memory
   tc_fence_before_sync();
   __syncthreads();
   if (bars->abort_flag) {

@@ -91,6 +91,14 @@ int32_t validate_attn(const h3a_attn_params* p) {
   if (p->mode == H3A_MODE_BLOCK_SPARSE && (!p->row_ptr || !p->col_idx || p->nnz < 0)) return H3A_ERR_ARG;
   if (!aligned16(p->o) || (p->o_stride_l % 8) != 0 || (p->o_stride_h % 8) != 0) return H3A_ERR_ALIGN;
   if (p->o_stride_l <= 0 || p->o_stride_h <= 0) return H3A_ERR_ARG;
+  if (p->o_n_ranks < 0 || p->o_n_ranks > H3A_MAX_RANKS) return H3A_ERR_ARG;
+  if (p->o_n_ranks > 1) {
+    if (p->o_rank_rows <= 0 || static_cast<int64_t>(p->o_rank_rows) * p->o_n_ranks < p->Lq) return H3A_ERR_SHAPE;
+    for (int r = 0; r < p->o_n_ranks; ++r) {
+      if (!p->o_rank_base[r]) return H3A_ERR_ARG;
+      if (!aligned16(p->o_rank_base[r])) return H3A_ERR_ALIGN;
+    }
+  }
   return H3A_OK;
 }
 
@@ -239,52 +247,9 @@ int32_t static_scratch_for_current_device(int32_t** out) {
   return H3A_OK;
 }
 
-}  // namespace
-
-extern "C" {
-
-int32_t h3a_version(int32_t* major, int32_t* minor) {
-  if (major) *major = H3A_VERSION_MAJOR;
-  if (minor) *minor = H3A_VERSION_MINOR;
-  return H3A_OK;
-}
-
-const char* h3a_status_string(int32_t s) {
-  switch (s) {
-    case H3A_OK: return "ok";
-    case H3A_ERR_ARG: return "invalid argument (null pointer, bad enum or flag)";
-    case H3A_ERR_ALIGN: return "pointer or stride not 16-byte aligned";
-    case H3A_ERR_SHAPE: return "unsupported shape (head dim must be 128, batch 1, extents > 0)";
-    case H3A_ERR_ARCH: return "device is not compute capability 10.x (B200)";
-    case H3A_ERR_LAUNCH: return "CUDA runtime or driver call failed";
-    case H3A_ERR_TIMEOUT: return "a bounded device-side wait ran out";
-    case H3A_ERR_WORKSPACE: return "workspace missing or too small";
-    case H3A_ERR_DRIVER: return "driver entry point cuTensorMapEncodeTiled not available";
-    case H3A_ERR_STATIC_SCRATCH: return "block index too large for the static scratch array (kept tiles + query-tile pairs > 262144)";
-    default: return "unknown status";
-  }
-}
-
-int32_t h3a_attn_workspace_bytes(const h3a_attn_params* p, size_t* bytes) {
-  if (!p || !bytes) return H3A_ERR_ARG;
-  if (p->mode == H3A_MODE_BLOCK_SPARSE) {
-    *bytes = sparse_workspace_bytes(p);
-  } else {
-    // optional: partial sums of the split last wave (dense launches with a logit bound); without it the launch
-    // simply does not split
-    const bool fixed = p->logit_bound > 0.f && p->logit_bound <= 30.f;
-    const bool pairs = fixed && pair_kernel_enabled() && p->Lq > 0 && p->H > 0 && (p->Lk + 127) / 128 >= kPairMinKeyTiles;
-    *bytes = pairs ? plan_split(p->Lq, p->Lk, p->H).bytes : 0;
-  }
-  return H3A_OK;
-}
-
-int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream) {
-  int32_t rc = validate_attn(p);
-  if (rc != H3A_OK) return rc;
-  rc = check_arch();
-  if (rc != H3A_OK) return rc;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
+// The launch behind h3a_attn_fwd and h3a_attn_fwd_sparse_static: the two differ only in where the scratch comes from.
+int32_t attn_fwd_impl(const h3a_attn_params* p, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  int32_t rc = H3A_OK;
   const bool fp8 = p->mode == H3A_MODE_FP8_QK;
   const bool sparse = p->mode == H3A_MODE_BLOCK_SPARSE;
 
@@ -308,6 +273,11 @@ int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream) {
   a.lse = p->lse;
   a.status = p->status_word;
   a.wait_ns = p->wait_limit_ns > 0 ? p->wait_limit_ns : 2000000000ll;
+  if (p->o_n_ranks > 1) {
+    a.o_n_ranks = p->o_n_ranks;
+    a.o_rank_rows = p->o_rank_rows;
+    for (int r = 0; r < p->o_n_ranks; ++r) a.o_rank[r] = static_cast<__nv_bfloat16*>(p->o_rank_base[r]);
+  }
   // fixed softmax reference: the bound rescaled like the logits (x softmax_scale is already in it), in log2 units.
   // Above 30 (2^-87 for a logit at minus the bound) the running-maximum kernel is used instead.
   const bool fixed = p->logit_bound > 0.f && p->logit_bound <= 30.f;
@@ -315,12 +285,12 @@ int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream) {
 
   if (sparse) {
     const size_t need = sparse_workspace_bytes(p);
-    if (!p->workspace || p->workspace_bytes < need) return H3A_ERR_WORKSPACE;
-    if (!aligned16(p->workspace)) return H3A_ERR_ALIGN;
-    int32_t* plan = static_cast<int32_t*>(p->workspace);
+    if (!workspace || workspace_bytes < need) return H3A_ERR_WORKSPACE;
+    if (!aligned16(workspace)) return H3A_ERR_ALIGN;
+    int32_t* plan = static_cast<int32_t*>(workspace);
     int32_t* plan_cnt = plan + p->nnz;
     const int threads = 128;
-    a.row_ptr = p->row_ptr; a.plan = plan; a.plan_cnt = plan_cnt;
+    a.row_ptr = p->row_ptr; a.plan = plan; a.plan_cnt = plan_cnt; a.nnz = p->nnz;
     a.heavy_pairs = (p->sparse_heavy_pairs > 0 && p->sparse_heavy_pairs < a.n_qpairs) ? p->sparse_heavy_pairs : 0;
     // A CTA pair computes a key tile for two adjacent query tiles whenever either lists it.  With very sparse
     // neighbourhood masks that duplicated work outweighs what the pair saves (measured: 7 % density, 7 % extra
@@ -331,25 +301,25 @@ int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream) {
       // are no more groups of four than pairs of two, so the same workspace holds it)
       const int n_clusters = (p->Lq + 511) / 512;
       h3a::build_cluster_plan_kernel<<<(n_clusters + threads - 1) / threads, threads, 0, st>>>(p->row_ptr, p->col_idx, a.nqb,
-                                                                                              n_clusters, plan, plan_cnt);
+                                                                                              n_clusters, p->nnz, a.nkb, plan, plan_cnt, p->status_word);
       if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
       if ((rc = make_map(&mk, p->k, false, p->Lk, p->H, p->k_stride_l, p->k_stride_h, h3a::kPairKBoxRows)) != H3A_OK) return rc;
       return launch_attn_pair<false, true>(mq, mk, mv, a, st);
     }
     h3a::build_pair_plan_kernel<<<(a.n_qpairs + threads - 1) / threads, threads, 0, st>>>(p->row_ptr, p->col_idx, a.nqb,
-                                                                                         a.n_qpairs, plan, plan_cnt);
+                                                                                         a.n_qpairs, p->nnz, a.nkb, plan, plan_cnt, p->status_word);
     if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
     return fixed ? launch_attn<false, true, true>(mq, mk, mv, a, st) : launch_attn<false, true, false>(mq, mk, mv, a, st);
   }
   if (fixed && pair_kernel_enabled() && a.n_kv_tiles >= kPairMinKeyTiles) {
     a.split_begin = static_cast<int>((p->Lq + 511) / 512 * p->H);
     a.kv_splits = 1;
-    if (p->workspace && aligned16(p->workspace)) {
+    if (workspace && aligned16(workspace)) {
       const SplitPlan sp = plan_split(p->Lq, p->Lk, p->H);
-      if (sp.kv_splits > 1 && p->workspace_bytes >= sp.bytes) {
+      if (sp.kv_splits > 1 && workspace_bytes >= sp.bytes) {
         a.split_begin = sp.split_begin;
         a.kv_splits = sp.kv_splits;
-        a.part = static_cast<float*>(p->workspace);
+        a.part = static_cast<float*>(workspace);
       }
     }
     // CTA pairs: each CTA stages 32-key boxes of K (its share of every 64-key MMA group) and 64 columns of V
@@ -360,19 +330,27 @@ int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream) {
   return fixed ? launch_attn<false, false, true>(mq, mk, mv, a, st) : launch_attn<false, false, false>(mq, mk, mv, a, st);
 }
 
-int32_t h3a_qk_prep(const h3a_prep_params* p, void* stream) {
+
+// The launch behind h3a_qk_prep and h3a_qk_prep_scatter (`scatter`: rows go to the head's owning rank).
+int32_t prep_impl(const h3a_prep_params* p, const h3a_head_scatter* q_to, const h3a_head_scatter* k_to, bool scatter, void* stream) {
   if (!p) return H3A_ERR_ARG;
   if (p->d != 128 || p->H <= 0) return H3A_ERR_SHAPE;
   if (p->rope_mode != H3A_ROPE_INTERLEAVED && p->rope_mode != H3A_ROPE_HALF) return H3A_ERR_ARG;
-  if (p->flags & ~H3A_PREP_FP8) return H3A_ERR_ARG;
+  if (p->flags & ~(H3A_PREP_FP8 | H3A_PREP_NO_NORM)) return H3A_ERR_ARG;
   const bool fp8 = (p->flags & H3A_PREP_FP8) != 0;
+  if (scatter && fp8) return H3A_ERR_ARG;  // block scales need whole blocks of the full sequence: quantise at the owner
   int32_t rc = check_arch();
   if (rc != H3A_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   for (int which = 0; which < 2; ++which) {
     h3a::PrepArgs a;
+    std::memset(&a, 0, sizeof(a));
     a.in = static_cast<const __nv_bfloat16*>(which ? p->k_in : p->q_in);
-    if (!a.in) continue;
+    const h3a_head_scatter* to = which ? k_to : q_to;
+    if (!a.in) {
+      if (to) return H3A_ERR_ARG;
+      continue;
+    }
     a.out = which ? p->k_out : p->q_out;
     a.scale = which ? p->k_scale : p->q_scale;
     a.stride_l = which ? p->k_stride_l : p->q_stride_l;
@@ -383,7 +361,22 @@ int32_t h3a_qk_prep(const h3a_prep_params* p, void* stream) {
     a.weight = which ? p->k_weight : p->q_weight;
     a.eps = p->eps > 0.f ? p->eps : 1e-6f;
     a.rope_half = p->rope_mode == H3A_ROPE_HALF;
+    a.no_norm = (p->flags & H3A_PREP_NO_NORM) != 0;
     if (a.L <= 0) return H3A_ERR_SHAPE;
+    if (scatter) {
+      if (!to) return H3A_ERR_ARG;
+      if (to->n_ranks < 1 || to->n_ranks > H3A_MAX_RANKS || to->heads_per_rank < 1 || to->head0 < 0 || to->row_offset < 0) return H3A_ERR_ARG;
+      if (static_cast<int64_t>(to->row_offset) + a.L > to->L_total) return H3A_ERR_SHAPE;
+      if (static_cast<int64_t>(to->head0) + a.H > static_cast<int64_t>(to->heads_per_rank) * to->n_ranks) return H3A_ERR_SHAPE;
+      for (int r = 0; r < to->n_ranks; ++r) {
+        if (!to->base[r]) return H3A_ERR_ARG;
+        if (!aligned16(to->base[r])) return H3A_ERR_ALIGN;
+        a.rank_out[r] = to->base[r];
+      }
+      a.n_ranks = to->n_ranks; a.heads_per_rank = to->heads_per_rank; a.round_robin = to->round_robin != 0;
+      a.head0 = to->head0; a.row_offset = to->row_offset; a.L_total = to->L_total;
+      a.out = to->base[0];
+    }
     if (!a.out || (fp8 && !a.scale)) return H3A_ERR_ARG;
     if (!aligned16(a.in) || !aligned16(a.out) || (a.stride_l % 8) || (a.stride_h % 8)) return H3A_ERR_ALIGN;
     if (a.rope && !aligned16(a.rope)) return H3A_ERR_ALIGN;
@@ -394,6 +387,96 @@ int32_t h3a_qk_prep(const h3a_prep_params* p, void* stream) {
     if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
   }
   return H3A_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t h3a_version(int32_t* major, int32_t* minor) {
+  if (major) *major = H3A_VERSION_MAJOR;
+  if (minor) *minor = H3A_VERSION_MINOR;
+  return H3A_OK;
+}
+
+const char* h3a_status_string(int32_t s) {
+  switch (s) {
+    case H3A_OK: return "ok";
+    case H3A_ERR_ARG: return "invalid argument (null pointer, bad enum or flag)";
+    case H3A_ERR_ALIGN: return "pointer or stride not 16-byte aligned";
+    case H3A_ERR_SHAPE: return "unsupported shape (head dim must be 128, batch 1, extents > 0)";
+    case H3A_ERR_ARCH: return "device is not compute capability 10.x (B200)";
+    case H3A_ERR_LAUNCH: return "CUDA runtime or driver call failed";
+    case H3A_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case H3A_ERR_WORKSPACE: return "workspace missing or too small";
+    case H3A_ERR_DRIVER: return "driver entry point cuTensorMapEncodeTiled not available";
+    case H3A_ERR_STATIC_SCRATCH: return "block index too large for the static scratch array (kept tiles + query-tile pairs > 262144)";
+    case H3A_ERR_INDEX: return "malformed block index (row pointers must not decrease and stay within nnz; columns in range, ascending)";
+    default: return "unknown status";
+  }
+}
+
+int32_t h3a_attn_workspace_bytes(const h3a_attn_params* p, size_t* bytes) {
+  if (!p || !bytes) return H3A_ERR_ARG;
+  if (p->mode == H3A_MODE_BLOCK_SPARSE) {
+    *bytes = sparse_workspace_bytes(p);
+  } else {
+    // optional: partial sums of the split last wave (dense launches with a logit bound); without it the launch
+    // simply does not split
+    const bool fixed = p->logit_bound > 0.f && p->logit_bound <= 30.f;
+    const bool pairs = fixed && pair_kernel_enabled() && p->Lq > 0 && p->H > 0 && (p->Lk + 127) / 128 >= kPairMinKeyTiles;
+    *bytes = pairs ? plan_split(p->Lq, p->Lk, p->H).bytes : 0;
+  }
+  return H3A_OK;
+}
+
+int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream) {
+  int32_t rc = validate_attn(p);
+  if (rc != H3A_OK) return rc;
+  rc = check_arch();
+  if (rc != H3A_OK) return rc;
+  return attn_fwd_impl(p, p->workspace, p->workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int32_t h3a_qk_prep(const h3a_prep_params* p, void* stream) { return prep_impl(p, nullptr, nullptr, false, stream); }
+
+int32_t h3a_qk_prep_scatter(const h3a_prep_params* p, const h3a_head_scatter* q_to, const h3a_head_scatter* k_to, void* stream) {
+  return prep_impl(p, q_to, k_to, true, stream);
+}
+
+int32_t h3a_peer_alloc(size_t bytes, void** ptr, uint8_t handle[H3A_PEER_HANDLE_BYTES]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == H3A_PEER_HANDLE_BYTES, "handle size");
+  if (!ptr || !handle || bytes == 0) return H3A_ERR_ARG;
+  void* d = nullptr;
+  if (cudaMalloc(&d, bytes) != cudaSuccess) return H3A_ERR_LAUNCH;
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, d) != cudaSuccess) {
+    cudaFree(d);
+    return H3A_ERR_LAUNCH;
+  }
+  std::memcpy(handle, &h, sizeof(h));
+  *ptr = d;
+  return H3A_OK;
+}
+
+int32_t h3a_peer_open(const uint8_t handle[H3A_PEER_HANDLE_BYTES], void** ptr) {
+  if (!ptr || !handle) return H3A_ERR_ARG;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, sizeof(h));
+  void* d = nullptr;
+  if (cudaIpcOpenMemHandle(&d, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return H3A_ERR_LAUNCH;
+  *ptr = d;
+  return H3A_OK;
+}
+
+int32_t h3a_peer_close(void* ptr) {
+  if (!ptr) return H3A_ERR_ARG;
+  return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
+}
+
+int32_t h3a_peer_free(void* ptr) {
+  if (!ptr) return H3A_ERR_ARG;
+  return cudaFree(ptr) == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
 }
 
 int32_t h3a_rope_table(const float* pos, int32_t L, const int32_t split[3], float theta, float* table, void* stream) {
@@ -503,38 +586,11 @@ int32_t h3a_attn_fwd_sparse_static(const h3a_attn_params* p, void* stream) {
   if (rc != H3A_OK) return rc;
   int32_t* scratch = nullptr;
   if ((rc = static_scratch_for_current_device(&scratch)) != H3A_OK) return rc;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-
-  CUtensorMap mq, mk, mv;
-  if ((rc = make_map(&mq, p->q, false, p->Lq, p->H, p->q_stride_l, p->q_stride_h)) != H3A_OK) return rc;
-  if ((rc = make_map(&mk, p->k, false, p->Lk, p->H, p->k_stride_l, p->k_stride_h)) != H3A_OK) return rc;
-  if ((rc = make_map(&mv, p->v, false, p->Lk, p->H, p->v_stride_l, p->v_stride_h)) != H3A_OK) return rc;
-
-  AttnArgs a;
-  std::memset(&a, 0, sizeof(a));
-  a.Lq = p->Lq; a.Lk = p->Lk; a.H = p->H;
-  a.nqb = (p->Lq + 127) / 128;
-  a.nkb = (p->Lk + 127) / 128;
-  a.n_kv_tiles = a.nkb;
-  a.n_qpairs = static_cast<int>(n_qpairs);
-  const float scale = p->softmax_scale > 0.f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->d));
-  a.scale_log2 = scale * 1.4426950408889634f;
-  a.o = static_cast<__nv_bfloat16*>(p->o);
-  a.o_stride_l = p->o_stride_l; a.o_stride_h = p->o_stride_h;
-  a.lse = p->lse;
-  a.status = p->status_word;
-  a.wait_ns = p->wait_limit_ns > 0 ? p->wait_limit_ns : 2000000000ll;
-
-  // The plan kernel writes every count and every plan entry the attention kernel will read, so nothing in
-  // the array has to start at zero and whatever the previous call left there is never looked at.
-  int32_t* plan = scratch;
-  int32_t* plan_cnt = scratch + p->nnz;
-  const int threads = 128;
-  h3a::build_pair_plan_kernel<<<(a.n_qpairs + threads - 1) / threads, threads, 0, st>>>(p->row_ptr, p->col_idx, a.nqb,
-                                                                                       a.n_qpairs, plan, plan_cnt);
-  if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
-  a.row_ptr = p->row_ptr; a.plan = plan; a.plan_cnt = plan_cnt;
-  return launch_attn<false, true>(mq, mk, mv, a, st);
+  // The plan kernel writes every count and every plan entry the attention kernel will read, so nothing in the
+  // array has to start at zero and whatever the previous call left there is never looked at.  From here on the
+  // launch is the one h3a_attn_fwd makes (same kernel choice from logit_bound and density, same scheduling hint),
+  // so the two entry points give bit-identical results for the same arguments.
+  return attn_fwd_impl(p, scratch, kStaticScratchInts * sizeof(int32_t), static_cast<cudaStream_t>(stream));
 }
 
 #ifdef H3A_TRACE
@@ -641,7 +697,8 @@ int32_t h3a_read_device_status(const int32_t* status_word, void* stream, int32_t
   if (cudaMemcpyAsync(&v, status_word, sizeof(v), cudaMemcpyDeviceToHost, st) != cudaSuccess) return H3A_ERR_LAUNCH;
   if (cudaStreamSynchronize(st) != cudaSuccess) return H3A_ERR_LAUNCH;
   if (raw) *raw = v;
-  return v == 0 ? H3A_OK : H3A_ERR_TIMEOUT;
+  if (v == 0) return H3A_OK;
+  return (v & 0xFF) == h3a::kBadBlockIndex ? H3A_ERR_INDEX : H3A_ERR_TIMEOUT;
 }
 
 }  // extern "C"

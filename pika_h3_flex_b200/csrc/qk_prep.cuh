@@ -20,7 +20,24 @@ struct PrepArgs {
   const float* weight;  // [128] or null
   float eps;
   int rope_half;        // 0: pairs (2j,2j+1); 1: pairs (j, j+64)
+  int no_norm;          // skip the RMSNorm (re-layout / quantisation of rows that are already prepared, or of V)
+  // Sequence parallelism (n_ranks > 0, bf16 only): head h of the input is global head head0 + h, owned by rank
+  // (head0 + h) / heads_per_rank [blocks] or (head0 + h) % n_ranks [round robin]; its rows go to that rank's
+  // [heads_per_rank, L_total, 128] buffer (own memory or a peer GPU's), token l at row row_offset + l.
+  void* rank_out[8];
+  int n_ranks, heads_per_rank, round_robin, head0, row_offset, L_total;
 };
+
+// where row l of (local) head `head` is written: head-major in `out`, or at the head's owner
+__device__ __forceinline__ __nv_bfloat16* prep_dst_bf16(const PrepArgs& a, int head, int l) {
+  if (a.n_ranks > 0) {
+    const int h = a.head0 + head;
+    const int owner = a.round_robin ? h % a.n_ranks : h / a.heads_per_rank;
+    const int slot = a.round_robin ? h / a.n_ranks : h % a.heads_per_rank;
+    return static_cast<__nv_bfloat16*>(a.rank_out[owner]) + (static_cast<long long>(slot) * a.L_total + a.row_offset + l) * 128;
+  }
+  return static_cast<__nv_bfloat16*>(a.out) + (static_cast<long long>(head) * a.L + l) * 128;
+}
 
 // One CTA = one (128-token block, head).  Thread (r = tid/8, sub = tid%8) owns, in each of 4 passes,
 // the two 8-element chunks [8*sub, 8*sub+8) and [64+8*sub, 64+8*sub+8) of row pass*32 + r, so that both
@@ -69,7 +86,7 @@ __global__ void __launch_bounds__(kPrepThreads) qk_prep_kernel(const PrepArgs a)
     ss += __shfl_xor_sync(0xFFFFFFFFu, ss, 1);
     ss += __shfl_xor_sync(0xFFFFFFFFu, ss, 2);
     ss += __shfl_xor_sync(0xFFFFFFFFu, ss, 4);
-    const float rinv = rsqrtf(ss * (1.0f / 128.0f) + a.eps);
+    const float rinv = a.no_norm ? 1.0f : rsqrtf(ss * (1.0f / 128.0f) + a.eps);
 #pragma unroll
     for (int x = 0; x < 8; ++x) {
       x_lo[x] = x_lo[x] * rinv * w_lo[x];
@@ -120,7 +137,7 @@ __global__ void __launch_bounds__(kPrepThreads) qk_prep_kernel(const PrepArgs a)
         amax = fmaxf(amax, fmaxf(fabsf(x_lo[x]), fabsf(x_hi[x])));
       }
     } else if (valid) {
-      __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(a.out) + (static_cast<long long>(head) * a.L + l) * 128;
+      __nv_bfloat16* dst = prep_dst_bf16(a, head, l);
       uint4 o0, o1;
       __nv_bfloat162* p0 = reinterpret_cast<__nv_bfloat162*>(&o0);
       __nv_bfloat162* p1 = reinterpret_cast<__nv_bfloat162*>(&o1);
@@ -166,6 +183,7 @@ __global__ void __launch_bounds__(kPrepThreads) qk_prep_kernel(const PrepArgs a)
       }
     }
   }
+  if (a.n_ranks > 1) __threadfence_system();  // rows stored into other GPUs' memory: ordered before this kernel's completion is observed
 }
 
 // table[l][j] = (cos, sin)(pos[l][axis(j)] * theta^(-2 jj / d_axis)), computed in double like the host

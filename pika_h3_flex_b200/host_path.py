@@ -53,8 +53,10 @@ class HostJointAttention:
     bf16 host tensors.  Device staging buffers and streams are created once and reused."""
 
     def __init__(self, L: int, H: int, mode: int = _lib.MODE_DENSE_BF16, block_index: Optional[ops.BlockIndex] = None,
-                 head_groups: Optional[Sequence[int]] = None, device=None, copy_to_compute: float = 0.75):
+                 head_groups: Optional[Sequence[int]] = None, device=None, copy_to_compute: float = 0.75,
+                 status: Optional[ops.StatusWord] = None):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.status = status if status is not None else ops.StatusWord(self.device)
         self.L, self.H, self.mode, self.block_index = L, H, mode, block_index
         if head_groups is None:
             head_groups = default_head_groups(H, copy_to_compute)
@@ -83,7 +85,7 @@ class HostJointAttention:
             cur.wait_event(ev_in)
             qp, kp, qs, ks = ops.qk_prep(self.dq[:, h0:h1], self.dk[:, h0:h1], rope, rope, fp8=fp8)
             ops.attn_fwd(qp, kp, self.dv[:, h0:h1], self.mode, qs, ks, self.block_index, out=self.do[:, h0:h1],
-                         logit_bound=ops.normed_logit_bound(fp8=fp8))
+                         logit_bound=ops.normed_logit_bound(fp8=fp8), status_word=self.status.tensor())
             ev_c = torch.cuda.Event()
             ev_c.record(cur)
             self.s_out.wait_event(ev_c)
@@ -92,42 +94,196 @@ class HostJointAttention:
         cur.wait_stream(self.s_out)  # the result is complete in stream order of the caller's stream
         return out
 
+    def check_status(self) -> None:
+        """Synchronise and raise ``H3AError`` when a launch of this object gave up a bounded wait or refused its block
+        index: the host buffer then holds an incomplete result."""
+        self.status.check("HostJointAttention")
+
 
 class HostUlyssesAttention:
     """The host-buffer call under Ulysses sequence parallelism: every rank passes pinned host tensors holding ITS
     ``[L/P, H, 128]`` shard of Q, K, V and gets its shard of the output in a pinned host tensor.
 
     The pipeline of :class:`HostJointAttention` (copy-in / compute / copy-out over groups of heads) needs each
-    group to be a CONTIGUOUS head range, so heads are dealt to ranks round-robin here (head ``h`` is computed by
-    rank ``h % P``) instead of in blocks: local head slots ``[j0, j1)`` are then the heads ``[j0 P, j1 P)``.  Per
-    group: one 2-D copy per tensor brings the head range in (copy stream), preparation and a pack into per-peer
-    blocks run on a preparation stream and start the inbound ``all_to_all``; the caller's stream places the blocks,
-    runs the attention and starts the outbound ``all_to_all``; a copy-out stream unpacks into token-major order
-    and copies the head range to the host.  Dense bf16 and block-sparse modes (FP8-QK would add a scale exchange).
+    group to be a CONTIGUOUS head range on the host side, so heads are dealt to ranks round-robin here (head ``h``
+    is computed by rank ``h % P`` in its head slot ``h // P``) instead of in blocks: local head slots ``[j0, j1)``
+    are then the heads ``[j0 P, j1 P)``.  Per group of slots, on four streams:
+
+      copy-in      one 2-D copy per tensor brings the head range into token-major staging buffers
+      scatter      the preparation kernel (RMSNorm + rotation; a plain re-layout for V) stores every row straight
+                   into the memory of the rank that owns the row's head (``h3a_qk_prep_scatter``, see ``peer.py``);
+                   the ranks then meet
+      attention    each rank runs its slots of the group; the kernel stores every output row straight into the
+                   token-major output staging buffer of the rank that holds the row's token; the ranks meet again
+      copy-out     the head range of the output staging buffer goes to the host
+
+    so a group's copy-in overlaps the previous group's attention and the copy-out of the one before.  FP8-QK:
+    the rows travel as bf16 and each owner quantises its heads (block scales need whole 128-token blocks of the
+    full sequence).  ``transport="nccl"`` keeps the staged ``all_to_all`` exchange (dense bf16 and block-sparse
+    only) for comparison.  ``stage_ms()`` gives the device time of each stage of the last call.
     """
 
     def __init__(self, Ls: int, H: int, mode: int = _lib.MODE_DENSE_BF16, block_index: Optional[ops.BlockIndex] = None,
-                 group=None, slot_groups: Optional[Sequence[int]] = None, device=None):
+                 group=None, slot_groups: Optional[Sequence[int]] = None, device=None, status: Optional[ops.StatusWord] = None,
+                 transport: str = "auto"):
         import torch.distributed as dist
 
-        if mode == _lib.MODE_FP8_QK:
-            raise NotImplementedError("FP8-QK under the host-buffer Ulysses path is not built")
         self.dist = dist
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        if transport not in ("auto", "peer", "nccl"):
+            raise ValueError("transport must be auto, peer or nccl")
+        self.transport = "peer" if transport == "auto" else transport
+        if self.transport == "nccl" and mode == _lib.MODE_FP8_QK:
+            raise NotImplementedError("FP8-QK under the host-buffer Ulysses path needs the peer transport")
+        self.status = status if status is not None else ops.StatusWord(self.device)
         self.Ls, self.H, self.mode, self.block_index = Ls, H, mode, block_index
-        self.hp = (H + self.world - 1) // self.world  # head slots per rank
-        if slot_groups is None:  # measured on 2 GPUs: the fine schedule (26.7 ms) beats five coarse groups (28.8 ms)
-            slot_groups = default_head_groups(self.hp)
+        P = self.world
+        self.hp = (H + P - 1) // P  # head slots per rank
+        if block_index is not None:
+            nt = (P * Ls + ops.TILE - 1) // ops.TILE
+            if block_index.n_q_tiles != nt or block_index.n_k_tiles != nt:
+                raise ValueError("block index does not describe the full sequence")
+        if slot_groups is None:
+            # peer transport: a group costs two meetings of the ranks and nothing else, so small groups hide the most
+            # copy time; the staged exchange pays per group and prefers the coarser schedule
+            slot_groups = [1] * self.hp if (self.transport == "peer" and self.hp <= 8) else default_head_groups(self.hp)
         if sum(slot_groups) != self.hp or min(slot_groups) < 1:
             raise ValueError("slot_groups must be positive and sum to ceil(H / world)")
         self.slot_groups = list(slot_groups)
         mk = lambda: torch.empty(Ls, H, ops.HEAD_DIM, dtype=torch.bfloat16, device=self.device)
-        self.dq, self.dk, self.dv, self.do = mk(), mk(), mk(), mk()
+        self.dq, self.dk, self.dv = mk(), mk(), mk()
         self.s_in, self.s_prep, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
         self._keep = []
+        self._marks = None
+        self.arena = None
+        if self.transport == "peer":
+            from .peer import Carver, PeerArena
+
+            c = Carver()
+            L = P * Ls
+            nb = self.hp * L * ops.HEAD_DIM * 2
+            self._off = {n: c.take(nb) for n in ("q", "k", "v")}
+            self._off["o"] = c.take(Ls * H * ops.HEAD_DIM * 2)
+            self.arena = PeerArena(c.size, group, self.device)
+            self.qh, self.kh, self.vh = (self.arena.tensor(self._off[n], (self.hp, L, ops.HEAD_DIM), torch.bfloat16) for n in ("q", "k", "v"))
+            self.do = self.arena.tensor(self._off["o"], (Ls, H, ops.HEAD_DIM), torch.bfloat16)
+        else:
+            self.do = mk()
+
+    def close(self) -> None:
+        if self.arena is not None:
+            self.arena.close()
+            self.arena = None
+
+    def check_status(self) -> None:
+        self.status.check("HostUlyssesAttention")
+
+    def stage_ms(self):
+        """Device time of each stage of the last call on this rank (sums over the groups; the stages overlap, so the
+        sums add up to more than the call): host->device copies, preparation + scatter, attention, device->host
+        copies, and the span of the whole call."""
+        if not self._marks:
+            return None
+        torch.cuda.synchronize(self.device)
+        out = {k: sum(a.elapsed_time(b) for a, b in v) for k, v in self._marks.items() if k != "span"}
+        a, b = self._marks["span"]
+        out["call"] = a.elapsed_time(b)
+        return out
+
+    def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rope: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+        Ls, H, Cc = self.Ls, self.H, ops.HEAD_DIM
+        for t in (q, k, v, out):
+            if t.is_cuda or not t.is_pinned() or t.dtype != torch.bfloat16 or tuple(t.shape) != (Ls, H, Cc) or not t.is_contiguous():
+                raise ValueError("host tensors must be pinned, contiguous bf16 [L/P, H, 128] shards")
+        return self._call_peer(q, k, v, rope, out) if self.transport == "peer" else self._call_nccl(q, k, v, rope, out)
+
+    def _call_peer(self, q, k, v, rope, out):
+        P, Ls, H, Cc, rank = self.world, self.Ls, self.H, ops.HEAD_DIM, self.rank
+        L = P * Ls
+        fp8 = self.mode == _lib.MODE_FP8_QK
+        cur = torch.cuda.current_stream(self.device)
+        for s in (self.s_in, self.s_prep, self.s_out):
+            s.wait_stream(cur)  # staging buffers may still be in use by earlier work on the caller's stream
+        bound = ops.normed_logit_bound(fp8=fp8)
+        ev = lambda: torch.cuda.Event(enable_timing=True)
+        marks = {"h2d": [], "prep_scatter": [], "attention": [], "d2h": []}
+        span0 = ev()
+        span0.record(cur)
+        ranges, ev_in = [], []
+        j0 = 0
+        for n in self.slot_groups:
+            h0, h1 = j0 * P, min((j0 + n) * P, H)
+            ranges.append((j0, n, h0, h1))
+            a, b = ev(), ev()
+            a.record(self.s_in)
+            if h1 > h0:
+                for dst, src in ((self.dq, q), (self.dk, k), (self.dv, v)):
+                    _copy_heads(dst, src, h0, h1, False, self.s_in)
+            b.record(self.s_in)
+            marks["h2d"].append((a, b))
+            ev_in.append(b)
+            j0 += n
+
+        def owners(name, h0):
+            return ops.HeadOwners([self.arena.addr(p, self._off[name]) for p in range(P)], self.hp, True, rank * Ls, L, head0=h0)
+
+        def stage_in(g):
+            """Scatter stream: prepare group g's heads of this rank's tokens into their owners' memory, then meet."""
+            _, n, h0, h1 = ranges[g]
+            with torch.cuda.stream(self.s_prep):
+                self.s_prep.wait_event(ev_in[g])
+                a, b = ev(), ev()
+                a.record(self.s_prep)
+                if h1 > h0:
+                    ops.prep_scatter(self.dq[:, h0:h1], owners("q", h0), rope)
+                    ops.prep_scatter(self.dk[:, h0:h1], owners("k", h0), rope)
+                    ops.prep_scatter(self.dv[:, h0:h1], owners("v", h0), no_norm=True)
+                b.record(self.s_prep)
+                marks["prep_scatter"].append((a, b))
+                self.arena.barrier()
+                done = torch.cuda.Event()
+                done.record(self.s_prep)
+            return done
+
+        pending = stage_in(0)
+        for g, (j0, n, h0, h1) in enumerate(ranges):
+            cur.wait_event(pending)
+            n_real = sum(1 for j in range(j0, j0 + n) if j * P + rank < H)  # this rank's real heads among the group's slots
+            if n_real > 0:
+                a, b = ev(), ev()
+                a.record(cur)
+                qg, kg, vg = (t[j0 : j0 + n_real].permute(1, 0, 2) for t in (self.qh, self.kh, self.vh))
+                qs = ks = None
+                if fp8:
+                    qg, kg, qs, ks = ops.qk_prep(qg, kg, fp8=True, no_norm=True)
+                head = j0 * P + rank  # first head of the launch; the next slot's head is P heads further
+                to = ops.RankOutputs([self.arena.addr(t, self._off["o"]) + head * Cc * 2 for t in range(P)], Ls, H * Cc, P * Cc)
+                ops.attn_fwd(qg, kg, vg, self.mode, qs, ks, self.block_index, out_ranks=to, logit_bound=bound,
+                             status_word=self.status.tensor())
+                b.record(cur)
+                marks["attention"].append((a, b))
+            if g + 1 < len(ranges):
+                pending = stage_in(g + 1)  # issued while this group's attention runs
+            self.arena.barrier()  # every rank's output rows of this group have landed
+            landed = torch.cuda.Event()
+            landed.record(cur)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(landed)
+                a, b = ev(), ev()
+                a.record(self.s_out)
+                if h1 > h0:
+                    _copy_heads(out, self.do, h0, h1, True, self.s_out)
+                b.record(self.s_out)
+                marks["d2h"].append((a, b))
+        cur.wait_stream(self.s_out)  # the result is complete in stream order of the caller's stream
+        span1 = ev()
+        span1.record(cur)
+        marks["span"] = (span0, span1)
+        self._marks = marks
+        return out
 
     def _pack(self, x_hm: torch.Tensor, hg: int) -> torch.Tensor:
         """``[n <= hg*P, Ls, C]`` head-major (head ``j*P + p`` at row ``j*P + p``) -> ``[P, hg, Ls, C]`` contiguous: the
@@ -137,11 +293,9 @@ class HostUlyssesAttention:
             x_hm = torch.cat([x_hm, x_hm.new_zeros(hg * P - x_hm.shape[0], Ls, Cc)], dim=0)
         return x_hm.view(hg, P, Ls, Cc).permute(1, 0, 2, 3).contiguous()
 
-    def __call__(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, rope: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+    def _call_nccl(self, q, k, v, rope, out):
+        """The staged form: per group, pack per peer, ``all_to_all``, place, attention, pack, ``all_to_all``, unpack."""
         dist, P, Ls, H, Cc = self.dist, self.world, self.Ls, self.H, ops.HEAD_DIM
-        for t in (q, k, v, out):
-            if t.is_cuda or not t.is_pinned() or t.dtype != torch.bfloat16 or tuple(t.shape) != (Ls, H, Cc) or not t.is_contiguous():
-                raise ValueError("host tensors must be pinned, contiguous bf16 [L/P, H, 128] shards")
         cur = torch.cuda.current_stream(self.device)
         for s in (self.s_in, self.s_prep, self.s_out):
             s.wait_stream(cur)  # staging buffers may still be in use by earlier work on the caller's stream
@@ -204,7 +358,7 @@ class HostUlyssesAttention:
             qh, kh, vh = (s.permute(1, 0, 2, 3).reshape(n, P * Ls, Cc) for s in staged)  # [head slot, all tokens, c]
             oh = torch.empty(n, P * Ls, Cc, dtype=torch.bfloat16, device=self.device)
             ops.attn_fwd(qh.permute(1, 0, 2), kh.permute(1, 0, 2), vh.permute(1, 0, 2), self.mode, None, None, self.block_index,
-                         out=oh.permute(1, 0, 2), logit_bound=bound)
+                         out=oh.permute(1, 0, 2), logit_bound=bound, status_word=self.status.tensor())
             if g + 1 < len(ranges):
                 # the next group's preparation and inbound exchange are issued while this group's attention runs (host
                 # time hidden behind it) and BEFORE this group's outbound exchange, which has to wait for the attention

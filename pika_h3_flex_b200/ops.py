@@ -40,6 +40,64 @@ def _lhd(t: torch.Tensor, name: str, dtypes) -> Tuple[int, int, int, int]:
 
 
 @dataclass
+class RankOutputs:
+    """Where the attention output goes under sequence parallelism: query row ``g`` is stored at row ``g % rows`` of
+    the buffer at device address ``bases[g // rows]`` (this process's memory or a peer GPU's, see ``peer.py``), head
+    ``j`` of the launch at ``j * stride_h`` elements, rows ``stride_l`` elements apart; each base already points at
+    the launch's first head."""
+
+    bases: list
+    rows: int
+    stride_l: int
+    stride_h: int
+
+
+@dataclass
+class HeadOwners:
+    """Where prepared rows go under sequence parallelism (``h3a_head_scatter``): ``bases[p]`` is the device address of
+    rank p's ``[heads_per_rank, L_total, 128]`` bf16 buffer; head ``head0 + h`` of the input belongs to rank
+    ``// heads_per_rank`` (blocks) or ``% n_ranks`` (``round_robin``); this shard's token l is row ``row_offset + l``."""
+
+    bases: list
+    heads_per_rank: int
+    round_robin: bool
+    row_offset: int
+    L_total: int
+    head0: int = 0
+
+    def c_struct(self):
+        s = _lib.HeadScatter()
+        for r, b in enumerate(self.bases):
+            s.base[r] = b
+        s.n_ranks, s.heads_per_rank, s.round_robin = len(self.bases), int(self.heads_per_rank), int(bool(self.round_robin))
+        s.head0, s.row_offset, s.L_total = int(self.head0), int(self.row_offset), int(self.L_total)
+        return s
+
+
+def prep_scatter(x: torch.Tensor, to: HeadOwners, rope: Optional[torch.Tensor] = None, weight: Optional[torch.Tensor] = None,
+                 eps: float = 1e-6, rope_half: bool = False, no_norm: bool = False) -> None:
+    """``h3a_qk_prep_scatter`` for one tensor: prepare this rank's ``x [Ls, H, 128]`` bf16 rows (RMSNorm x ``weight``,
+    rotation by ``rope``; ``no_norm`` with no table = the plain re-layout V needs) and store each row at its head's
+    owning rank.  Returns nothing: the rows are in the owners' buffers once every rank's kernel has finished."""
+    _require_cuda(x)
+    L, H, sl, sh = _lhd(x, "x", (torch.bfloat16,))
+    p = PrepParams()
+    p.d, p.H, p.eps = HEAD_DIM, H, float(eps)
+    p.rope_mode = _lib.ROPE_HALF if rope_half else _lib.ROPE_INTERLEAVED
+    p.flags = _lib.PREP_NO_NORM if no_norm else 0
+    p.q_in, p.q_stride_l, p.q_stride_h, p.Lq = x.data_ptr(), sl, sh, L
+    if rope is not None:
+        if rope.shape != (L, 64, 2) or rope.dtype != torch.float32 or not rope.is_contiguous():
+            raise ValueError("rope must be a contiguous fp32 [L, 64, 2] table")
+        p.q_rope = rope.data_ptr()
+    if weight is not None:
+        weight = weight.to(torch.float32).contiguous()
+        p.q_weight = weight.data_ptr()
+    st = to.c_struct()
+    check(_lib.load().h3a_qk_prep_scatter(C.byref(p), C.byref(st), None, _stream()), "h3a_qk_prep_scatter")
+
+
+@dataclass
 class BlockIndex:
     """CSR index over 128x128 tiles: ``row_ptr [nQB+1]``, ``col_idx [nnz]`` (int32, columns ascending)."""
 
@@ -127,16 +185,19 @@ def qk_prep(
     eps: float = 1e-6,
     fp8: bool = False,
     rope_half: bool = False,
+    no_norm: bool = False,
 ):
     """RMSNorm + rotation (+ e4m3 quantisation).  Returns ``(q', k', q_scale, k_scale)``; the prepared
-    tensors are logical ``[L, H, 128]`` views of head-major storage; scales are ``[H, ceil(L/128)]`` or None."""
+    tensors are logical ``[L, H, 128]`` views of head-major storage; scales are ``[H, ceil(L/128)]`` or None.
+    ``no_norm`` skips the RMSNorm: with no rotation table the call only re-lays rows out head-major, or (``fp8``)
+    quantises rows that are prepared already."""
     _require_cuda(q, k)
     lib = _lib.load()
     p = PrepParams()
     p.d = HEAD_DIM
     p.eps = float(eps)
     p.rope_mode = _lib.ROPE_HALF if rope_half else _lib.ROPE_INTERLEAVED
-    p.flags = _lib.PREP_FP8 if fp8 else 0
+    p.flags = (_lib.PREP_FP8 if fp8 else 0) | (_lib.PREP_NO_NORM if no_norm else 0)
     outs = {}
     keep = []
     H = None
@@ -187,8 +248,11 @@ def attn_fwd(
     wait_limit_ns: int = 0,
     workspace: Optional[torch.Tensor] = None,
     logit_bound: float = 0.0,
+    out_ranks: Optional["RankOutputs"] = None,
 ):
-    """Forward attention through ``h3a_attn_fwd``.  Returns ``out [Lq, H, 128]`` bf16 (and ``lse [H, Lq]``)."""
+    """Forward attention through ``h3a_attn_fwd``.  Returns ``out [Lq, H, 128]`` bf16 (and ``lse [H, Lq]``).
+    ``out_ranks`` (sequence parallelism): the rows are stored where their token lives, in the buffers it names,
+    instead of in ``out``; the call then returns None for the output."""
     _require_cuda(q, k, v)
     lib = _lib.load()
     fp8 = mode == _lib.MODE_FP8_QK
@@ -198,11 +262,23 @@ def attn_fwd(
     Lv, Hv, vsl, vsh = _lhd(v, "v", (torch.bfloat16,))
     if Hk != H or Hv != H or Lv != Lk:
         raise ValueError("q, k, v disagree on heads or key length")
-    if out is None:
-        out = torch.empty(Lq, H, HEAD_DIM, dtype=torch.bfloat16, device=q.device)
-    _, _, osl, osh = _lhd(out, "out", (torch.bfloat16,))
     p = AttnParams()
-    p.q, p.k, p.v, p.o = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    if out_ranks is not None:
+        if out is not None:
+            raise ValueError("out and out_ranks exclude each other")
+        if len(out_ranks.bases) * out_ranks.rows < Lq or not 1 <= len(out_ranks.bases) <= _lib.MAX_RANKS:
+            raise ValueError("out_ranks does not cover the query rows")
+        osl, osh = int(out_ranks.stride_l), int(out_ranks.stride_h)
+        p.o = out_ranks.bases[0]
+        for r, b in enumerate(out_ranks.bases):
+            p.o_rank_base[r] = b
+        p.o_n_ranks, p.o_rank_rows = len(out_ranks.bases), int(out_ranks.rows)
+    else:
+        if out is None:
+            out = torch.empty(Lq, H, HEAD_DIM, dtype=torch.bfloat16, device=q.device)
+        _, _, osl, osh = _lhd(out, "out", (torch.bfloat16,))
+        p.o = out.data_ptr()
+    p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     p.q_stride_l, p.q_stride_h = qsl, qsh
     p.k_stride_l, p.k_stride_h = ksl, ksh
     p.v_stride_l, p.v_stride_h = vsl, vsh
@@ -391,7 +467,8 @@ def static_scratch_capacity() -> int:
 
 
 def attn_fwd_sparse_static(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_index: BlockIndex,
-                           out: torch.Tensor, softmax_scale: float = 0.0, status_word: Optional[torch.Tensor] = None):
+                           out: torch.Tensor, softmax_scale: float = 0.0, status_word: Optional[torch.Tensor] = None,
+                           logit_bound: float = 0.0):
     """Block-sparse attention through ``h3a_attn_fwd_sparse_static``: for hosts that may not allocate device
     memory once they are running, so the tile-plan scratch is the 1 MiB array inside the library and ``out``
     must be supplied.  This wrapper itself creates no tensor.  Calls on one device share that scratch: do not
@@ -418,6 +495,8 @@ def attn_fwd_sparse_static(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bl
     p.mode = _lib.MODE_BLOCK_SPARSE
     p.softmax_scale = float(softmax_scale)
     p.row_ptr, p.col_idx, p.nnz = block_index.row_ptr.data_ptr(), block_index.col_idx.data_ptr(), block_index.nnz
+    p.sparse_heavy_pairs = block_index.heavy_pairs
+    p.logit_bound = float(logit_bound)
     if status_word is not None:
         p.status_word = status_word.data_ptr()
     check(lib.h3a_attn_fwd_sparse_static(C.byref(p), _stream()), "h3a_attn_fwd_sparse_static")
@@ -425,12 +504,48 @@ def attn_fwd_sparse_static(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bl
 
 
 def read_status(status_word: torch.Tensor) -> int:
-    """Synchronise the current stream and return the raw device status word (0 = no wait gave up)."""
+    """Synchronise the current stream and return the raw device status word (0 = no wait gave up and no block
+    index failed its check)."""
     raw = C.c_int32(0)
     rc = _lib.load().h3a_read_device_status(status_word.data_ptr(), _stream(), C.byref(raw))
-    if rc not in (_lib.H3A_OK, _lib.H3A_ERR_TIMEOUT):
+    if rc not in (_lib.H3A_OK, _lib.H3A_ERR_TIMEOUT, _lib.H3A_ERR_INDEX):
         check(rc, "h3a_read_device_status")
     return raw.value
+
+
+def check_status(status_word: torch.Tensor, where: str = "h3attn") -> None:
+    """Synchronise the current stream and raise :class:`H3AError` (``H3A_ERR_TIMEOUT`` / ``H3A_ERR_INDEX``) when a
+    kernel that was given this status word gave up a bounded wait or found a malformed block index.  The word stays
+    set (every later launch given it does nothing) until the caller zeroes it."""
+    raw = C.c_int32(0)
+    rc = _lib.load().h3a_read_device_status(status_word.data_ptr(), _stream(), C.byref(raw))
+    if rc != _lib.H3A_OK:
+        raise _lib.H3AError(rc, f"{where} (device status word 0x{raw.value & 0xFFFFFFFF:x})")
+
+
+class StatusWord:
+    """One persistent device ``int32`` shared by all the launches of an object (a processor, a sequence-parallel
+    wrapper, a host-buffer pipeline): zeroed once, handed to every kernel that has bounded waits, read with
+    :meth:`check` at a point where the caller synchronises anyway (once per forward or per sampler step)."""
+
+    def __init__(self, device=None):
+        self.device = device
+        self._t: Optional[torch.Tensor] = None
+
+    def tensor(self, like: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self._t is None:
+            dev = self.device if self.device is not None else (like.device if like is not None else torch.device("cuda", torch.cuda.current_device()))
+            self._t = torch.zeros(1, dtype=torch.int32, device=dev)
+        return self._t
+
+    def check(self, where: str = "h3attn") -> None:
+        if self._t is not None:
+            with torch.cuda.device(self._t.device):
+                check_status(self._t, where)
+
+    def reset(self) -> None:
+        if self._t is not None:
+            self._t.zero_()
 
 
 def normed_logit_bound(q_weight=None, k_weight=None, softmax_scale: float = 0.0, fp8: bool = False) -> float:

@@ -28,35 +28,79 @@ MODES = {"dense_bf16": _lib.MODE_DENSE_BF16, "fp8_qk": _lib.MODE_FP8_QK, "block_
 
 
 class RopeCache:
-    """Small LRU of (cos, sin) tables keyed by the storage and version of the position tensor, like the
-    reference's per-geometry layout cache (``src/pika_h3/core/wrapper.py:71-78``).  Each entry keeps its
-    position tensor alive, so a freed buffer whose address is reused can never alias a cached key."""
+    """(cos, sin) tables per position grid, like the reference's per-geometry layout cache
+    (``src/pika_h3/core/wrapper.py:71-78``).  The reference re-creates the device copy of its layout on every
+    forward (``layout.to(device)``, ``src/pika_h3/core/wrapper.py:164-166``), so a grid is recognised by its
+    CONTENT: the cache keeps its own device copy of each grid it has built a table for (``size`` of them, a
+    few hundred KB each) and compares a new tensor with them (one device-side comparison, i.e. one
+    synchronisation per forward).  All blocks of one forward pass the same tensor object; that is recognised
+    by identity first, through a weak reference, so the comparison runs once per forward and no caller tensor
+    is kept alive."""
 
-    def __init__(self, size: int = 8):
+    def __init__(self, size: int = 2):
         self.size = size
-        self._d: "OrderedDict[tuple, tuple]" = OrderedDict()
+        self._tables: "OrderedDict[int, tuple]" = OrderedDict()  # serial -> (own copy of the grid, split, theta, table)
+        self._seen: "OrderedDict[tuple, tuple]" = OrderedDict()   # identity of a caller tensor -> (weakref, serial)
+        self._serial = 0
+        self.hits = self.content_hits = self.misses = 0
+
+    def __len__(self) -> int:
+        return len(self._tables)
 
     def get(self, pos: torch.Tensor, split, theta) -> torch.Tensor:
-        key = (pos.data_ptr(), tuple(pos.shape), pos.dtype, pos._version, str(pos.device), tuple(split), float(theta))
-        hit = self._d.get(key)
-        if hit is None:
-            tab = ops.rope_table(pos.to(device=_cuda_device(pos)), split, theta)
-            if len(self._d) >= self.size:
-                self._d.popitem(last=False)
-            self._d[key] = (tab, pos)
-            return tab
-        self._d.move_to_end(key)
-        return hit[0]
+        split, theta = tuple(split), float(theta)
+        ident = (id(pos), pos.data_ptr(), pos._version, tuple(pos.shape), pos.dtype, str(pos.device), split, theta)
+        seen = self._seen.get(ident)
+        if seen is not None and seen[0]() is pos and seen[1] in self._tables:
+            self._tables.move_to_end(seen[1])
+            self.hits += 1
+            return self._tables[seen[1]][3]
+        dev = _cuda_device(pos)
+        p32 = pos.to(device=dev, dtype=torch.float32)
+        serial = None
+        for sn, (own, sp, th, _) in self._tables.items():
+            if sp == split and th == theta and own.shape == p32.shape and own.device == p32.device and torch.equal(own, p32):
+                serial = sn
+                self.content_hits += 1
+                break
+        if serial is None:
+            self.misses += 1
+            tab = ops.rope_table(p32, split, theta)
+            if len(self._tables) >= self.size:
+                self._tables.popitem(last=False)
+            self._serial += 1
+            serial = self._serial
+            own = p32 if p32.data_ptr() != pos.data_ptr() else p32.clone()
+            self._tables[serial] = (own, split, theta, tab)
+        self._tables.move_to_end(serial)
+        import weakref
+
+        while len(self._seen) >= 8:
+            self._seen.popitem(last=False)
+        self._seen[ident] = (weakref.ref(pos), serial)
+        return self._tables[serial][3]
 
 
 def _cuda_device(t: torch.Tensor):
     return t.device if t.is_cuda else torch.device("cuda", torch.cuda.current_device())
 
 
-def _norm_params(mod):
+def _norm_params(mod, name: str = "norm"):
+    """``(weight, eps)`` of a per-head RMSNorm module, or ``(None, None)`` for no module.  The library normalises
+    each head's 128 values by their own root mean square and multiplies by ONE weight vector of 128 entries shared
+    by all heads; anything that computes something else (a norm across all heads with a ``[heads * 128]`` weight, a
+    LayerNorm with a bias or with mean subtraction) is refused here instead of being silently replaced."""
     if mod is None:
         return None, None
+    if isinstance(mod, torch.nn.LayerNorm):
+        raise NotImplementedError(f"{name} is a LayerNorm (mean subtraction); the library's Q/K preparation is a per-head RMSNorm")
+    if getattr(mod, "bias", None) is not None:
+        raise NotImplementedError(f"{name} has a bias; the library's Q/K preparation is a bias-free per-head RMSNorm")
     w = getattr(mod, "weight", None)
+    if w is not None and w.numel() != ops.HEAD_DIM:
+        raise NotImplementedError(
+            f"{name}.weight has {w.numel()} entries: only a per-head RMSNorm over the 128 head dims (one [128] weight shared "
+            "by all heads) is implemented, not a norm across heads")
     eps = getattr(mod, "eps", None)
     if eps is None:
         eps = getattr(mod, "variance_epsilon", None)
@@ -104,7 +148,14 @@ class B200AttnProcessor:
     mode          ``dense_bf16`` | ``fp8_qk`` | ``block_sparse``
     block_index   ``ops.BlockIndex`` on the device (``block_sparse`` only; self-attention only)
     rope_half     rotary pairs ``(j, j+64)`` instead of ``(2j, 2j+1)``
-    qk_norm       apply per-head RMSNorm even when the module has no ``norm_q`` / ``norm_k`` (unit weights)
+    qk_norm       what to do with a module that has NO ``norm_q`` / ``norm_k``: ``True`` applies the per-head RMSNorm
+                  with unit weights all the same (BASELINE's configs), ``None`` (default) refuses such a module, so
+                  that a norm-free model is never normalised by accident.  Modules WITH ``norm_q`` / ``norm_k`` must
+                  carry a per-head RMSNorm (one ``[128]`` weight, no bias); anything else raises.
+    status        ``ops.StatusWord`` shared by every launch of this processor (default: its own).  A kernel whose
+                  bounded wait runs out, or that finds a malformed block index, records it there and every later
+                  launch does nothing; :meth:`check_status` (one synchronisation: call it once per forward or per
+                  sampler step) raises ``H3AError`` then.  ``check_every_call=True`` does that after each call.
     group         a ``torch.distributed`` process group (NCCL, one process per GPU): Ulysses sequence parallelism.
                   ``hidden_states`` is then this rank's shard ``[1, S/P, D]`` of the packed sequence (rank r holds
                   tokens ``[r*S/P, (r+1)*S/P)``; rotary inputs are the rows of the same shard) and so is the result.
@@ -117,8 +168,9 @@ class B200AttnProcessor:
     """
 
     def __init__(self, mode: str = "dense_bf16", block_index: Optional[ops.BlockIndex] = None, rope_half: bool = False,
-                 rope_split=ops.ROPE_SPLIT, rope_theta: float = 10000.0, qk_norm: bool = True, eps: float = 1e-6,
-                 group=None, sequence_parallel: bool = False, fused_projection: bool = False):
+                 rope_split=ops.ROPE_SPLIT, rope_theta: float = 10000.0, qk_norm: Optional[bool] = None, eps: float = 1e-6,
+                 group=None, sequence_parallel: bool = False, fused_projection: bool = False,
+                 status: Optional[ops.StatusWord] = None, check_every_call: bool = False):
         if mode not in MODES:
             raise ValueError(f"mode must be one of {sorted(MODES)}")
         if mode == "block_sparse" and block_index is None:
@@ -135,11 +187,24 @@ class B200AttnProcessor:
         self._bounds = {}
         self.fused_projection = fused_projection
         self._scaled_b = {}
+        self.status = status if status is not None else ops.StatusWord()
+        self.check_every_call = check_every_call
         self._ulysses = None
         if group is not None or sequence_parallel:  # sequence_parallel=True with group=None: the default group
             from .ulysses import UlyssesAttention
 
-            self._ulysses = UlyssesAttention(group, MODES[mode], block_index)
+            self._ulysses = UlyssesAttention(group, MODES[mode], block_index, status=self.status)
+
+    def close(self) -> None:
+        """Release what the sequence-parallel mode shares with the other ranks (call on every rank before the process
+        group is destroyed); nothing to do on one GPU."""
+        if self._ulysses is not None:
+            self._ulysses.close()
+
+    def check_status(self) -> None:
+        """Synchronise and raise ``H3AError`` if any launch of this processor gave up a bounded wait (``H3A_ERR_TIMEOUT``)
+        or found a malformed block index (``H3A_ERR_INDEX``) since the status word was last zeroed."""
+        self.status.check("B200AttnProcessor")
 
     # ---- rotary information from whatever the caller passes
     def _rope(self, S: int, image_rotary_emb, kwargs) -> Optional[torch.Tensor]:
@@ -173,10 +238,15 @@ class B200AttnProcessor:
         return (q.to(**to).view(-1, H, ops.HEAD_DIM), k.to(**to).view(-1, H, ops.HEAD_DIM), v.to(**to).view(-1, H, ops.HEAD_DIM))
 
     def _norm_and_bound(self, attn, mode):
-        qw, qeps = _norm_params(getattr(attn, "norm_q", None))
-        kw, keps = _norm_params(getattr(attn, "norm_k", None))
-        if not self.qk_norm and qw is None and kw is None:
-            raise NotImplementedError("the fused Q/K preparation always normalises; qk_norm=False needs norm-free modules")
+        nq, nk = getattr(attn, "norm_q", None), getattr(attn, "norm_k", None)
+        if (nq is None) != (nk is None):
+            raise NotImplementedError("norm_q and norm_k must both be present or both be absent")
+        if nq is None and self.qk_norm is not True:
+            raise NotImplementedError(
+                "the attention module has no norm_q / norm_k and the library's Q/K preparation always normalises: pass "
+                "qk_norm=True to apply the unit-weight per-head RMSNorm on purpose")
+        qw, qeps = _norm_params(nq, "norm_q")
+        kw, keps = _norm_params(nk, "norm_k")
         eps = qeps or keps or self.eps
         # the logit bound depends only on the (static) norm weights: read them once per module
         key = (id(attn), mode == _lib.MODE_FP8_QK)
@@ -192,7 +262,8 @@ class B200AttnProcessor:
         if cross and mode == _lib.MODE_BLOCK_SPARSE:
             mode, bi = _lib.MODE_DENSE_BF16, None  # the block index describes the joint self-attention only
         qw, kw, eps, bound = self._norm_and_bound(attn, mode)
-        return ops.joint_attention(q, k, v, None if cross else rope, mode, bi, qw, kw, eps, self.rope_half, logit_bound=bound)
+        return ops.joint_attention(q, k, v, None if cross else rope, mode, bi, qw, kw, eps, self.rope_half, logit_bound=bound,
+                                   status_word=self.status.tensor(q))
 
     # ---- fused projections
     def _fusable(self, attn, x, ctx):
@@ -216,7 +287,8 @@ class B200AttnProcessor:
             bs = self._scaled_b.get(key)
             if bs is None:  # (alpha / rank) * B, static at inference: scaled once per module
                 bs = self._scaled_b[key] = (b.float() * scale).to(torch.bfloat16).contiguous()
-        return ops.proj_fwd(x2d, w, bias, t, bs, prep=prep, rope=rope, norm_weight=norm_w, eps=eps, rope_half=self.rope_half, fp8=fp8)
+        return ops.proj_fwd(x2d, w, bias, t, bs, prep=prep, rope=rope, norm_weight=norm_w, eps=eps, rope_half=self.rope_half, fp8=fp8,
+                            status_word=self.status.tensor(x2d))
 
     def attention_fused(self, attn, parts, hidden_states, ctx, rope, cross: bool):
         """Projections with the preparation in their epilogue, then attention (one GPU)."""
@@ -231,7 +303,7 @@ class B200AttnProcessor:
         k = self._fused(attn.to_k, parts[1], c2d, True, None if cross else rope, kw, eps, fp8)
         v = self._fused(attn.to_v, parts[2], c2d, False, None, None, eps)
         (q, qs), (k, ks) = (q, k) if fp8 else ((q, None), (k, None))
-        return ops.attn_fwd(q, k, v, mode, qs, ks, bi, logit_bound=bound)
+        return ops.attn_fwd(q, k, v, mode, qs, ks, bi, logit_bound=bound, status_word=self.status.tensor(v))
 
     def attention_sequence_parallel(self, attn, hidden_states, rope):
         """Self-attention with the sequence sharded over the group: each projection is computed when the previous
@@ -293,9 +365,11 @@ class B200AttnProcessor:
                 bs = self._scaled_b.get(key)
                 if bs is None:
                     bs = self._scaled_b[key] = (b.float() * scale).to(torch.bfloat16).contiguous()
-            o = ops.proj_fwd(o[0].contiguous(), w, bias, t, bs, token_major=True)[None]
+            o = ops.proj_fwd(o[0].contiguous(), w, bias, t, bs, token_major=True, status_word=self.status.tensor(o))[None]
         else:
             o = to_out[0](o)
         if len(to_out) > 1:
             o = to_out[1](o)
+        if self.check_every_call:
+            self.check_status()
         return o

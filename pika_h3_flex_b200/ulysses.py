@@ -9,7 +9,13 @@ carries final operands in head-major layout ``[H, L/P, 128]``: the block that go
 ``H/P`` heads) is contiguous, and each received ``[L/P, 128]`` block lands directly at its final place in
 ``[H/P, L, 128]``, so neither side needs a pack or unpack pass.
 
-Two transports, same results.  On NCCL each exchange is ONE list-form ``all_to_all`` per tensor (grouped
+Transports, same results.  ``peer`` (the default on NCCL groups of more than one GPU): no exchange step at all. The
+preparation kernels store each prepared row straight into the memory of the rank that owns the row's head
+(``h3a_qk_prep_scatter``, plain stores over NVLink into buffers opened through CUDA's inter-process handles, see
+``peer.py``), the attention kernel stores each output row straight into the memory of the rank that owns the row's
+token (``h3a_attn_params.o_rank_base``), and the ranks meet twice per call (before the owners read, after the
+outputs have landed).  Peer memory is a store target only; every load and every tensor map covers local memory.
+``nccl``: on NCCL each exchange is ONE list-form ``all_to_all`` per tensor (grouped
 ncclSend/ncclRecv inside the library): the block for a peer is contiguous on the sending side, arrives as one
 contiguous ``[heads, L/P, 128]`` block per peer, and a single strided copy puts the blocks at their final place
 (the return trip packs instead).  That costs one extra pass over the exchanged tensor (well under 2 % of the
@@ -172,18 +178,159 @@ class UlyssesAttention:
     ``attn_fn(q, k, v, mode, q_scale, k_scale, block_index)`` default to the CUDA library; the CPU tests
     inject host stand-ins to exercise the reshard logic with gloo ranks.  ``head_groups``: 1 = one attention
     launch, 2 = up to two groups chosen by the wave model (default), or an explicit list of group sizes.
+
+    Every rank must bring the same shard shape.  That is checked on the host, once per shape, by one small
+    ``all_gather_object`` on the group before the first exchange of that shape: a mismatch raises ``ValueError`` on
+    every rank instead of leaving the ranks blocked in an exchange whose sizes disagree.  Exchanges themselves have
+    no deadline of their own: create the process group with a finite ``timeout`` (``init_process_group(...,
+    timeout=...)``) so that a rank that never arrives ends the collective with an error.  ``status`` is the
+    ``ops.StatusWord`` handed to the attention launches (bounded device-side waits); ``check_status()`` reads it.
     """
 
     def __init__(self, group=None, mode: int = _lib.MODE_DENSE_BF16, block_index: Optional[ops.BlockIndex] = None,
                  prep_fn: Optional[Callable] = None, attn_fn: Optional[Callable] = None,
-                 to_head_major: Optional[Callable] = None, head_groups: int = 2):
+                 to_head_major: Optional[Callable] = None, head_groups: int = 2, status: Optional[ops.StatusWord] = None,
+                 transport: str = "auto"):
+        if transport not in ("auto", "peer", "nccl"):
+            raise ValueError("transport must be auto, peer or nccl")
+        self._transport_arg = transport
+        self.transport = None  # resolved at the first call: "peer" or "nccl" (which also names the gloo path of the CPU tests)
+        self._peer = {}
         self.group = group
+        self.status = status if status is not None else ops.StatusWord()
+        self._validated = set()
+        # set to a list to have every call append {"prep": [(start, end) CUDA events ...], "attention": [...]}:
+        # the token-local preparation passes and the attention launches of that call on this rank's stream
+        self.timeline = None
         self.head_groups = head_groups
         self.mode = mode
         self.block_index = block_index
         self.prep_fn = prep_fn
         self.attn_fn = attn_fn
         self.to_head_major = to_head_major or (lambda v: v.permute(1, 0, 2).contiguous())
+
+    def check_status(self) -> None:
+        self.status.check("UlyssesAttention")
+
+    def close(self) -> None:
+        """Release the buffers shared with the other ranks (every rank must call it; needed before the process group
+        is destroyed when the peer transport was used)."""
+        for st in self._peer.values():
+            st.arena.close()
+        self._peer = {}
+
+    def _resolve_transport(self, like: torch.Tensor) -> str:
+        if self.transport is None:
+            t = self._transport_arg
+            if t == "auto":
+                own = self.prep_fn is None and self.attn_fn is None
+                t = "peer" if (own and like.is_cuda and dist.get_backend(self.group) == "nccl" and dist.get_world_size(self.group) > 1) else "nccl"
+            if t == "peer" and (self.prep_fn is not None or self.attn_fn is not None or not like.is_cuda):
+                raise ValueError("the peer transport runs the library's own kernels on CUDA tensors")
+            self.transport = t
+        return self.transport
+
+    def launches_per_step(self, Ls: int, H: int) -> int:
+        """Kernels of this library one call launches on this rank (for the benchmark's launch count)."""
+        fp8 = self.mode == _lib.MODE_FP8_QK
+        n = 3 + 1  # Q, K (and, on the peer transport, V) preparation / re-layout + attention
+        if self.transport != "peer":
+            n -= 1  # V's head-major copy is a torch kernel there
+        if self.block_index is not None:
+            n += 1
+        if fp8 and self.transport == "peer":
+            n += 2
+        return n
+
+    class _PeerState:
+        pass
+
+    def _peer_state(self, Ls: int, H: int, device) -> "_PeerState":
+        """Buffers of one shard shape, shared with the other ranks: this rank's heads of Q, K, V over ALL tokens
+        (written by every rank's preparation kernels) and this rank's tokens of the output for all heads (written by
+        every rank's attention kernel)."""
+        from .peer import Carver, PeerArena
+
+        key = (Ls, H)
+        st = self._peer.get(key)
+        if st is None:
+            world = dist.get_world_size(self.group)
+            rank = dist.get_rank(self.group)
+            st = self._PeerState()
+            st.hp = padded_heads(H, world) // world
+            st.L = world * Ls
+            st.n_local = max(0, min(st.hp, H - rank * st.hp))
+            c = Carver()
+            nb = st.hp * st.L * ops.HEAD_DIM * 2
+            st.off = {n: c.take(nb) for n in ("q", "k", "v")}
+            st.off["o"] = c.take(Ls * H * ops.HEAD_DIM * 2)
+            st.arena = PeerArena(c.size, self.group, device)
+            for n in ("q", "k", "v"):
+                setattr(st, n, st.arena.tensor(st.off[n], (st.hp, st.L, ops.HEAD_DIM), torch.bfloat16))
+            st.o = st.arena.tensor(st.off["o"], (Ls, H, ops.HEAD_DIM), torch.bfloat16)
+            st.owners = {n: ops.HeadOwners([st.arena.addr(p, st.off[n]) for p in range(world)], st.hp, False, rank * Ls, st.L)
+                         for n in ("q", "k", "v")}
+            # output rows of this rank's heads (global heads rank * hp ...) go to the rank that holds the token
+            st.out_ranks = ops.RankOutputs([st.arena.addr(t, st.off["o"]) + rank * st.hp * ops.HEAD_DIM * 2 for t in range(world)],
+                                           Ls, H * ops.HEAD_DIM, ops.HEAD_DIM)
+            self._peer[key] = st
+        return st
+
+    def _run_peer(self, q, k_fn, v_fn, rope, q_weight, k_weight, eps, rope_half, logit_bound, prepared, marks):
+        """One call on the peer transport (see the module docstring).  The result is a view of this rank's output
+        buffer, which the next call of the same shape overwrites."""
+        fp8 = self.mode == _lib.MODE_FP8_QK
+        Ls, H, _ = q.shape
+        st = self._peer_state(Ls, H, q.device)
+
+        def timed(kind, fn):
+            if marks is None:
+                return fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn()
+            e1.record()
+            marks[kind].append((e0, e1))
+            return r
+
+        for name, x in (("q", q), ("k", None), ("v", None)):
+            if x is None:
+                x = (k_fn if name == "k" else v_fn)()
+                if tuple(x.shape) != (Ls, H, ops.HEAD_DIM):
+                    raise ValueError("q, k, v must be [L/P, H, 128] shards of the same shape")
+            if name == "v" or prepared:
+                timed("prep", lambda: ops.prep_scatter(x, st.owners[name], no_norm=True))
+            else:
+                w = q_weight if name == "q" else k_weight
+                timed("prep", lambda: ops.prep_scatter(x, st.owners[name], rope, w, eps, rope_half))
+        st.arena.barrier()  # every rank's rows have landed before an owner reads
+        if st.n_local > 0:
+            n = st.n_local
+            qg, kg, vg = (getattr(st, name)[:n].permute(1, 0, 2) for name in ("q", "k", "v"))
+            qs = ks = None
+            if fp8:  # block scales need whole 128-token blocks of the FULL sequence: quantise here, at the owner
+                qg, kg, qs, ks = timed("prep", lambda: ops.qk_prep(qg, kg, fp8=True, no_norm=True))
+            timed("attention", lambda: ops.attn_fwd(qg, kg, vg, self.mode, qs, ks, self.block_index, out_ranks=st.out_ranks,
+                                                    logit_bound=logit_bound, status_word=self.status.tensor(q)))
+        st.arena.barrier()  # every rank's output rows have landed
+        return st.o
+
+    def _validate(self, Ls: int, H: int) -> None:
+        """All ranks must hold shards of one shape, and the block index must describe the whole sequence."""
+        world = dist.get_world_size(self.group)
+        if self.block_index is not None:
+            nt = (world * Ls + ops.TILE - 1) // ops.TILE
+            if self.block_index.n_q_tiles != nt or self.block_index.n_k_tiles != nt:
+                raise ValueError(f"block index is {self.block_index.n_q_tiles} x {self.block_index.n_k_tiles} tiles, "
+                                 f"the sequence of {world} x {Ls} tokens has {nt}")
+        key = (Ls, H)
+        if key in self._validated:
+            return
+        shapes = [None] * world
+        dist.all_gather_object(shapes, key, group=self.group)
+        if any(tuple(x) != key for x in shapes):
+            raise ValueError(f"ranks disagree on the shard shape (tokens per rank, heads): {shapes}")
+        self._validated.add(key)
 
     @staticmethod
     def _waves(n_heads: int, L: int, sms: int) -> float:
@@ -239,6 +386,17 @@ class UlyssesAttention:
         callables return ``(e4m3 bytes, block scales)``."""
         world = dist.get_world_size(self.group)
         fp8 = self.mode == _lib.MODE_FP8_QK
+        marks = {"prep": [], "attention": []} if self.timeline is not None else None
+
+        def timed(kind, fn):
+            if marks is None:
+                return fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn()
+            e1.record()
+            marks[kind].append((e0, e1))
+            return r
 
         def prep(x, which):  # token-local work first: the wire then carries final operands
             if prepared:  # FP8-QK: the callable returned (e4m3 bytes, block scales)
@@ -256,6 +414,15 @@ class UlyssesAttention:
 
         q = q_fn()
         Ls, H, _ = (q[0] if isinstance(q, tuple) else q).shape
+        self._validate(Ls, H)
+        transport = self._resolve_transport(q[0] if isinstance(q, tuple) else q)
+        if transport == "peer" and not (prepared and fp8):  # prepared e4m3 operands carry per-shard scales: exchanged below
+            if logit_bound is None:
+                logit_bound = ops.normed_logit_bound(q_weight, k_weight, 0.0, fp8)
+            out = self._run_peer(q, k_fn, v_fn, rope, q_weight, k_weight, eps, rope_half, logit_bound, prepared, marks)
+            if marks is not None:
+                self.timeline.append(marks)
+            return out
         if fp8 and Ls % ops.TILE:
             raise ValueError("FP8 mode under Ulysses needs the local sequence length to be a multiple of 128")
         Hp = padded_heads(H, world)
@@ -271,11 +438,11 @@ class UlyssesAttention:
             if tuple((x[0] if isinstance(x, tuple) else x).shape) != (Ls, H, ops.HEAD_DIM):
                 raise ValueError("q, k, v must be [L/P, H, 128] shards of the same shape")
             if which < 2:
-                xp, xs = prep(x, which)
+                xp, xs = timed("prep", lambda: prep(x, which))
                 x_hm = _pad_heads_hm(xp.permute(1, 0, 2).contiguous(), Hp)  # prepared tensors are views of head-major storage
             else:
                 xs = None
-                x_hm = _pad_heads_hm(self.to_head_major(x), Hp)
+                x_hm = _pad_heads_hm(timed("prep", lambda: self.to_head_major(x)), Hp)
             for gi, sl in enumerate(groups):
                 heads[which], r = seq_to_head(x_hm, self.group, True, heads[which], sl)
                 inbound[gi] += r
@@ -302,9 +469,12 @@ class UlyssesAttention:
             else:
                 # head-major output so that the return exchange sends contiguous blocks without a copy
                 oh = torch.empty(j1 - j0, qg.shape[0], ops.HEAD_DIM, dtype=torch.bfloat16, device=qg.device).permute(1, 0, 2)
-                ops.attn_fwd(qg, kg, vg, self.mode, sq, sk, self.block_index, out=oh, logit_bound=logit_bound)
+                timed("attention", lambda: ops.attn_fwd(qg, kg, vg, self.mode, sq, sk, self.block_index, out=oh, logit_bound=logit_bound,
+                                                        status_word=self.status.tensor(qg)))
             o_hm, r = head_to_seq(oh.permute(1, 0, 2).contiguous(), self.group, True, o_hm, sl, hp)
             outbound += r
         for r in outbound:
             r.wait()
+        if marks is not None:
+            self.timeline.append(marks)
         return o_hm[:H].permute(1, 0, 2)

@@ -27,9 +27,9 @@ def test_header_and_library_agree(lib):
 
 
 def test_version_and_status_strings(lib):
-    assert _lib.version() == (0, 1)
+    assert _lib.version() == (0, 2)
     seen = set()
-    for code in range(0, -9, -1):
+    for code in range(0, -11, -1):
         s = _lib.status_string(code)
         assert s and s != "unknown status" and s not in seen
         seen.add(s)
@@ -38,7 +38,8 @@ def test_version_and_status_strings(lib):
 
 def test_struct_sizes_match_header(lib):
     # natural-alignment sizes of the two parameter structs as a C compiler lays them out
-    assert C.sizeof(_lib.AttnParams) == 216
+    assert C.sizeof(_lib.AttnParams) == 216 + 8 * 8 + 8  # + the per-rank output bases of the sequence-parallel return trip
+    assert C.sizeof(_lib.HeadScatter) == 8 * 8 + 6 * 4
     assert C.sizeof(_lib.PrepParams) == 144
     assert C.sizeof(_lib.ProjParams) == 168
     assert C.sizeof(_lib.AdaLnParams) == 112
@@ -54,13 +55,13 @@ def test_struct_sizes_match_a_c_compiler(tmp_path):
         pytest.skip("no gcc")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     src = tmp_path / "sz.c"
-    src.write_text('#include <stdio.h>\n#include "h3attn.h"\nint main(void) { printf("%zu %zu %zu %zu\\n", sizeof(h3a_attn_params), '
-                   'sizeof(h3a_prep_params), sizeof(h3a_proj_params), sizeof(h3a_adaln_params)); return 0; }\n')
+    src.write_text('#include <stdio.h>\n#include "h3attn.h"\nint main(void) { printf("%zu %zu %zu %zu %zu\\n", sizeof(h3a_attn_params), '
+                   'sizeof(h3a_prep_params), sizeof(h3a_proj_params), sizeof(h3a_adaln_params), sizeof(h3a_head_scatter)); return 0; }\n')
     exe = tmp_path / "sz"
     subprocess.run(["gcc", "-I", os.path.join(root, "include"), "-o", str(exe), str(src)], check=True)
     out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
     assert [int(v) for v in out] == [C.sizeof(_lib.AttnParams), C.sizeof(_lib.PrepParams), C.sizeof(_lib.ProjParams),
-                                     C.sizeof(_lib.AdaLnParams)]
+                                     C.sizeof(_lib.AdaLnParams), C.sizeof(_lib.HeadScatter)]
 
 
 def test_proj_argument_validation_without_a_device(lib):

@@ -288,6 +288,105 @@ def test_config1_full_length_properties(h, bounded):
     assert float((o3.float() - 2 * out.float()).abs().max()) <= 8e-3
 
 
+def test_config2_full_length_fp8(h):
+    """Config 2 at its own shape: FP8-QK at the 480p-like length (49,384 tokens: 386 key tiles, tail tile of 104,
+    block scales [H, 386]), 8 of the 40 heads, through joint_attention on CTA pairs with the split last wave.
+    Sampled rows against (a) the fp64 oracle on the SAME e4m3-quantised operands, bf16 bounds, and (b) the fp32
+    dense result of config 1, the looser FP8 bounds; V = 1 must give O = 1."""
+    from pika_h3_flex_b200.ops import normed_logit_bound, split_workspace_bytes
+
+    H = 8
+    grid, n_audio, L, q, k, v = _full_inputs("cfg1", H)  # config 2 = the inputs of config 1
+    assert L == 49384
+    pos = O.make_positions(grid, n_audio)
+    tab = h.rope_table(dev(pos))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    bound = normed_logit_bound(fp8=True)
+    assert split_workspace_bytes(L, L, H, h.MODE_FP8_QK, bound) > 0  # this launch splits its last wave
+    out = h.joint_attention(q, k, v, tab, h.MODE_FP8_QK, status_word=status)
+    assert h.read_status(status) == 0
+    rows = torch.cat([torch.arange(0, L, 997), torch.tensor([L - 1, L - 104, L - 105, 1023, 1024])])
+    hs = [0, H - 1]
+    qo, ko = O.qk_prep(q[:, hs].cpu().double(), k[:, hs].cpu().double(), *O.rope_table(pos))
+    # (a) same quantised operands: quantise the full prepared tensors (block scales need whole 128-token blocks)
+    qq, sq = O.quantize_e4m3_blocks(qo.float())
+    kq, sk = O.quantize_e4m3_blocks(ko.float())
+    ref_q = O.attention(O.dequantize_blocks(qq, sq).double(), O.dequantize_blocks(kq, sk).double(), v[:, hs].cpu().double(), q_rows=rows)
+    check(out[rows][:, hs], ref_q.float())
+    # (b) the fp32 / fp64 dense result on unquantised operands
+    ref_d = O.attention(qo, ko, v[:, hs].cpu().double(), q_rows=rows)
+    check(out[rows][:, hs], ref_d.float(), FP8_MAX, FP8_MEAN, FP8_REL)
+    # the library's own quantisation equals the oracle's on these operands (scales to fp32 rounding)
+    qp, kp, qs, ks = h.qk_prep(q[:, hs].contiguous(), k[:, hs].contiguous(), tab, tab, fp8=True)
+    assert tuple(qs.shape) == (2, 386) and tuple(ks.shape) == (2, 386)
+    np.testing.assert_allclose(ks.cpu().numpy(), sk.numpy(), rtol=2e-2)
+    o1 = h.joint_attention(q, k, torch.ones_like(v), tab, h.MODE_FP8_QK)
+    assert float((o1.float() - 1).abs().max()) <= 8e-3
+
+
+def test_config1_all_forty_heads(h):
+    """Config 1 with all 40 heads, once: the real schedule (3,880 CTA pairs = 52.4 waves of 74, head-major order,
+    split last wave at the real pair count).  Sampled rows of the first, a middle and the last head (the last head's
+    query tiles are the ones the split wave covers) against the fp64 oracle; V = 1 gives O = 1 for every head."""
+    H = 40
+    grid, n_audio, L, q, k, v = _full_inputs("cfg1", H)
+    pos = O.make_positions(grid, n_audio)
+    tab = h.rope_table(dev(pos))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = h.joint_attention(q, k, v, tab, status_word=status)
+    assert h.read_status(status) == 0
+    rows = torch.cat([torch.arange(0, L, 1999), torch.tensor([L - 1, L - 104, L - 105, L - 513, 1023, 1024])])
+    hs = [0, 17, H - 1]
+    qo, ko = O.qk_prep(q[:, hs].cpu().double(), k[:, hs].cpu().double(), *O.rope_table(pos))
+    ref = O.attention(qo, ko, v[:, hs].cpu().double(), q_rows=rows)
+    check(out[rows][:, hs], ref.float())
+    o1 = h.joint_attention(q, k, torch.ones_like(v), tab)
+    assert float((o1.float() - 1).abs().max()) <= 8e-3
+
+
+@pytest.mark.parametrize("L,bound", [(1024, 0.0), (1024, 12.0), (2304, 12.0)])
+def test_malformed_block_index_is_reported_and_never_overruns(h, L, bound):
+    """The plan kernels check the caller's index: an out-of-range column, a descending list, row pointers beyond
+    nnz.  Nothing is written outside the workspace (canary words after it stay intact), the status word receives the
+    index code (H3A_ERR_INDEX) and the attention launch does nothing."""
+    from pika_h3_flex_b200 import _lib
+
+    H = 1
+    q, k, v = (dev(x) for x in bf16_inputs(L, H, 81))
+    nb = L // 128
+    good_rp = np.arange(nb + 1, dtype=np.int32) * nb
+    good_ci = np.tile(np.arange(nb, dtype=np.int32), nb)
+    cases = []
+    ci = good_ci.copy(); ci[5] = nb + 7           # column beyond the key tiles
+    cases.append((good_rp, ci))
+    ci = good_ci.copy(); ci[[2, 3]] = ci[[3, 2]]   # not ascending
+    cases.append((good_rp, ci))
+    rp = good_rp.copy(); rp[-1] = nb * nb + 4096   # row pointer beyond nnz
+    cases.append((rp, good_ci))
+    rp = good_rp.copy(); rp[3] = rp[2] - 1         # decreasing row pointers
+    cases.append((rp, good_ci))
+    for rp, ci in cases:
+        bi = h.BlockIndex(torch.from_numpy(rp).cuda(), torch.from_numpy(ci).cuda(), int(ci.size), nb, nb)
+        need = (int(ci.size) + (L + 255) // 256) * 4
+        ws = torch.full((need + 4096,), 0x5A, dtype=torch.uint8, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        out = torch.full((L, H, 128), 7.0, dtype=torch.bfloat16, device="cuda")
+        h.attn_fwd(q, k, v, h.MODE_BLOCK_SPARSE, block_index=bi, out=out, status_word=status, workspace=ws[:need], logit_bound=bound)
+        raw = h.read_status(status)
+        assert raw & 0xFF == 10, hex(raw)
+        assert h._lib.load().h3a_read_device_status(status.data_ptr(), torch.cuda.current_stream().cuda_stream, None) == _lib.H3A_ERR_INDEX
+        with pytest.raises(h.H3AError):
+            h.check_status(status)
+        assert bool((ws[need:] == 0x5A).all())       # nothing written past the workspace
+        assert bool((out == 7.0).all())              # the attention launch did nothing
+    # the well-formed index still runs and the status word stays clear
+    bi = h.BlockIndex(torch.from_numpy(good_rp).cuda(), torch.from_numpy(good_ci).cuda(), int(good_ci.size), nb, nb)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = h.attn_fwd(q, k, v, h.MODE_BLOCK_SPARSE, block_index=bi, status_word=status, logit_bound=bound)
+    assert h.read_status(status) == 0
+    check(out, O.attention(q.float().cpu(), k.float().cpu(), v.float().cpu()))
+
+
 @pytest.mark.parametrize("window,bounded", [((2, 8, 8), False), ((2, 8, 8), True), ((3, 48, 84), True)])
 def test_config3_full_length_block_sparse_properties(h, window, bounded):
     """768p-like length (126,016 tokens), 2 heads: the literal neighbourhood rule (7.2 % of tiles) with the running

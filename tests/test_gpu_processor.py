@@ -80,10 +80,21 @@ def test_self_attention_with_position_ids(setup):
     ref = oracle_forward(attn, x, None, pos)
     assert y.shape == x.shape and y.dtype == x.dtype
     assert float((y.float() - ref.float()).abs().max()) < 3e-2
-    # the table is cached per position tensor
-    assert len(proc._rope_cache._d) == 1
-    proc(attn, x, position_ids=pos.cuda())
-    assert len(proc._rope_cache._d) == 2  # a new tensor object is a new key
+    # the table is cached per position GRID: the reference makes a new device copy of its layout every forward
+    # (src/pika_h3/core/wrapper.py:164-166), so an equal-valued but distinct tensor must hit
+    c = proc._rope_cache
+    assert len(c) == 1 and c.misses == 1
+    p2 = pos.cuda()
+    proc(attn, x, position_ids=p2)
+    assert len(c) == 1 and c.misses == 1 and c.content_hits == 1
+    proc(attn, x, position_ids=p2)  # the same tensor object again (the next block of the same forward): identity hit
+    assert c.hits == 1 and c.content_hits == 1
+    del p2
+    other = pos.cuda() + 1.0
+    proc(attn, x, position_ids=other)
+    assert len(c) == 2 and c.misses == 2
+    proc(attn, x, position_ids=(pos.cuda() + 2.0))
+    assert len(c) == 2  # two grids are kept
 
 
 @torch.no_grad()
@@ -131,6 +142,66 @@ def test_processor_rejects_what_it_cannot_do(setup):
         proc(attn, x.cpu(), position_ids=pos)
     with pytest.raises(ValueError):
         B200AttnProcessor("block_sparse")
+
+
+@torch.no_grad()
+def test_processor_refuses_norms_it_does_not_implement(setup):
+    """The library's preparation is a per-head RMSNorm with one [128] weight.  A norm across heads ([heads * 128]
+    weight), a LayerNorm, a norm with a bias, or a module without norm_q / norm_k (unless qk_norm=True asks for the
+    unit-weight norm) must raise instead of silently computing something else."""
+    import copy
+
+    from pika_h3_flex_b200.processor import B200AttnProcessor
+
+    attn, x, pos, _, _ = setup
+    proc = B200AttnProcessor()
+    wide = copy.deepcopy(attn)
+    wide.norm_q.weight = nn.Parameter(torch.ones(attn.heads * 128, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(NotImplementedError, match="across heads"):
+        proc(wide, x, position_ids=pos.cuda())
+    ln = copy.deepcopy(attn)
+    ln.norm_k = nn.LayerNorm(128).cuda().bfloat16()
+    with pytest.raises(NotImplementedError, match="LayerNorm"):
+        proc(ln, x, position_ids=pos.cuda())
+    biased = copy.deepcopy(attn)
+    biased.norm_q.bias = nn.Parameter(torch.zeros(128, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(NotImplementedError, match="bias"):
+        proc(biased, x, position_ids=pos.cuda())
+    bare = copy.deepcopy(attn)
+    bare.norm_q = bare.norm_k = None
+    with pytest.raises(NotImplementedError, match="qk_norm=True"):
+        proc(bare, x, position_ids=pos.cuda())
+    y = B200AttnProcessor(qk_norm=True)(bare, x, position_ids=pos.cuda())  # on purpose: unit-weight per-head RMSNorm
+    H = attn.heads
+    q, k, v = (m(x).view(-1, H, 128).float().cpu() for m in (bare.to_q, bare.to_k, bare.to_v))
+    ref = bare.to_out[0](O.joint_attention(q, k, v, pos, "dense").reshape(1, x.shape[1], -1).to(x))
+    assert float((y.float() - ref.float()).abs().max()) < 3e-2
+
+
+@torch.no_grad()
+def test_processor_surfaces_a_wait_that_gave_up(setup):
+    """Every launch of a processor carries the processor's own status word.  A bounded wait that runs out (made to
+    run out here with the library's self-test, on that very word) is raised by check_status() as H3A_ERR_TIMEOUT,
+    launches made while the word is set do nothing, and after a reset the processor works again."""
+    import pika_h3_flex_b200 as h3
+    from pika_h3_flex_b200.processor import B200AttnProcessor
+
+    attn, x, pos, _, _ = setup
+    proc = B200AttnProcessor()
+    y0 = proc(attn, x, position_ids=pos.cuda())
+    proc.check_status()  # clean
+    word = proc.status.tensor()
+    lib = h3._lib.load()
+    assert lib.h3a_selftest_wait_timeout(word.data_ptr(), 5_000_000, torch.cuda.current_stream().cuda_stream) == 0
+    with pytest.raises(h3.H3AError) as ei:
+        proc.check_status()
+    assert ei.value.status == h3._lib.H3A_ERR_TIMEOUT
+    with pytest.raises(h3.H3AError):
+        B200AttnProcessor(status=proc.status, check_every_call=True)(attn, x, position_ids=pos.cuda())
+    proc.status.reset()
+    y1 = proc(attn, x, position_ids=pos.cuda())
+    proc.check_status()
+    assert torch.equal(y0, y1)
 
 
 class PeftLikeLinear(nn.Module):

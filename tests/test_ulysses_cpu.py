@@ -117,6 +117,46 @@ def test_ulysses_rejects_bad_shapes():
     assert padded_heads(40, 8) == 40 and padded_heads(6, 4) == 8 and padded_heads(1, 8) == 8
 
 
+def _mismatch_worker(rank, world, port, result_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from pika_h3_flex_b200.ops import BlockIndex
+
+        H = 2
+        Ls = 64 if rank == 0 else 80  # rank 1 brings a longer shard
+        q, k, v = O.seeded_qkv(Ls, H, seed=5 + rank)
+        ua = UlyssesAttention(None, _lib.MODE_DENSE_BF16, None, prep_fn=_cpu_prep, attn_fn=_cpu_attn)
+        try:
+            ua(q, k, v, None)
+            verdict = "no error"
+        except ValueError as e:
+            verdict = "ValueError: " + str(e)
+        # a block index that does not describe the whole sequence is refused before any exchange
+        keep = O.neighbourhood_block_mask((4, 4, 4), 0, (1, 1, 1))
+        bi = BlockIndex.from_csr(*O.mask_to_csr(keep), n_k_tiles=keep.shape[1])  # 64 tokens = 1 tile
+        ub = UlyssesAttention(None, _lib.MODE_BLOCK_SPARSE, bi, prep_fn=_cpu_prep, attn_fn=_cpu_attn)
+        q, k, v = O.seeded_qkv(128, H, seed=9)  # 2 x 128 tokens = 2 tiles
+        try:
+            ub(q, k, v, None)
+            verdict2 = "no error"
+        except ValueError as e:
+            verdict2 = "ValueError: " + str(e)
+        torch.save({"shape": verdict, "index": verdict2}, os.path.join(result_dir, f"m{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ulysses_shape_mismatch_between_ranks_raises_on_every_rank(tmp_path):
+    """Ranks that bring shards of different length would block in an exchange whose sizes disagree; the one-time
+    host-side check must turn that into a ValueError on every rank instead."""
+    mp.spawn(_mismatch_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        res = torch.load(os.path.join(tmp_path, f"m{r}.pt"))
+        assert res["shape"].startswith("ValueError") and "disagree" in res["shape"], res
+        assert res["index"].startswith("ValueError") and "block index" in res["index"], res
+
+
 def test_round_robin_head_assignment_of_the_host_path_simulated():
     """The index arithmetic of the host-buffer Ulysses pipeline (heads dealt round-robin, blocks packed per peer,
     placed per source rank, unpacked per owner) with all ranks simulated in one process: after the inbound

@@ -33,14 +33,17 @@ def test_static_scratch_entry_point_matches_regular_one_twice_in_a_row(lib):
     assert h3.static_scratch_capacity() == 262144
     # first a wide index (many plan entries), then a narrow one on a shorter sequence: the second call sees the
     # first call's leftovers in the shared array and must not be affected by them
-    cases = [_case((6, 8, 16), 256, (2, 8, 8), 2, 71), _case((3, 8, 16), 128, (0, 1, 1), 3, 72)]
-    for q, k, v, csr, keep in cases:
+    # the third and fourth calls pass a logit bound (N(0,1) inputs: |q.k| / sqrt(128) stays far below 12): the fixed-
+    # reference kernels, on CTA pairs for the 18-tile sequence, whose merged plan lives in the same array
+    cases = [(_case((6, 8, 16), 256, (2, 8, 8), 2, 71), 0.0), (_case((3, 8, 16), 128, (0, 1, 1), 3, 72), 0.0),
+             (_case((8, 16, 16), 256, (2, 8, 8), 2, 73), 12.0), (_case((6, 8, 16), 256, (1, 2, 2), 2, 74), 12.0)]
+    for (q, k, v, csr, keep), bound in cases:
         bi = h3.BlockIndex.from_csr(csr[0], csr[1], keep.shape[1]).to("cuda")
-        want = h3.attn_fwd(q, k, v, h3.MODE_BLOCK_SPARSE, block_index=bi)
+        want = h3.attn_fwd(q, k, v, h3.MODE_BLOCK_SPARSE, block_index=bi, logit_bound=bound)
         status = torch.zeros(1, dtype=torch.int32, device="cuda")
         out = torch.full_like(want, 3.0)
         before = torch.cuda.memory_allocated()
-        h3.attn_fwd_sparse_static(q, k, v, bi, out, status_word=status)
+        h3.attn_fwd_sparse_static(q, k, v, bi, out, status_word=status, logit_bound=bound)
         assert torch.cuda.memory_allocated() == before  # the call took nothing from the caching allocator either
         assert h3.read_status(status) == 0
         # same kernels, same plan: bit-identical; the oracle bounds (2e-2 / 2e-3) hold as for the regular call
