@@ -293,12 +293,13 @@ def make_case(name, world, rank, dev, online_max=False):
     return c
 
 
-def kernel_name(c, online_max):
-    """Which attention kernel the library picks for this case: CTA pairs with a logit bound, from 16 key tiles and
-    (block-sparse) 12 % density up."""
-    pair = (not online_max and os.environ.get("H3A_PAIR", "1")[:1] != "0" and (c.Lk + 127) // 128 >= 16
-            and (c.mode_name != "block_sparse" or c.density >= 0.12))
-    return "attn_fwd_pair_kernel" if pair else "attn_fwd_kernel"
+def kernel_name(c, online_max, world=1):
+    """Which attention kernel the library launches for this case (asked of the library itself)."""
+    from pika_h3_flex_b200.ops import kernel_choice
+
+    nnz = 0 if c.bi_host is None else c.bi_host.nnz
+    ch = kernel_choice(c.L, c.Lk, max(1, c.H // world), c.mode, c.bound, nnz)
+    return ch["kernel"] + ("" if ch["fixed_reference"] else " (online softmax)")
 
 
 def single_gpu_step(c, status):
@@ -430,10 +431,10 @@ def roofline_of(c, attn_ms, online_max, world=1):
     1/world of the step's FLOPs; `achieved` and the fractions are per GPU (fractions of ONE GPU's peak)."""
     burst, sustained, src = measured_peaks()
     achieved = c.flops / world / (attn_ms * 1e-3) / 1e12
-    kern = kernel_name(c, online_max)
+    kern = kernel_name(c, online_max, world)
     traffic, traffic_src = None, None
     cap = NCU_TRAFFIC.get(c.mode_name)
-    if cap is not None and cap[0] == kern:
+    if cap is not None and cap[0] == kern:  # only a capture of the kernel variant that ran counts
         traffic = cap[1] * (c.L * c.H / world) / cap[2]
         traffic_src = f"{cap[3]} (captured workload scaled by L*H per launch)"
     r = {"bound": "tensor", "kernel": kern, "achieved": achieved, "peak": burst, "unit": "TFLOP/s", "frac": achieved / burst,

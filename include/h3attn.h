@@ -40,7 +40,8 @@ enum {
   H3A_ERR_WORKSPACE = -7, /* workspace missing or too small */
   H3A_ERR_DRIVER = -8,  /* driver entry point for tensor-map encoding not found */
   H3A_ERR_STATIC_SCRATCH = -9, /* h3a_attn_fwd_sparse_static: block index larger than the built-in scratch */
-  H3A_ERR_INDEX = -10   /* the device-side check of a block index failed (read back from the status word) */
+  H3A_ERR_INDEX = -10,  /* the device-side check of a block index failed (read back from the status word) */
+  H3A_ERR_BOUND = -11   /* logit_bound did not hold for the data: a row sum under- or overflowed (status word) */
 };
 
 #define H3A_MAX_RANKS 8 /* GPUs one sequence can be spread over (one NVSwitch domain) */
@@ -102,11 +103,13 @@ typedef struct h3a_attn_params {
                              calls of a forward pass and read once at its end; zero it before the first use */
   int64_t wait_limit_ns;  /* bound for each device-side wait; <= 0 selects 2 s */
   float logit_bound;      /* optional: a value B with |q.k| * softmax_scale <= B for every query/key pair (with
-                             QK-RMSNorm: 128 * max|w_q| * max|w_k| * softmax_scale).  When 0 < B <= 30 the kernel
-                             uses B as the fixed softmax reference instead of a running row maximum: the result is
-                             the same softmax (any reference is exact), without the max pass and without rescaling.
-                             A bound that is too small only costs range, not correctness, up to a factor 2^40.
-                             0 = unknown: running maximum. */
+                             QK-RMSNorm: 128 * max|w_q| * max|w_k| * softmax_scale).  When 0 < B <= 60 the kernel
+                             uses a fixed softmax reference (B up to 30, sliding to 0 at B = 60) instead of a running
+                             row maximum: the result is the same softmax (any reference is exact), without the max
+                             pass and without rescaling.  A bound that is somewhat too small only costs range; one that
+                             is wrong enough for a row sum to under- or overflow is reported through the status
+                             word (code 11, H3A_ERR_BOUND) and that launch's output must not be used.
+                             0, or a value above 60 = no usable bound: online softmax with a running row maximum. */
   int32_t sparse_heavy_pairs; /* BLOCK_SPARSE scheduling hint: the first this-many pairs of query tiles (256 rows
                              each) list far more key tiles than the rest (the dense audio rows of the joint
                              sequence); their CTAs of all heads are started first.  0 = no hint.  Never affects
@@ -153,6 +156,13 @@ const char* h3a_status_string(int32_t status);
  * no logit bound, short key range, or a CTA count that already fills whole waves); needs Lq, Lk, H, mode and
  * logit_bound only. */
 int32_t h3a_attn_workspace_bytes(const h3a_attn_params* p, size_t* bytes);
+
+/* Which kernel h3a_attn_fwd would launch for these params on the current device (needs Lq, Lk, H, mode, logit_bound,
+ * nnz for BLOCK_SPARSE, workspace / workspace_bytes for the split): an OR of the bits below.  For reports and tests. */
+#define H3A_KERNEL_CTA_PAIRS 1        /* attn_fwd_pair_kernel (two CTAs per MMA) instead of attn_fwd_kernel */
+#define H3A_KERNEL_FIXED_REFERENCE 2  /* fixed softmax reference from logit_bound instead of the running row maximum */
+#define H3A_KERNEL_SPLIT_LAST_WAVE 4  /* the CTA pairs of the last wave split the key range (+ combine_partials_kernel) */
+int32_t h3a_attn_kernel_choice(const h3a_attn_params* p, int32_t* choice);
 
 /* Launch the attention forward on `stream` (a cudaStream_t passed as void*). */
 int32_t h3a_attn_fwd(const h3a_attn_params* p, void* stream);
@@ -333,7 +343,8 @@ typedef struct h3a_adaln_params {
 int32_t h3a_adaln_norm(const h3a_adaln_params* p, void* stream);
 
 /* Copy the device status word to the host after synchronising `stream`.  Returns H3A_OK for 0, H3A_ERR_INDEX when a
- * block index failed its device-side check (low byte 10), H3A_ERR_TIMEOUT for every other non-zero value; *raw (optional)
+ * block index failed its device-side check (low byte 10), H3A_ERR_BOUND when a logit bound did not hold (low byte
+ * 11), H3A_ERR_TIMEOUT for every other non-zero value; *raw (optional)
  * receives the word: low byte = which wait or check, upper bits = the CTA (waits) or query tile (index check). */
 int32_t h3a_read_device_status(const int32_t* status_word, void* stream, int32_t* raw);
 

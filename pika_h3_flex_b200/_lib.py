@@ -18,10 +18,12 @@ H3A_ERR_ARG, H3A_ERR_ALIGN, H3A_ERR_SHAPE, H3A_ERR_ARCH = -1, -2, -3, -4
 H3A_ERR_LAUNCH, H3A_ERR_TIMEOUT, H3A_ERR_WORKSPACE, H3A_ERR_DRIVER = -5, -6, -7, -8
 H3A_ERR_STATIC_SCRATCH = -9
 H3A_ERR_INDEX = -10
+H3A_ERR_BOUND = -11
 MODE_DENSE_BF16, MODE_FP8_QK, MODE_BLOCK_SPARSE = 0, 1, 2
 ROPE_INTERLEAVED, ROPE_HALF = 0, 1
 PREP_FP8 = 1
 PREP_NO_NORM = 2
+KERNEL_CTA_PAIRS, KERNEL_FIXED_REFERENCE, KERNEL_SPLIT_LAST_WAVE = 1, 2, 4
 MAX_RANKS = 8
 PEER_HANDLE_BYTES = 64
 
@@ -41,6 +43,7 @@ EXPORTS = (
     "h3a_proj_fwd",
     "h3a_adaln_norm",
     "h3a_qk_prep_scatter",
+    "h3a_attn_kernel_choice",
     "h3a_peer_alloc",
     "h3a_peer_open",
     "h3a_peer_close",
@@ -155,6 +158,8 @@ def load() -> C.CDLL:
     lib.h3a_proj_fwd.restype = C.c_int32
     lib.h3a_adaln_norm.argtypes = [C.POINTER(AdaLnParams), C.c_void_p]
     lib.h3a_adaln_norm.restype = C.c_int32
+    lib.h3a_attn_kernel_choice.argtypes = [C.POINTER(AttnParams), C.POINTER(C.c_int32)]
+    lib.h3a_attn_kernel_choice.restype = C.c_int32
     lib.h3a_qk_prep_scatter.argtypes = [C.POINTER(PrepParams), C.POINTER(HeadScatter), C.POINTER(HeadScatter), C.c_void_p]
     lib.h3a_qk_prep_scatter.restype = C.c_int32
     lib.h3a_peer_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]

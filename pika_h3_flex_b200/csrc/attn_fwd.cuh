@@ -218,6 +218,14 @@ __global__ void wait_selftest_kernel(const AttnArgs args) {
 // kBadBlockIndex | offending query tile << 8: the attention launch that follows then does nothing, exactly as
 // after a wait that gave up.  Without a status word the launch runs on the entries that passed.
 constexpr int kBadBlockIndex = 10;
+// Fixed-reference kernels: a row whose exponentials all underflowed, or overflowed, shows in its row sum (0, inf or
+// NaN).  That can only happen when the caller's logit bound does not hold for the data; it is reported through the
+// status word (once) as kBadLogitBound | CTA << 8 and the stored rows are not to be used.
+constexpr int kBadLogitBound = 11;
+__device__ __forceinline__ void check_row_sum(const AttnArgs& a, float l, bool zero_is_legal) {
+  const bool bad = !(l < 3.0e38f) || (!zero_is_legal && !(l > 0.0f));  // NaN fails both comparisons
+  if (bad && a.status) atomicCAS(a.status, 0, kBadLogitBound | (static_cast<int>(blockIdx.x & 0x7FFFFF) << 8));
+}
 __device__ __forceinline__ int clamp_row_ptr(int v, int nnz) { return max(0, min(v, nnz)); }
 __device__ __forceinline__ void report_bad_index(int* status, int q_tile) {
   if (status) atomicCAS(status, 0, kBadBlockIndex | ((q_tile & 0x7FFFFF) << 8));
@@ -602,6 +610,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     __nv_bfloat16* orow = out_row_ptr(args, q_row, head) + 64 * hf;
     if (have) {
       const float l_tot = l_sum + lbuf[(hf ^ 1) * 128 + row];
+      if (hf == 0 && row_valid) check_row_sum(args, l_tot, false);
       const float inv = 1.0f / l_tot;
 #pragma unroll
       for (int i = 0; i < 2; ++i) {

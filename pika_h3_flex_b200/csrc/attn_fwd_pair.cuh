@@ -14,8 +14,11 @@
 //                       every commit is sent to the barrier in both CTAs
 //   warps 0-15        : softmax with the fixed reference, one warpgroup per (stream, 64-key half); P is published
 //                       with one arrive per warp on rank 0's barrier (local or through the cluster)
-// Only the fixed-reference softmax is implemented here (dense bf16, FP8-QK, block-sparse); the running-maximum
-// softmax runs on the single-CTA kernel.
+// kFixed = true: the fixed-reference softmax (dense bf16, FP8-QK, block-sparse), 16 softmax warps as above.
+// kFixed = false (dense bf16 and FP8-QK): the online softmax with a running row maximum and lazy rescaling of O in
+// TMEM, for callers that cannot bound their logits: 8 softmax warps, one warpgroup per stream walking both halves of
+// every tile exactly as in the single-CTA kernel; the issuers then also signal the completion of every P V
+// (o_done), which a rescale has to wait for.
 //
 // Block-sparse: the four key-tile lists of a pair are merged into one plan, entry = (key tile << 4) | flags, flag
 // bit 2 t + r set when query tile 4 c + 2 t + r lists the key tile.  Both CTAs load every listed tile; stream t
@@ -44,7 +47,7 @@ namespace h3a {
 #endif
 constexpr int kPairStages = H3A_PAIR_STAGES;
 constexpr int kPairStageBytes = 16384;
-constexpr int kPairThreads = AttnLayout<true>::kThreads;
+constexpr int kPairThreads = AttnLayout<true>::kThreads;  // fixed-reference kernels; the running-maximum ones use AttnLayout<false>
 
 struct PairBars {
   uint64_t kv_full[kPairStages];   // waited on in rank 0: counts the bytes of both CTAs' halves
@@ -53,6 +56,7 @@ struct PairBars {
   uint64_t s_full[2][2];           // [stream][half], both CTAs
   uint64_t p_full[2][2];           // rank 0: one arrive per softmax warp of the (stream, half) warpgroup of BOTH CTAs
   uint64_t o_full[2];              // both CTAs: every MMA of stream t has completed (one phase, after the last tile)
+  uint64_t o_done[2][2];           // both CTAs, running-maximum kernels: the P V of (stream, half) has completed, one phase per tile
   uint64_t drain[2];               // rank 0: last commit of issuer t
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
@@ -143,6 +147,7 @@ __global__ void combine_partials_kernel(const AttnArgs args, int n_clusters) {
       acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
       l += part_l[rix];
     }
+    if (sub == 0) check_row_sum(args, l, false);
     const float inv = 1.0f / l;
     uint4 w;
     w.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
@@ -156,8 +161,8 @@ __global__ void combine_partials_kernel(const AttnArgs args, int n_clusters) {
   if (args.o_n_ranks > 1) __threadfence_system();  // rows stored into other GPUs' memory
 }
 
-template <bool kFp8, bool kSparse>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+template <bool kFp8, bool kSparse, bool kFixed = true>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(AttnLayout<kFixed>::kThreads, 1)
 attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const AttnArgs args) {
   extern __shared__ uint8_t smem_raw[];
@@ -168,7 +173,10 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const uint32_t ring_smem = base + 2 * kQTileBytes;
   PairBars* bars = reinterpret_cast<PairBars*>(smem + 2 * kQTileBytes + kPairStages * kPairStageBytes);
 
-  using LY = AttnLayout<true>;
+  static_assert(kFixed || (!kSparse && !kPairFullS), "the running-maximum pair kernel is dense, with N = 64 S groups");
+  using LY = AttnLayout<kFixed>;
+  constexpr int kHelperRegs = kFixed ? kPairHelperRegs : LY::kHelperRegs;
+  constexpr int kSoftmaxRegs = kFixed ? kPairSoftmaxRegs : LY::kSoftmaxRegs;
   constexpr int kProducerWarp = LY::kSoftmaxWarps;
   constexpr int kIssuerWarp = LY::kSoftmaxWarps + 1;
   const int warp = threadIdx.x >> 5;
@@ -242,6 +250,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         mbar_init(smem_u32(&bars->p_full[t][hf]), 8);
       }
       mbar_init(smem_u32(&bars->o_full[t]), 1);
+      mbar_init(smem_u32(&bars->o_done[t][0]), 1);
+      mbar_init(smem_u32(&bars->o_done[t][1]), 1);
       mbar_init(smem_u32(&bars->drain[t]), 1);
     }
     bars->abort_flag = 0;
@@ -274,7 +284,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   tmem = bars->tmem_base;
 
   if (warp >= LY::kSoftmaxWarps) {
-   setmaxnreg_dec<kPairHelperRegs>();
+   setmaxnreg_dec<kHelperRegs>();
    if (warp == kProducerWarp) {
     // =========================================================== producer (both CTAs)
     const uint32_t leader = elect_one();
@@ -371,6 +381,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         for (int k = 0; k < 4; ++k)
           umma_pair_bf16_ts_if(leader, o_tmem, a + k * 8, vd + (k * 2048 >> 4), idesc_pv, (pv_cnt > 0 || k > 0) ? 1u : 0u);
         ++pv_cnt;
+        if constexpr (!kFixed) commit_both(&bars->o_done[t][hf]);  // a rescale of O waits for this
       };
 
       // Each issuer walks every plan entry, also those its stream skips: a K/V stage is released by one commit
@@ -432,7 +443,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     __syncwarp();
    }
   } else {
-    setmaxnreg_inc<kPairSoftmaxRegs>();
+    setmaxnreg_inc<kSoftmaxRegs>();
+    if constexpr (kFixed) {
     // =========================================================== softmax, fixed reference: one warpgroup per (stream, half)
     const int wg = warp >> 2;
     const int t = wg & 1;
@@ -538,6 +550,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const bool row_valid = q_row < args.Lq;
     __nv_bfloat16* orow = out_row_ptr(args, q_row, head) + 64 * hf;
     const float l_tot = l_sum + lbuf[(hf ^ 1) * 128 + row];
+    // block-sparse: a row whose query tile lists nothing legitimately sums to zero; a share of a split row may too
+    if (have && hf == 0 && row_valid) check_row_sum(args, l_tot, kSparse || part_slot >= 0);
     if (!kSparse && part_slot >= 0) {
       // a share of the key tiles: leave the un-normalised sums for the combining kernel
       if (have) {
@@ -581,6 +595,186 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
       for (int x = 0; x < 64; x += 8) *reinterpret_cast<uint4*>(orow + x) = z;
       if (args.lse && hf == 0) args.lse[static_cast<long long>(head) * args.Lq + q_row] = -INFINITY;
+    }
+    } else {
+    // =========================================================== online softmax: running row maximum, lazy rescale of O
+    // One warpgroup per stream walks both halves of every key tile (they share the row's maximum), as in the
+    // single-CTA kernel.  What the pair changes: P is published with one arrive per warp on rank 0's barrier, and O
+    // may be rescaled only when the pair's previous P V of the stream has completed in BOTH CTAs - o_done is
+    // committed to each CTA's copy, and the next P V is not issued before all eight warps of the two CTAs have
+    // published, which each does after its own rescale stores have completed.
+    const int t = warp >> 2;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem + lane_base + t * kTile;
+    const uint32_t o_addr = tmem + lane_base + 256 + t * kTile;
+    const int q_row = q_tile(t) * kTile + row;
+    const int last_tile = args.n_kv_tiles - 1;
+    const int tail = args.Lk - last_tile * kTile;
+    const uint32_t p_bar[2] = {at0(&bars->p_full[t][0]), at0(&bars->p_full[t][1])};
+    float qs = 1.0f;
+    if constexpr (kFp8) {
+      const int qb = min(q_tile(t), args.nqb - 1);
+      qs = args.q_scale[head * args.nqb + qb];
+    }
+    float m_ref = 0.0f, l_sum = 0.0f;
+    uint32_t j = 0;
+    bool ok = true;
+    uint32_t ra[64], rb[64];  // two register images of an S half: one being processed, one being prefetched
+
+    auto load_s = [&](uint32_t (&r)[64], int hf) {
+      tc_fence_after_sync();
+      tmem_ld32(s_addr + hf * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+      tmem_ld32(s_addr + hf * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+    };
+    auto fetch_s = [&](uint32_t (&r)[64], int hf, uint32_t jt) -> bool {
+      const bool got = warp_wait(wc, smem_u32(&bars->s_full[t][hf]), jt & 1, kWaitSFull);
+      if (got) load_s(r, hf);
+      return got;
+    };
+    auto try_fetch_s = [&](uint32_t (&r)[64], int hf, uint32_t jt) -> bool {
+      const bool ready = __all_sync(0xFFFFFFFFu, mbar_test_wait(smem_u32(&bars->s_full[t][hf]), jt & 1));
+      if (ready) load_s(r, hf);
+      return ready;
+    };
+    auto softmax_half = [&](uint32_t (&s)[64], int hf, int tile, float c) -> bool {
+      if (tile == last_tile && tail < kTile) {
+        const int valid = tail - hf * 64;
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (i >= valid) s[i] = 0xFF800000u;  // -inf
+      }
+      float mx0 = fmax3(__uint_as_float(s[0]), __uint_as_float(s[1]), __uint_as_float(s[2]));
+      float mx1 = fmax3(__uint_as_float(s[3]), __uint_as_float(s[4]), __uint_as_float(s[5]));
+      float mx2 = fmax3(__uint_as_float(s[6]), __uint_as_float(s[7]), __uint_as_float(s[8]));
+      float mx3 = fmax3(__uint_as_float(s[9]), __uint_as_float(s[10]), __uint_as_float(s[11]));
+#pragma unroll
+      for (int i = 12; i < 60; i += 8) {
+        mx0 = fmax3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+        mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+        mx2 = fmax3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+        mx3 = fmax3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+      }
+      mx0 = fmax3(mx0, __uint_as_float(s[60]), __uint_as_float(s[61]));
+      mx1 = fmax3(mx1, __uint_as_float(s[62]), __uint_as_float(s[63]));
+      const float m_tile = fmax3(fmaxf(mx0, mx1), mx2, mx3) * c;
+      if (j == 0 && hf == 0) {
+        m_ref = m_tile;
+      } else {
+        const bool grow = (m_tile - m_ref) > kRescaleThreshold;
+        if (__any_sync(0xFFFFFFFFu, grow)) {
+          const float m_new = fmaxf(m_ref, m_tile);
+          const float alpha = ex2_approx(m_ref - m_new);
+          m_ref = m_new;
+          l_sum *= alpha;
+          // the stream's previous P V (the only one that can still be running: MMAs complete in issue order)
+          if (!warp_wait(wc, smem_u32(&bars->o_done[t][hf ^ 1]), (hf ? j : j - 1) & 1, kWaitOFull)) return false;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t o[32];
+            tmem_ld32(o_addr + 32 * i, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * alpha);
+            tmem_st32(o_addr + 32 * i, o);
+          }
+        }
+      }
+      uint64_t acc0 = 0, acc1 = 0;
+      const uint64_t c2 = pack2(c, c), nm2 = pack2(-m_ref, -m_ref);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const uint64_t x = fma2(pack2u(s[2 * i], s[2 * i + 1]), c2, nm2);
+        uint64_t pp;
+        if ((i & 3) < (kFp8 ? kPolyPairsFp8 : kPolyPairsBf16)) {
+          pp = exp2_poly2(x);
+        } else {
+          float x0, x1;
+          unpack2(x, x0, x1);
+          pp = pack2(ex2_approx(x0), ex2_approx(x1));
+        }
+        if (i & 1) acc1 = add2(acc1, pp);
+        else acc0 = add2(acc0, pp);
+        float p0, p1;
+        unpack2(pp, p0, p1);
+        s[i] = pack_bf16x2(p0, p1);
+      }
+      float a0, a1, a2, a3;
+      unpack2(acc0, a0, a1);
+      unpack2(acc1, a2, a3);
+      l_sum += (a0 + a1) + (a2 + a3);
+      return true;
+    };
+    auto publish_p = [&](uint32_t (&s)[64], int hf) {
+      tmem_st32(s_addr + hf * 64, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_wait_st();  // also covers the stores of a rescale of O just before
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(p_bar[hf]);
+    };
+
+    if (n_it > 0) ok = fetch_s(ra, 0, 0);
+    for (int it = 0; ok && it < n_it; ++it) {
+      const int tile = entry_at(it) >> 4;
+      const bool has_next = it + 1 < n_it;
+      float c = args.scale_log2;
+      if constexpr (kFp8) c *= qs * args.k_scale[head * args.nkb + tile];
+      // half 0 from image A; half 1 is loaded into image B as early as its S is complete
+      tmem_wait_ld();
+      reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&ra[0]));
+      reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&ra[32]));
+      ok = softmax_half(ra, 0, tile, c);
+      if (!ok) break;
+      {
+        const bool early = try_fetch_s(rb, 1, j);
+        publish_p(ra, 0);
+        if (!early) ok = fetch_s(rb, 1, j);
+        if (!ok) break;
+      }
+      tmem_wait_ld();
+      reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&rb[0]));
+      reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&rb[32]));
+      ok = softmax_half(rb, 1, tile, c);
+      if (!ok) break;
+      {
+        const bool early = has_next && try_fetch_s(ra, 0, j + 1);
+        publish_p(rb, 1);
+        if (!early && has_next) ok = fetch_s(ra, 0, j + 1);
+        if (!ok) break;
+      }
+      ++j;
+    }
+    // ---- epilogue: O / l -> bf16 -> global (each thread owns its whole row)
+    const bool row_valid = q_row < args.Lq;
+    __nv_bfloat16* orow = out_row_ptr(args, q_row, head);
+    if (ok && j > 0) {
+      ok = warp_wait(wc, smem_u32(&bars->o_full[t]), 0, kWaitOFull);
+      if (ok) {
+        tc_fence_after_sync();
+        const float inv = 1.0f / l_sum;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + 32 * i, o);
+          tmem_wait_ld();
+          if (row_valid) {
+#pragma unroll
+            for (int x = 0; x < 32; x += 8) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(o[x]) * inv, __uint_as_float(o[x + 1]) * inv);
+              w.y = pack_bf16x2(__uint_as_float(o[x + 2]) * inv, __uint_as_float(o[x + 3]) * inv);
+              w.z = pack_bf16x2(__uint_as_float(o[x + 4]) * inv, __uint_as_float(o[x + 5]) * inv);
+              w.w = pack_bf16x2(__uint_as_float(o[x + 6]) * inv, __uint_as_float(o[x + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + 32 * i + x) = w;
+            }
+          }
+        }
+        if (row_valid && args.lse)
+          args.lse[static_cast<long long>(head) * args.Lq + q_row] = (m_ref + log2f(l_sum)) * 0.6931471805599453f;
+      }
+    }
     }
   }
   }  // run

@@ -137,6 +137,11 @@ int32_t launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
 // Pairs pay a cluster set-up per CTA; with very few key tiles (cross-attention to 512 text tokens = 4 tiles:
 // 0.93 ms on pairs against 0.80 ms) the single-CTA kernel is the faster one.
 constexpr int kPairMinKeyTiles = 16;
+constexpr double kPairMinDensity = 0.12;
+
+constexpr float kMaxLogitBound = 60.f;
+bool fixed_reference_ok(float bound) { return bound > 0.f && bound <= kMaxLogitBound; }
+float fixed_reference(float bound) { return bound <= 30.f ? bound : kMaxLogitBound - bound; }
 
 bool pair_kernel_enabled() {
   static const bool on = [] {
@@ -193,18 +198,18 @@ SplitPlan plan_split(int64_t Lq, int64_t Lk, int64_t H) {
   return sp;
 }
 
-template <bool kFp8, bool kSparse = false>
+template <bool kFp8, bool kSparse = false, bool kFixed = true>
 int32_t launch_attn_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a, cudaStream_t st) {
   static std::once_flag once[kMaxDevices];
   static cudaError_t attr_err[kMaxDevices];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return H3A_ERR_LAUNCH;
   std::call_once(once[dev], [dev] {
-    cudaError_t e = cudaFuncSetAttribute(h3a::attn_fwd_pair_kernel<kFp8, kSparse>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(h3a::attn_fwd_pair_kernel<kFp8, kSparse, kFixed>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          h3a::kPairSmemBytes);
     cudaFuncAttributes fa;
-    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, h3a::attn_fwd_pair_kernel<kFp8, kSparse>);
-    if (e == cudaSuccess && fa.numRegs < h3a::AttnLayout<true>::kLaunchRegs) e = cudaErrorLaunchOutOfResources;
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, h3a::attn_fwd_pair_kernel<kFp8, kSparse, kFixed>);
+    if (e == cudaSuccess && fa.numRegs < h3a::AttnLayout<kFixed>::kLaunchRegs) e = cudaErrorLaunchOutOfResources;
     attr_err[dev] = e;
   });
   if (attr_err[dev] != cudaSuccess) return H3A_ERR_LAUNCH;
@@ -212,7 +217,7 @@ int32_t launch_attn_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUt
   unsigned pairs = n_clusters * static_cast<unsigned>(a.H);
   const bool split = !kSparse && a.kv_splits > 1;
   if (split) pairs = static_cast<unsigned>(a.split_begin) + (pairs - static_cast<unsigned>(a.split_begin)) * static_cast<unsigned>(a.kv_splits);
-  h3a::attn_fwd_pair_kernel<kFp8, kSparse><<<2u * pairs, h3a::kPairThreads, h3a::kPairSmemBytes, st>>>(mq, mk, mv, a);  // cluster shape (2,1,1) is the kernel's
+  h3a::attn_fwd_pair_kernel<kFp8, kSparse, kFixed><<<2u * pairs, h3a::AttnLayout<kFixed>::kThreads, h3a::kPairSmemBytes, st>>>(mq, mk, mv, a);  // cluster shape (2,1,1) is the kernel's
   if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
   if (split) {
     const unsigned groups = n_clusters * static_cast<unsigned>(a.H) - static_cast<unsigned>(a.split_begin);
@@ -278,10 +283,12 @@ int32_t attn_fwd_impl(const h3a_attn_params* p, void* workspace, size_t workspac
     a.o_rank_rows = p->o_rank_rows;
     for (int r = 0; r < p->o_n_ranks; ++r) a.o_rank[r] = static_cast<__nv_bfloat16*>(p->o_rank_base[r]);
   }
-  // fixed softmax reference: the bound rescaled like the logits (x softmax_scale is already in it), in log2 units.
-  // Above 30 (2^-87 for a logit at minus the bound) the running-maximum kernel is used instead.
-  const bool fixed = p->logit_bound > 0.f && p->logit_bound <= 30.f;
-  a.fixed_m = fixed ? p->logit_bound * 1.4426950408889634f : 0.f;
+  // Fixed softmax reference, in log2 units (x softmax_scale is already in the bound).  Logits lie in [-B, B] and every
+  // term 2^((s - ref) log2 e) must stay inside fp32's range with room for the row sum: |s - ref| <= 60.  Up to B = 30
+  // the reference is B itself (terms <= 1); from there to B = 60 it slides down to 0 (ref = 60 - B), which keeps
+  // s - ref within [-60, 60].  Beyond 60 no fixed reference is safe: the running-maximum kernels are used instead.
+  const bool fixed = fixed_reference_ok(p->logit_bound);
+  a.fixed_m = fixed ? fixed_reference(p->logit_bound) * 1.4426950408889634f : 0.f;
 
   if (sparse) {
     const size_t need = sparse_workspace_bytes(p);
@@ -296,7 +303,7 @@ int32_t attn_fwd_impl(const h3a_attn_params* p, void* workspace, size_t workspac
     // neighbourhood masks that duplicated work outweighs what the pair saves (measured: 7 % density, 7 % extra
     // tiles, 3 % slower; 23 % density, 0.4 % extra, 7 % faster), so sparse launches go to pairs from 12 % up.
     const double density = static_cast<double>(p->nnz) / (static_cast<double>(a.nqb) * static_cast<double>(a.nkb));
-    if (fixed && pair_kernel_enabled() && density >= 0.12 && a.n_kv_tiles >= kPairMinKeyTiles) {
+    if (fixed && pair_kernel_enabled() && density >= kPairMinDensity && a.n_kv_tiles >= kPairMinKeyTiles) {
       // CTA pairs: one merged plan per four query tiles (never longer than the four lists together, and there
       // are no more groups of four than pairs of two, so the same workspace holds it)
       const int n_clusters = (p->Lq + 511) / 512;
@@ -325,6 +332,14 @@ int32_t attn_fwd_impl(const h3a_attn_params* p, void* workspace, size_t workspac
     // CTA pairs: each CTA stages 32-key boxes of K (its share of every 64-key MMA group) and 64 columns of V
     if ((rc = make_map(&mk, p->k, fp8, p->Lk, p->H, p->k_stride_l, p->k_stride_h, h3a::kPairKBoxRows)) != H3A_OK) return rc;
     return fp8 ? launch_attn_pair<true>(mq, mk, mv, a, st) : launch_attn_pair<false>(mq, mk, mv, a, st);
+  }
+  if (!fixed && pair_kernel_enabled() && a.n_kv_tiles >= kPairMinKeyTiles) {
+    // no usable logit bound: the online softmax (running row maximum), also on CTA pairs; no split of the last wave
+    // (partial rows of different maxima are not directly addable)
+    a.split_begin = static_cast<int>((p->Lq + 511) / 512 * p->H);
+    a.kv_splits = 1;
+    if ((rc = make_map(&mk, p->k, fp8, p->Lk, p->H, p->k_stride_l, p->k_stride_h, h3a::kPairKBoxRows)) != H3A_OK) return rc;
+    return fp8 ? launch_attn_pair<true, false, false>(mq, mk, mv, a, st) : launch_attn_pair<false, false, false>(mq, mk, mv, a, st);
   }
   if (fp8) return fixed ? launch_attn<true, false, true>(mq, mk, mv, a, st) : launch_attn<true, false, false>(mq, mk, mv, a, st);
   return fixed ? launch_attn<false, false, true>(mq, mk, mv, a, st) : launch_attn<false, false, false>(mq, mk, mv, a, st);
@@ -411,6 +426,7 @@ const char* h3a_status_string(int32_t s) {
     case H3A_ERR_WORKSPACE: return "workspace missing or too small";
     case H3A_ERR_DRIVER: return "driver entry point cuTensorMapEncodeTiled not available";
     case H3A_ERR_STATIC_SCRATCH: return "block index too large for the static scratch array (kept tiles + query-tile pairs > 262144)";
+    case H3A_ERR_BOUND: return "logit_bound does not hold for the data: a softmax row sum under- or overflowed (pass a larger bound, or 0)";
     case H3A_ERR_INDEX: return "malformed block index (row pointers must not decrease and stay within nnz; columns in range, ascending)";
     default: return "unknown status";
   }
@@ -423,10 +439,29 @@ int32_t h3a_attn_workspace_bytes(const h3a_attn_params* p, size_t* bytes) {
   } else {
     // optional: partial sums of the split last wave (dense launches with a logit bound); without it the launch
     // simply does not split
-    const bool fixed = p->logit_bound > 0.f && p->logit_bound <= 30.f;
+    const bool fixed = fixed_reference_ok(p->logit_bound);
     const bool pairs = fixed && pair_kernel_enabled() && p->Lq > 0 && p->H > 0 && (p->Lk + 127) / 128 >= kPairMinKeyTiles;
     *bytes = pairs ? plan_split(p->Lq, p->Lk, p->H).bytes : 0;
   }
+  return H3A_OK;
+}
+
+int32_t h3a_attn_kernel_choice(const h3a_attn_params* p, int32_t* choice) {
+  if (!p || !choice) return H3A_ERR_ARG;
+  if (p->Lq <= 0 || p->Lk <= 0 || p->H <= 0) return H3A_ERR_SHAPE;
+  const bool fixed = fixed_reference_ok(p->logit_bound);
+  const int64_t nqb = (p->Lq + 127) / 128, nkb = (p->Lk + 127) / 128;
+  bool pairs = pair_kernel_enabled() && nkb >= kPairMinKeyTiles;
+  if (p->mode == H3A_MODE_BLOCK_SPARSE)
+    pairs = pairs && fixed && static_cast<double>(p->nnz) / (static_cast<double>(nqb) * static_cast<double>(nkb)) >= kPairMinDensity;
+  int32_t c = 0;
+  if (pairs) c |= H3A_KERNEL_CTA_PAIRS;
+  if (fixed) c |= H3A_KERNEL_FIXED_REFERENCE;
+  if (pairs && fixed && p->mode != H3A_MODE_BLOCK_SPARSE && p->workspace && aligned16(p->workspace)) {
+    const SplitPlan sp = plan_split(p->Lq, p->Lk, p->H);
+    if (sp.kv_splits > 1 && p->workspace_bytes >= sp.bytes) c |= H3A_KERNEL_SPLIT_LAST_WAVE;
+  }
+  *choice = c;
   return H3A_OK;
 }
 
@@ -698,7 +733,8 @@ int32_t h3a_read_device_status(const int32_t* status_word, void* stream, int32_t
   if (cudaStreamSynchronize(st) != cudaSuccess) return H3A_ERR_LAUNCH;
   if (raw) *raw = v;
   if (v == 0) return H3A_OK;
-  return (v & 0xFF) == h3a::kBadBlockIndex ? H3A_ERR_INDEX : H3A_ERR_TIMEOUT;
+  if ((v & 0xFF) == h3a::kBadBlockIndex) return H3A_ERR_INDEX;
+  return (v & 0xFF) == h3a::kBadLogitBound ? H3A_ERR_BOUND : H3A_ERR_TIMEOUT;
 }
 
 }  // extern "C"

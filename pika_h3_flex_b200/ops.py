@@ -341,6 +341,21 @@ def split_workspace_bytes(Lq: int, Lk: int, H: int, mode: int = _lib.MODE_DENSE_
     return int(need.value)
 
 
+def kernel_choice(Lq: int, Lk: int, H: int, mode: int = _lib.MODE_DENSE_BF16, logit_bound: float = 0.0, nnz: int = 0,
+                  workspace_bytes: int = 0) -> dict:
+    """Which attention kernel the library launches for this shape on the current device (``h3a_attn_kernel_choice``):
+    ``{"kernel", "cta_pairs", "fixed_reference", "split_last_wave"}``."""
+    p = AttnParams()
+    p.Lq, p.Lk, p.H, p.d, p.B, p.mode, p.logit_bound, p.nnz = int(Lq), int(Lk), int(H), HEAD_DIM, 1, int(mode), float(logit_bound), int(nnz)
+    if workspace_bytes:
+        p.workspace, p.workspace_bytes = 16, int(workspace_bytes)  # only looked at, never dereferenced
+    c = C.c_int32(0)
+    check(_lib.load().h3a_attn_kernel_choice(C.byref(p), C.byref(c)), "h3a_attn_kernel_choice")
+    pairs = bool(c.value & _lib.KERNEL_CTA_PAIRS)
+    return {"kernel": "attn_fwd_pair_kernel" if pairs else "attn_fwd_kernel", "cta_pairs": pairs,
+            "fixed_reference": bool(c.value & _lib.KERNEL_FIXED_REFERENCE), "split_last_wave": bool(c.value & _lib.KERNEL_SPLIT_LAST_WAVE)}
+
+
 def proj_fwd(
     x: torch.Tensor,
     weight: torch.Tensor,
@@ -508,7 +523,7 @@ def read_status(status_word: torch.Tensor) -> int:
     index failed its check)."""
     raw = C.c_int32(0)
     rc = _lib.load().h3a_read_device_status(status_word.data_ptr(), _stream(), C.byref(raw))
-    if rc not in (_lib.H3A_OK, _lib.H3A_ERR_TIMEOUT, _lib.H3A_ERR_INDEX):
+    if rc not in (_lib.H3A_OK, _lib.H3A_ERR_TIMEOUT, _lib.H3A_ERR_INDEX, _lib.H3A_ERR_BOUND):
         check(rc, "h3a_read_device_status")
     return raw.value
 

@@ -29,7 +29,7 @@ def test_header_and_library_agree(lib):
 def test_version_and_status_strings(lib):
     assert _lib.version() == (0, 2)
     seen = set()
-    for code in range(0, -11, -1):
+    for code in range(0, -12, -1):
         s = _lib.status_string(code)
         assert s and s != "unknown status" and s not in seen
         seen.add(s)

@@ -465,12 +465,58 @@ def test_fixed_logit_bound_gives_the_same_softmax(h, L, Lk, H):
     ref, ref_lse = O.attention(q.float(), k.float(), v.float(), return_lse=True)
     s = torch.einsum("qhd,khd->hqk", q.float(), k.float()) / 128 ** 0.5
     true_bound = float(s.abs().max())
-    for bound in (true_bound * 1.05, 30.0, true_bound * 0.5):  # tight, loosest accepted, and too small (still exact)
+    # tight; the largest bound that is its own reference; the sliding-reference range up to its end; too small (still exact)
+    for bound in (true_bound * 1.05, 30.0, 45.0, 60.0, true_bound * 0.5):
         out, lse = h.attn_fwd(dev(q), dev(k), dev(v), return_lse=True, logit_bound=bound)
         check(out, ref, mx=3e-2 if Lk < 256 else BF16_MAX, mean=4e-3 if Lk < 256 else BF16_MEAN)
         assert float((lse.cpu().t() - ref_lse).abs().max()) < 2e-3
     out = h.attn_fwd(dev(q), dev(k), dev(v), logit_bound=1e6)  # unusable bound: falls back to the running maximum
     check(out, ref, mx=3e-2 if Lk < 256 else BF16_MAX, mean=4e-3 if Lk < 256 else BF16_MEAN)
+
+
+@pytest.mark.parametrize("L,Lk,H", [(512, 1024, 2), (1000, 2304, 2)])
+def test_large_logits_inside_the_sliding_reference_range(h, L, Lk, H):
+    """Logits spread over +-50 (operands scaled up): a bound of 55 uses the sliding reference (60 - B = 5), on the
+    single-CTA kernel (8 key tiles) and on CTA pairs (18); rows keep full accuracy although their maxima differ by
+    tens of units, and the online kernels agree."""
+    g = torch.Generator().manual_seed(17)
+    q = (3.0 * torch.randn(L, H, 128, generator=g)).bfloat16()
+    k = (3.0 * torch.randn(Lk, H, 128, generator=g)).bfloat16()
+    v = torch.randn(Lk, H, 128, generator=g).bfloat16()
+    s = torch.einsum("qhd,khd->hqk", q.float(), k.float()) / 128 ** 0.5
+    assert 30.0 < float(s.abs().max()) < 55.0
+    ref = O.attention(q.double(), k.double(), v.double()).float()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for bound in (55.0, 0.0):
+        ch = h.ops.kernel_choice(L, Lk, H, logit_bound=bound)
+        assert ch["fixed_reference"] == (bound > 0) and ch["cta_pairs"] == (Lk >= 2048)
+        out = h.attn_fwd(dev(q), dev(k), dev(v), logit_bound=bound, status_word=status)
+        assert h.read_status(status) == 0
+        check(out, ref, mx=4e-2, mean=3e-3, rel=1.5e-2)  # peaked rows: the output is close to single V rows, |v| up to 4
+
+
+@pytest.mark.parametrize("Lk", [1024, 2304])
+def test_a_logit_bound_that_does_not_hold_is_reported(h, Lk):
+    """Operands far outside a stated bound of 12 (logits of several hundred): exponentials overflow, the row sums are
+    infinite, and the launch says so through the status word (H3A_ERR_BOUND) instead of handing back garbage silently;
+    the same data with no bound (online softmax) is fine."""
+    from pika_h3_flex_b200 import _lib
+
+    L, H = 512, 2
+    g = torch.Generator().manual_seed(18)
+    q = (8 * torch.randn(L, H, 128, generator=g)).bfloat16()
+    k = (8 * torch.randn(Lk, H, 128, generator=g)).bfloat16()
+    v = torch.randn(Lk, H, 128, generator=g).bfloat16()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    h.attn_fwd(dev(q), dev(k), dev(v), logit_bound=12.0, status_word=status)
+    assert h.read_status(status) & 0xFF == 11
+    with pytest.raises(h.H3AError) as ei:
+        h.check_status(status)
+    assert ei.value.status == _lib.H3A_ERR_BOUND
+    status.zero_()
+    out = h.attn_fwd(dev(q), dev(k), dev(v), logit_bound=0.0, status_word=status)
+    assert h.read_status(status) == 0
+    check(out, O.attention(q.double(), k.double(), v.double()).float(), mx=5e-2, mean=4e-3, rel=2e-2)
 
 
 def test_joint_path_bound_from_norm_weights(h):

@@ -116,7 +116,7 @@ def test_peer_arena_on_one_rank(h):
     assert a_off == 0 and b_off == 1024 and c.size == 5120
     before = torch.cuda.memory_allocated()
     ar = PeerArena(c.size)
-    assert torch.cuda.memory_allocated() == before  # not from torch's allocator: other processes must be able to map it
+    assert torch.cuda.memory_allocated() - before < 4096  # not from torch's allocator (other processes must be able to map it); only the barrier's flag is
     t = ar.tensor(b_off, (16, 128), torch.bfloat16)
     t.fill_(3.0)
     u = ar.tensor(b_off, (16 * 128,), torch.bfloat16)

@@ -179,6 +179,44 @@ def test_processor_refuses_norms_it_does_not_implement(setup):
 
 
 @torch.no_grad()
+def test_learned_norm_weights_beyond_the_fixed_reference_range_use_the_online_kernel():
+    """norm_q / norm_k weights three times the usual size: the bound from the weights (128 * 3 * 3 / sqrt(128) > 100)
+    is outside the fixed-reference range, so the launch is the online softmax, on CTA pairs at this length (18 key
+    tiles), and must match the oracle like any other."""
+    from pika_h3_flex_b200 import ops
+    from pika_h3_flex_b200.processor import B200AttnProcessor
+
+    torch.manual_seed(5)
+    attn = StubAttention(256, 2).cuda().bfloat16()
+    attn.norm_q.weight.mul_(3.0)
+    attn.norm_k.weight.mul_(3.0)
+    grid, n_audio = (8, 16, 16), 256  # 2,304 tokens
+    pos = O.make_positions(grid, n_audio)
+    x = torch.randn(1, pos.shape[0], 256, device="cuda").bfloat16()
+    proc = B200AttnProcessor()
+    y = proc(attn, x, position_ids=pos.cuda())
+    proc.check_status()
+    bound = ops.normed_logit_bound(attn.norm_q.weight, attn.norm_k.weight)
+    assert bound > 60.0
+    ch = ops.kernel_choice(pos.shape[0], pos.shape[0], 2, logit_bound=bound)
+    assert ch["cta_pairs"] and not ch["fixed_reference"]
+    ref = oracle_forward(attn, x, None, pos)
+    # nine times the usual logit scale: peaked rows, outputs of order one; bf16 rounding of such values is 4e-3 per term
+    assert float((y.float() - ref.float()).abs().max()) < 6e-2
+    assert float((y.float() - ref.float()).norm() / ref.float().norm()) < 1e-2
+    # 1.5 x the usual size stays inside the range (bound about 29): fixed reference
+    attn.norm_q.weight.mul_(0.5)
+    attn.norm_k.weight.mul_(0.5)
+    proc2 = B200AttnProcessor()
+    y2 = proc2(attn, x, position_ids=pos.cuda())
+    proc2.check_status()
+    b2 = ops.normed_logit_bound(attn.norm_q.weight, attn.norm_k.weight)
+    assert 20.0 < b2 < 60.0 and ops.kernel_choice(pos.shape[0], pos.shape[0], 2, logit_bound=b2)["fixed_reference"]
+    ref2 = oracle_forward(attn, x, None, pos).float()
+    assert float((y2.float() - ref2).abs().max()) < 4e-2 and float((y2.float() - ref2).norm() / ref2.norm()) < 1e-2
+
+
+@torch.no_grad()
 def test_processor_surfaces_a_wait_that_gave_up(setup):
     """Every launch of a processor carries the processor's own status word.  A bounded wait that runs out (made to
     run out here with the library's self-test, on that very word) is raised by check_status() as H3A_ERR_TIMEOUT,
