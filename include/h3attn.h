@@ -193,6 +193,10 @@ typedef struct h3a_head_scatter {
   int32_t head0;          /* global index of the input's first head */
   int32_t row_offset;     /* this shard's first token in the full sequence */
   int32_t L_total;        /* tokens of the full sequence */
+  int32_t start_head;     /* the launch walks the input's heads in the order start_head, start_head + 1, ... (wrapping).
+                             Results do not depend on it; give every rank a different start (the first head of the NEXT
+                             rank's block, say): with the same order everywhere all ranks would store to the same owner
+                             at the same time and share that one GPU's inbound NVLink bandwidth. */
 } h3a_head_scatter;
 int32_t h3a_qk_prep_scatter(const h3a_prep_params* p, const h3a_head_scatter* q_to, const h3a_head_scatter* k_to, void* stream);
 

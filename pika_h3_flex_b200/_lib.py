@@ -10,7 +10,8 @@ import os
 from typing import Optional
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libh3attn.so")
+# H3A_LIBRARY names another build of the library (for example one compiled with different tuning macros)
+LIB_PATH = os.environ.get("H3A_LIBRARY") or os.path.join(_HERE, "libh3attn.so")
 
 # status codes / enums (mirror include/h3attn.h)
 H3A_OK = 0
@@ -71,7 +72,7 @@ class AttnParams(C.Structure):
 class HeadScatter(C.Structure):
     _fields_ = [
         ("base", C.c_void_p * MAX_RANKS), ("n_ranks", C.c_int32), ("heads_per_rank", C.c_int32), ("round_robin", C.c_int32),
-        ("head0", C.c_int32), ("row_offset", C.c_int32), ("L_total", C.c_int32),
+        ("head0", C.c_int32), ("row_offset", C.c_int32), ("L_total", C.c_int32), ("start_head", C.c_int32),
     ]
 
 

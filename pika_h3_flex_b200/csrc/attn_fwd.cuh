@@ -66,6 +66,63 @@ constexpr int kPolyPairsBf16 = H3A_POLY_PAIRS;  // of every 4 element pairs, how
 #endif
 constexpr int kPolyPairsFp8 = H3A_POLY_FP8;    // FP8 mode has its own share: its S MMAs are cheaper, the balance differs
 
+// Of every 4 element pairs of an FP8-QK tile, how many take the packed-bf16 exponential (one MUFU operation for two
+// elements, its row-sum share accumulated in bf16 over 8 pairs at a time).  FP8-QK is bound by the MUFU; its error
+// budget (e4m3 operands) is an order of magnitude above what the bf16-rounded argument adds.
+#ifndef H3A_BF16X2_FP8
+#define H3A_BF16X2_FP8 0
+#endif
+#ifndef H3A_BF16X2_BF16
+#define H3A_BF16X2_BF16 0
+#endif
+constexpr int kPackedExpFp8 = H3A_BF16X2_FP8, kPackedExpBf16 = H3A_BF16X2_BF16;
+
+// P = 2^(s c - m) for the 64 logits in s[] (one half tile, one row per thread): the packed bf16 results replace
+// s[0..31]; returns the row-sum share.  Pair i uses, by (i & 3): the packed-bf16 MUFU path, the FMA-pipe polynomial,
+// or two fp32 MUFU operations.
+template <bool kFp8>
+__device__ __forceinline__ float exp_half_tile(uint32_t (&s)[64], float c, float m_ref) {
+  constexpr int kPacked = kFp8 ? kPackedExpFp8 : kPackedExpBf16;
+  constexpr int kPoly = kFp8 ? kPolyPairsFp8 : kPolyPairsBf16;
+  uint64_t acc0 = 0, acc1 = 0;  // two packed accumulators = four partial row sums (bit pattern 0 == 0.0f)
+  uint32_t accb[4] = {0u, 0u, 0u, 0u};
+  const uint64_t c2 = pack2(c, c), nm2 = pack2(-m_ref, -m_ref);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const uint64_t x = fma2(pack2u(s[2 * i], s[2 * i + 1]), c2, nm2);
+    if ((i & 3) < kPacked) {
+      float x0, x1;
+      unpack2(x, x0, x1);
+      const uint32_t pb = ex2_bf16x2(pack_bf16x2(x0, x1));
+      accb[i >> 3] = add_bf16x2(accb[i >> 3], pb);
+      s[i] = pb;
+      continue;
+    }
+    uint64_t pp;
+    if ((i & 3) < kPacked + kPoly) {
+      pp = exp2_poly2(x);
+    } else {
+      float x0, x1;
+      unpack2(x, x0, x1);
+      pp = pack2(ex2_approx(x0), ex2_approx(x1));
+    }
+    if (i & 1) acc1 = add2(acc1, pp);
+    else acc0 = add2(acc0, pp);
+    float p0, p1;
+    unpack2(pp, p0, p1);
+    s[i] = pack_bf16x2(p0, p1);  // slot i <= 2i: already consumed
+  }
+  float a0, a1, a2, a3;
+  unpack2(acc0, a0, a1);
+  unpack2(acc1, a2, a3);
+  float l = (a0 + a1) + (a2 + a3);
+  if constexpr (kPacked > 0) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) l += __uint_as_float(accb[g] << 16) + __uint_as_float(accb[g] & 0xFFFF0000u);
+  }
+  return l;
+}
+
 struct AttnBars {
   uint64_t kv_full[kStages];
   uint64_t kv_empty[kStages];
@@ -159,11 +216,19 @@ __device__ __forceinline__ void st_shared_u32_volatile(uint32_t addr, uint32_t v
   asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
+// H3A_WAIT_SLEEP_NS > 0: a waiting thread sleeps that long between polls (fewer issue slots and less power spent on
+// polling, at the price of a later wake-up).
+#ifndef H3A_WAIT_SLEEP_NS
+#define H3A_WAIT_SLEEP_NS 0
+#endif
 __device__ __forceinline__ bool bounded_wait(const WaitCtx& c, uint32_t bar, uint32_t parity, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   uint32_t polls = 0;
   uint64_t t0 = 0;
   while (!mbar_try_wait(bar, parity)) {
+#if H3A_WAIT_SLEEP_NS > 0
+    __nanosleep(H3A_WAIT_SLEEP_NS);
+#endif
     if ((++polls & 63u) == 0u) {
       if (ld_shared_u32_volatile(c.abort_smem)) return false;
       uint64_t now = global_timer_ns();
@@ -560,29 +625,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int i = 0; i < 64; ++i)
           if (i >= valid) s[i] = 0xFF800000u;  // -inf
       }
-      uint64_t acc0 = 0, acc1 = 0;
-      const uint64_t c2 = pack2(c, c), nm2 = pack2(-m_ref, -m_ref);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const uint64_t x = fma2(pack2u(s[2 * i], s[2 * i + 1]), c2, nm2);
-        uint64_t pp;
-        if ((i & 3) < (kFp8 ? kPolyPairsFp8 : kPolyPairsBf16)) {
-          pp = exp2_poly2(x);
-        } else {
-          float x0, x1;
-          unpack2(x, x0, x1);
-          pp = pack2(ex2_approx(x0), ex2_approx(x1));
-        }
-        if (i & 1) acc1 = add2(acc1, pp);
-        else acc0 = add2(acc0, pp);
-        float p0, p1;
-        unpack2(pp, p0, p1);
-        s[i] = pack_bf16x2(p0, p1);
-      }
-      float a0, a1, a2, a3;
-      unpack2(acc0, a0, a1);
-      unpack2(acc1, a2, a3);
-      l_sum += (a0 + a1) + (a2 + a3);
+      l_sum += exp_half_tile<kFp8>(s, c, m_ref);
       if (row == 0 && t == 0) H3A_STAMP(hf, j, 4);
       tmem_st32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_wait_st();
@@ -734,31 +777,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       }
-      // p = 2^(s c - m): scale-and-subtract as packed FFMA2; of every 4 pairs, kPolyPairs take the
-      // FMA-pipe polynomial and the rest the MUFU, so neither unit carries the whole tile
-      uint64_t acc0 = 0, acc1 = 0;  // two packed accumulators = four partial row sums (bit pattern 0 == 0.0f)
-      const uint64_t c2 = pack2(c, c), nm2 = pack2(-m_ref, -m_ref);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const uint64_t x = fma2(pack2u(s[2 * i], s[2 * i + 1]), c2, nm2);
-        uint64_t pp;
-        if ((i & 3) < (kFp8 ? kPolyPairsFp8 : kPolyPairsBf16)) {
-          pp = exp2_poly2(x);
-        } else {
-          float x0, x1;
-          unpack2(x, x0, x1);
-          pp = pack2(ex2_approx(x0), ex2_approx(x1));
-        }
-        if (i & 1) acc1 = add2(acc1, pp);
-        else acc0 = add2(acc0, pp);
-        float p0, p1;
-        unpack2(pp, p0, p1);
-        s[i] = pack_bf16x2(p0, p1);  // slot i <= 2i: already consumed
-      }
-      float a0, a1, a2, a3;
-      unpack2(acc0, a0, a1);
-      unpack2(acc1, a2, a3);
-      l_sum += (a0 + a1) + (a2 + a3);
+      // p = 2^(s c - m): scale-and-subtract as packed FFMA2, exponentials spread over the MUFU and the FMA pipe
+      l_sum += exp_half_tile<kFp8>(s, c, m_ref);
       return true;
     };
     // publish P[t][hf] (packed in s[0..31]) to TMEM and tell the issuer

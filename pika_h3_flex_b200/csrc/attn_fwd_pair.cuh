@@ -504,29 +504,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         for (int i = 0; i < 64; ++i)
           if (i >= valid) s[i] = 0xFF800000u;  // -inf
       }
-      uint64_t acc0 = 0, acc1 = 0;
-      const uint64_t c2 = pack2(c, c), nm2 = pack2(-m_ref, -m_ref);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const uint64_t x = fma2(pack2u(s[2 * i], s[2 * i + 1]), c2, nm2);
-        uint64_t pp;
-        if ((i & 3) < (kFp8 ? kPolyPairsFp8 : kPolyPairsBf16)) {
-          pp = exp2_poly2(x);
-        } else {
-          float x0, x1;
-          unpack2(x, x0, x1);
-          pp = pack2(ex2_approx(x0), ex2_approx(x1));
-        }
-        if (i & 1) acc1 = add2(acc1, pp);
-        else acc0 = add2(acc0, pp);
-        float p0, p1;
-        unpack2(pp, p0, p1);
-        s[i] = pack_bf16x2(p0, p1);
-      }
-      float a0, a1, a2, a3;
-      unpack2(acc0, a0, a1);
-      unpack2(acc1, a2, a3);
-      l_sum += (a0 + a1) + (a2 + a3);
+      l_sum += exp_half_tile<kFp8>(s, c, m_ref);
       if (row == 0 && t == 0) H3A_STAMP(hf, j, 4);
       tmem_st32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_wait_st();
@@ -682,29 +660,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
         }
       }
-      uint64_t acc0 = 0, acc1 = 0;
-      const uint64_t c2 = pack2(c, c), nm2 = pack2(-m_ref, -m_ref);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const uint64_t x = fma2(pack2u(s[2 * i], s[2 * i + 1]), c2, nm2);
-        uint64_t pp;
-        if ((i & 3) < (kFp8 ? kPolyPairsFp8 : kPolyPairsBf16)) {
-          pp = exp2_poly2(x);
-        } else {
-          float x0, x1;
-          unpack2(x, x0, x1);
-          pp = pack2(ex2_approx(x0), ex2_approx(x1));
-        }
-        if (i & 1) acc1 = add2(acc1, pp);
-        else acc0 = add2(acc0, pp);
-        float p0, p1;
-        unpack2(pp, p0, p1);
-        s[i] = pack_bf16x2(p0, p1);
-      }
-      float a0, a1, a2, a3;
-      unpack2(acc0, a0, a1);
-      unpack2(acc1, a2, a3);
-      l_sum += (a0 + a1) + (a2 + a3);
+      l_sum += exp_half_tile<kFp8>(s, c, m_ref);
       return true;
     };
     auto publish_p = [&](uint32_t (&s)[64], int hf) {

@@ -143,6 +143,31 @@ constexpr float kMaxLogitBound = 60.f;
 bool fixed_reference_ok(float bound) { return bound > 0.f && bound <= kMaxLogitBound; }
 float fixed_reference(float bound) { return bound <= 30.f ? bound : kMaxLogitBound - bound; }
 
+// H3A_SCATTER_BULK=0 in the environment (read once) makes h3a_qk_prep_scatter store rows with ordinary 16-byte
+// stores instead of one bulk copy per 128-row tile, for side-by-side measurements.
+bool scatter_bulk_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("H3A_SCATTER_BULK");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
+
+// Column tiles per band of the projection's tile order: the band's rows of W (256 x (K + R) bf16 per column tile)
+// should stay resident in L2 next to the X and output streams: about 16 MB.  H3A_PROJ_BAND in the environment (read
+// once) overrides the choice, for measurements.
+int proj_band_tiles(int n_tiles_n, int k_total) {
+  static const int forced = [] {
+    const char* e = std::getenv("H3A_PROJ_BAND");
+    return e ? std::atoi(e) : 0;
+  }();
+  if (forced > 0) return std::min(forced, n_tiles_n);
+  const long long per_tile = 256ll * k_total * 2;
+  const int fit = static_cast<int>(std::max(1ll, (16ll << 20) / std::max(1ll, per_tile)));
+  const int n_bands = (n_tiles_n + fit - 1) / fit;
+  return (n_tiles_n + n_bands - 1) / n_bands;
+}
+
 bool pair_kernel_enabled() {
   static const bool on = [] {
     const char* e = std::getenv("H3A_PAIR");
@@ -390,6 +415,7 @@ int32_t prep_impl(const h3a_prep_params* p, const h3a_head_scatter* q_to, const 
       }
       a.n_ranks = to->n_ranks; a.heads_per_rank = to->heads_per_rank; a.round_robin = to->round_robin != 0;
       a.head0 = to->head0; a.row_offset = to->row_offset; a.L_total = to->L_total;
+      a.head_rot = to->start_head > 0 ? to->start_head % a.H : 0;
       a.out = to->base[0];
     }
     if (!a.out || (fp8 && !a.scale)) return H3A_ERR_ARG;
@@ -398,6 +424,7 @@ int32_t prep_impl(const h3a_prep_params* p, const h3a_head_scatter* q_to, const 
     a.nblk = (a.L + 127) / 128;
     dim3 grid(a.nblk, a.H);
     if (fp8) h3a::qk_prep_kernel<true><<<grid, h3a::kPrepThreads, 0, st>>>(a);
+    else if (scatter && scatter_bulk_enabled()) h3a::qk_prep_kernel<false, true><<<grid, h3a::kPrepThreads, 0, st>>>(a);
     else h3a::qk_prep_kernel<false><<<grid, h3a::kPrepThreads, 0, st>>>(a);
     if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
   }
@@ -684,7 +711,9 @@ int32_t h3a_proj_fwd(const h3a_proj_params* p, void* stream) {
     attr_err[dev] = cudaFuncSetAttribute(h3a::qkv_proj_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, h3a::kProjSmemBytes);
   });
   if (attr_err[dev] != cudaSuccess) return H3A_ERR_LAUNCH;
-  a.n_tiles = ((p->L + 255) / 256) * a.n_tiles_n;
+  a.n_tiles_m = (p->L + 255) / 256;
+  a.n_tiles = a.n_tiles_m * a.n_tiles_n;
+  a.band_n = proj_band_tiles(a.n_tiles_n, p->K + p->R);
   const int sms = sm_count_of_current_device();
   const unsigned pairs = static_cast<unsigned>(std::min(a.n_tiles, std::max(1, sms / 2)));  // persistent: one pair per two SMs
   h3a::qkv_proj_kernel<<<2u * pairs, h3a::kProjThreads, h3a::kProjSmemBytes, st>>>(mx, mw, mt, mb, a);

@@ -26,6 +26,7 @@ struct PrepArgs {
   // [heads_per_rank, L_total, 128] buffer (own memory or a peer GPU's), token l at row row_offset + l.
   void* rank_out[8];
   int n_ranks, heads_per_rank, round_robin, head0, row_offset, L_total;
+  int head_rot;         // the grid's y index is rotated by this many heads (order of the stores, not their content)
 };
 
 // where row l of (local) head `head` is written: head-major in `out`, or at the head's owner
@@ -42,12 +43,17 @@ __device__ __forceinline__ __nv_bfloat16* prep_dst_bf16(const PrepArgs& a, int h
 // One CTA = one (128-token block, head).  Thread (r = tid/8, sub = tid%8) owns, in each of 4 passes,
 // the two 8-element chunks [8*sub, 8*sub+8) and [64+8*sub, 64+8*sub+8) of row pass*32 + r, so that both
 // rotary pair conventions stay inside a thread and a row's sum of squares is an 8-lane shuffle.
-template <bool kFp8>
+// kBulk (scatter mode, bf16): the CTA's 128 prepared rows are contiguous at their owner (32 KB), so they are staged in
+// shared memory and leave as ONE bulk asynchronous copy (cp.async.bulk, shared -> global) instead of 16-byte stores:
+// large transfers are what NVLink moves best when the owner is another GPU.  The destination is only written.
+template <bool kFp8, bool kBulk = false>
 __global__ void __launch_bounds__(kPrepThreads) qk_prep_kernel(const PrepArgs a) {
-  const int blk = blockIdx.x, head = blockIdx.y;
+  const int blk = blockIdx.x;
+  const int head = a.head_rot ? static_cast<int>((blockIdx.y + a.head_rot) % a.H) : static_cast<int>(blockIdx.y);
   const int tid = threadIdx.x;
   const int r = tid >> 3, sub = tid & 7;
   __shared__ float warp_max[kPrepThreads / 32];
+  __shared__ __align__(128) __nv_bfloat16 stage[kBulk ? 128 * 128 : 8];
 
   float w_lo[8], w_hi[8];
 #pragma unroll
@@ -137,7 +143,7 @@ __global__ void __launch_bounds__(kPrepThreads) qk_prep_kernel(const PrepArgs a)
         amax = fmaxf(amax, fmaxf(fabsf(x_lo[x]), fabsf(x_hi[x])));
       }
     } else if (valid) {
-      __nv_bfloat16* dst = prep_dst_bf16(a, head, l);
+      __nv_bfloat16* dst = kBulk ? stage + (pass * 32 + r) * 128 : prep_dst_bf16(a, head, l);
       uint4 o0, o1;
       __nv_bfloat162* p0 = reinterpret_cast<__nv_bfloat162*>(&o0);
       __nv_bfloat162* p1 = reinterpret_cast<__nv_bfloat162*>(&o1);
@@ -181,6 +187,18 @@ __global__ void __launch_bounds__(kPrepThreads) qk_prep_kernel(const PrepArgs a)
         *reinterpret_cast<uint2*>(dst + 8 * sub) = make_uint2(w[0], w[1]);
         *reinterpret_cast<uint2*>(dst + 64 + 8 * sub) = make_uint2(w[2], w[3]);
       }
+    }
+  }
+  if constexpr (kBulk) {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the staged rows, written by ordinary stores, are read by the copy engine
+    __syncthreads();
+    if (tid == 0) {
+      const int rows = min(128, a.L - blk * 128);
+      const unsigned long long dst = reinterpret_cast<unsigned long long>(prep_dst_bf16(a, head, blk * 128));
+      const uint32_t src = static_cast<uint32_t>(__cvta_generic_to_shared(stage));
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(rows * 256) : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // complete (not only read) before the CTA may leave
     }
   }
   if (a.n_ranks > 1) __threadfence_system();  // rows stored into other GPUs' memory: ordered before this kernel's completion is observed

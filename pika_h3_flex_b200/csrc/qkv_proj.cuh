@@ -54,6 +54,7 @@ static_assert(sizeof(ProjBars) <= 256, "barrier block too large");
 struct ProjArgs {
   AttnArgs wait;               // only .status and .wait_ns are used (bounded waits)
   int L, N, n_tiles_n, n_tiles; // tokens, output columns, 256-column tiles per token tile, all tiles
+  int band_n, n_tiles_m;       // column tiles per band of the tile order (see tile_mn), 256-token tiles
   int kb_main, kb_lora;        // 64-wide steps of the two products
   int epilogue;
   const float* bias;           // [N] or null
@@ -80,9 +81,22 @@ qkv_proj_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  // column tiles fastest: the pairs running together share a few token tiles of X and all of W in L2
-  auto tile_m0 = [&](int tile) { return (tile / args.n_tiles_n) * 256 + static_cast<int>(rank) * 128; };  // this CTA's first token
-  auto tile_n0 = [&](int tile) { return (tile % args.n_tiles_n) * 256; };                                 // the pair's first column
+  // Tile order: the output columns are cut into bands of band_n column tiles; a band is walked over ALL token tiles
+  // (column tiles fastest inside the band) before the next band starts.  The pairs running together then share a few
+  // token tiles of X and one band of W, and that band (band_n x 256 rows of W) is small enough to STAY in L2 from one
+  // wave of tiles to the next; with a single band of all columns W (52 MB at N = K = 5,120) was evicted by the X and
+  // output streams and re-read from DRAM by every wave.  X is read once per band instead of once.
+  auto tile_mn = [&](int tile, int& mt, int& nt) {
+    const int per_band = args.band_n * args.n_tiles_m;
+    const int n_bands = (args.n_tiles_n + args.band_n - 1) / args.band_n;
+    const int b = min(tile / per_band, n_bands - 1);
+    const int r = tile - b * per_band;
+    const int bw = (b == n_bands - 1) ? args.n_tiles_n - b * args.band_n : args.band_n;
+    mt = r / bw;
+    nt = b * args.band_n + r % bw;
+  };
+  auto tile_m0 = [&](int tile) { int mt, nt; tile_mn(tile, mt, nt); return mt * 256 + static_cast<int>(rank) * 128; };  // this CTA's first token
+  auto tile_n0 = [&](int tile) { int mt, nt; tile_mn(tile, mt, nt); return nt * 256; };                                 // the pair's first column
   const int n_kb = args.kb_main + args.kb_lora;
 
   if (threadIdx.x == 0) {

@@ -228,7 +228,9 @@ class HostUlyssesAttention:
             j0 += n
 
         def owners(name, h0):
-            return ops.HeadOwners([self.arena.addr(p, self._off[name]) for p in range(P)], self.hp, True, rank * Ls, L, head0=h0)
+            # round robin: consecutive heads already go to consecutive ranks; each rank starts one head further
+            return ops.HeadOwners([self.arena.addr(p, self._off[name]) for p in range(P)], self.hp, True, rank * Ls, L, head0=h0,
+                                  start_head=rank + 1)
 
         def stage_in(g):
             """Scatter stream: prepare group g's heads of this rank's tokens into their owners' memory, then meet."""

@@ -64,6 +64,7 @@ class HeadOwners:
     row_offset: int
     L_total: int
     head0: int = 0
+    start_head: int = 0  # order in which the launch walks the heads (see h3a_head_scatter.start_head): differs per rank
 
     def c_struct(self):
         s = _lib.HeadScatter()
@@ -71,6 +72,7 @@ class HeadOwners:
             s.base[r] = b
         s.n_ranks, s.heads_per_rank, s.round_robin = len(self.bases), int(self.heads_per_rank), int(bool(self.round_robin))
         s.head0, s.row_offset, s.L_total = int(self.head0), int(self.row_offset), int(self.L_total)
+        s.start_head = int(self.start_head)
         return s
 
 

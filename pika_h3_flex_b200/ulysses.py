@@ -268,7 +268,11 @@ class UlyssesAttention:
             for n in ("q", "k", "v"):
                 setattr(st, n, st.arena.tensor(st.off[n], (st.hp, st.L, ops.HEAD_DIM), torch.bfloat16))
             st.o = st.arena.tensor(st.off["o"], (Ls, H, ops.HEAD_DIM), torch.bfloat16)
-            st.owners = {n: ops.HeadOwners([st.arena.addr(p, st.off[n]) for p in range(world)], st.hp, False, rank * Ls, st.L)
+            # every rank starts with the heads of the rank after it and ends with its own: at any moment the ranks
+            # store to different owners instead of all to the same one
+            start = ((rank + 1) % world) * st.hp % H
+            st.owners = {n: ops.HeadOwners([st.arena.addr(p, st.off[n]) for p in range(world)], st.hp, False, rank * Ls, st.L,
+                                           start_head=start)
                          for n in ("q", "k", "v")}
             # output rows of this rank's heads (global heads rank * hp ...) go to the rank that holds the token
             st.out_ranks = ops.RankOutputs([st.arena.addr(t, st.off["o"]) + rank * st.hp * ops.HEAD_DIM * 2 for t in range(world)],

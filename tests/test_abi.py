@@ -39,7 +39,7 @@ def test_version_and_status_strings(lib):
 def test_struct_sizes_match_header(lib):
     # natural-alignment sizes of the two parameter structs as a C compiler lays them out
     assert C.sizeof(_lib.AttnParams) == 216 + 8 * 8 + 8  # + the per-rank output bases of the sequence-parallel return trip
-    assert C.sizeof(_lib.HeadScatter) == 8 * 8 + 6 * 4
+    assert C.sizeof(_lib.HeadScatter) == 8 * 8 + 8 * 4  # seven int32 fields, padded to the pointers' alignment
     assert C.sizeof(_lib.PrepParams) == 144
     assert C.sizeof(_lib.ProjParams) == 168
     assert C.sizeof(_lib.AdaLnParams) == 112

@@ -45,7 +45,7 @@ def test_prepared_rows_land_at_their_heads_owner(h, P, H, round_robin, half):
         for h0, h1 in ((0, cut), (cut, H)):
             if h1 <= h0:
                 continue
-            to = ops.HeadOwners([b.data_ptr() for b in bufs], hp, round_robin, r * Ls, L, head0=h0)
+            to = ops.HeadOwners([b.data_ptr() for b in bufs], hp, round_robin, r * Ls, L, head0=h0, start_head=r + 1)  # any order of the heads
             ops.prep_scatter(x[sl, h0:h1], to, tab[sl].contiguous(), w, rope_half=half)
             tov = ops.HeadOwners([b.data_ptr() for b in bufs_v], hp, round_robin, r * Ls, L, head0=h0)
             ops.prep_scatter(x[sl, h0:h1], tov, no_norm=True)
