@@ -449,6 +449,89 @@ def roofline_of(c, attn_ms, online_max, world=1):
     return r
 
 
+def ulysses_with_projections(c, ua, dev, world, rank, barrier, rank_max, steps=5):
+    """N > 1: one attention block's Q/K/V projections (LoRA rank 128, model width H * 128) feeding the sequence-parallel
+    attention.  Two forms of the same step: `fused_scatter` - the projection GEMM's epilogue normalises, rotates and
+    stores every row straight at its head's owning rank (no separate outbound pass); `separate_scatter` - the same
+    GEMMs store locally and the re-layout to the owners is a pass of its own.  Parity: sampled output rows against
+    the fp64 oracle on operands projected in fp32 (torch on the GPU, TF32 off) for two heads."""
+    import pika_h3_flex_b200 as h3
+    from oracle import oracle as O
+
+    H, Ls, L = c.H, c.Ls, c.L
+    D, R = H * 128, 128
+    g = torch.Generator(device=dev).manual_seed(3001)
+    x_full = torch.randn(L, D, device=dev, generator=g).bfloat16()
+    ws = [(torch.randn(D, D, device=dev, generator=g) / D ** 0.5).bfloat16() for _ in range(3)]
+    las = [(torch.randn(R, D, device=dev, generator=g) / D ** 0.5).bfloat16() for _ in range(3)]
+    lbs = [(0.5 * torch.randn(D, R, device=dev, generator=g) / R ** 0.5).bfloat16() for _ in range(3)]
+    x = x_full[c.lo : c.lo + Ls].contiguous()
+    status = ua.status.tensor(x)
+
+    def proj(i, out_to=None):
+        t = torch.nn.functional.linear(x, las[i])  # the thin LoRA product x A^T (torch / cuBLAS)
+        return h3.proj_fwd(x, ws[i], None, t, lbs[i], prep=(i < 2), rope=c.rope if i < 2 else None, status_word=status, out_to=out_to)
+
+    def fused():
+        return ua.run_scattered(Ls, H, dev, lambda to: proj(0, to), lambda to: proj(1, to), lambda to: proj(2, to), c.bound)
+
+    def separate():
+        return ua.run(lambda: proj(0), lambda: proj(1), lambda: proj(2), None, logit_bound=c.bound, prepared=True)
+
+    def time_of(fn):
+        for _ in range(3):
+            fn()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            out = fn()
+        b.record()
+        barrier()
+        return rank_max(a.elapsed_time(b)) / steps, out
+
+    ms_fused, out = time_of(fused)
+    out = out.clone()
+    ms_sep, _ = time_of(separate)
+    # projections alone (local head-major store), for the split of the step
+    def only_proj():
+        for i in range(3):
+            proj(i)
+    ms_proj, _ = time_of(only_proj)
+    ua.status.check("ulysses_with_projections")
+    # parity: two heads, projections in fp32 on the GPU, the rest by the fp64 oracle
+    hs = c.heads
+    cols = torch.cat([torch.arange(h * 128, (h + 1) * 128) for h in hs]).to(dev)
+    rows = sample_rows(c)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+
+    def ref_proj(i, xr):
+        y = xr.float() @ ws[i][cols].float().t() + (xr.float() @ las[i].float().t()).bfloat16().float() @ lbs[i][cols].float().t()
+        return y.view(-1, len(hs), 128).cpu().double()
+
+    q = ref_proj(0, x_full[rows.to(dev)])
+    k, v = ref_proj(1, x_full), ref_proj(2, x_full)
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    cos, sin = O.rope_table(c.pos.double())
+    qn = O.apply_rope(O.rms_norm(q), cos[rows], sin[rows])
+    kn = O.apply_rope(O.rms_norm(k), cos, sin)
+    ref = O.attention(qn, kn, v.bfloat16().double(), chunk=64)
+    st = O.error_stats(out[rows - c.lo][:, hs].float().cpu(), ref.float())
+    ok = st["max_abs"] <= 2e-2 and st["mean_abs"] <= 2e-3 and st["rel_l2"] <= 2e-2
+    t = torch.tensor([st["max_abs"], st["mean_abs"], st["rel_l2"], 0.0 if ok else 1.0], device=dev, dtype=torch.float64)
+    import torch.distributed as dist
+
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    flops = 3 * 2.0 * L * D * (D + R) + 3 * 2.0 * L * D * R + c.flops
+    return {"workload": "ulysses_with_projections", "ms_per_step": ms_fused, "ms_separate_scatter": ms_sep, "projections_only_ms": ms_proj,
+            "value": flops / (ms_fused * 1e-3) / 1e12, "unit": "TFLOP/s (projections + attention, whole job)", "steps": steps,
+            "step": "to_q, to_k, to_v (LoRA rank 128; RMSNorm + rotation and the store at the head's owner in the GEMM epilogue), attention, output rows stored at the token's owner",
+            "parity": {"ok": bool(t[3].item() == 0.0), "max_abs": float(t[0]), "mean_abs": float(t[1]), "rel_l2": float(t[2]), "rows": int(rows.numel()) * world,
+                       "bounds": {"max_abs": 2e-2, "mean_abs": 2e-3, "rel_l2": 2e-2},
+                       "against": "fp64 oracle attention on operands projected in fp32 (torch, TF32 off) for two heads; worst rank"}}
+
+
 def run_also(name, dev, online_max=False):
     """A short run (3 warm-up + 5 timed steps) of another configuration on this GPU, with its parity verdict."""
     import pika_h3_flex_b200 as h3
@@ -555,7 +638,7 @@ def run_ours(args):
     status.check("timed region")
     # ---- the same steps continued for about two seconds (every rank alike), timed again, with the clock record of
     #      exactly this stretch: nvidia-smi delivers a sample every 200 ms, and the power cap needs a second to bite
-    n_sus = max(args.steps, int(2000.0 / max(ms_per_step, 1e-3)) + 1)
+    n_sus = 0 if args.lean else max(args.steps, int(2000.0 / max(ms_per_step, 1e-3)) + 1)
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     m2 = sampler.mark()
     s0.record()
@@ -564,13 +647,13 @@ def run_ours(args):
     s1.record()
     barrier()
     m3 = sampler.mark()
-    ms_sustained = rank_max(s0.elapsed_time(s1)) / n_sus
+    ms_sustained = rank_max(s0.elapsed_time(s1)) / n_sus if n_sus else None
     clocks = clocks_sus = None
     if rank == 0:
         sampler.stop()
         clocks = sampler.summary(m0, m1)
         clocks_sus = sampler.summary(m2, m3)
-        if clocks["samples"] < 3:  # a short timed region holds too few samples: report the record of the whole run
+        if clocks["samples"] < 3 and n_sus:  # a short timed region holds too few samples: report the record of the whole run
             clocks = sampler.summary(m0, m3)
             clocks["note"] = f"timed region {ms_per_step * args.steps:.0f} ms: the record also covers the {n_sus} identical steps that followed"
     value = c.flops / (ms_per_step * 1e-3) / 1e12
@@ -592,9 +675,9 @@ def run_ours(args):
     # ---- end to end from host buffers through the public call
     e2e = None
     nbytes = L * H * 128 * 2  # over all ranks
-    if c.cross:
+    if c.cross or args.lean:
         e2e = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-               "note": "host-buffer end-to-end is measured on the self-attention workloads"}
+               "note": "host-buffer end-to-end is measured on the self-attention workloads" if c.cross else "skipped (--lean)"}
     else:
         try:
             hq, hk, hv = (torch.empty(Ls, H, 128, dtype=torch.bfloat16).pin_memory() for _ in range(3))
@@ -659,6 +742,11 @@ def run_ours(args):
         except (RuntimeError, ValueError) as exc:
             also.append({"workload": "cfg1_dense_online_max", "error": repr(exc)})
 
+    if world > 1 and not args.no_also and name == "cfg1_dense" and ua.transport == "peer":
+        try:
+            also = [ulysses_with_projections(c, ua, dev, world, rank, barrier, rank_max)]
+        except (RuntimeError, ValueError) as exc:
+            also = [{"workload": "ulysses_with_projections", "error": repr(exc)}]
     if world > 1:
         dist.barrier()
     if rank == 0:
@@ -678,7 +766,7 @@ def run_ours(args):
                        "l2": "inputs (Q,K,V = %.0f MB per rank) exceed the 126 MB L2; no flush" % (3 * Ls * H * 256 / 1e6)},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks, "parity": parity,
             "ms_per_step_sustained": ms_sustained, "sustained_steps": n_sus, "clocks_sustained": clocks_sus,
-            "ms_x_mhz": None if not sm else ms_sustained * sm,
+            "ms_x_mhz": None if not (sm and ms_sustained) else ms_sustained * sm,
             "prep_ms": prep_ms, "exchange_ms_exposed": None if world == 1 else ms_per_step - prep_ms - attn_ms,
             "gpu_launches": launches_per_step * args.steps,
             "attn_ms_per_dit_step_per_layer": ms_per_step,
@@ -874,11 +962,15 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of the cpu_baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="N = 1: skip the short runs of the other configurations")
+    ap.add_argument("--lean", action="store_true", help="for profiler captures: warm-up and timed steps only (no sustained stretch, host-buffer leg, "
+                    "CPU baseline or other configurations)")
     ap.add_argument("--head-groups", type=int, default=2, help="N > 1: head groups the reshard is pipelined over (1 = no overlap)")
     ap.add_argument("--transport", choices=["auto", "peer", "nccl"], default="auto",
                     help="N > 1: how operands are resharded: direct stores into the owning rank's memory (peer) or NCCL all-to-all")
     ap.add_argument("--online-max", action="store_true", help="use the running-maximum kernel instead of the fixed logit bound")
     args = ap.parse_args()
+    if args.lean:
+        args.no_also = args.no_cpu_baseline = True
     if args.workload == "cfg1_adaln":
         if args.impl == "reference" or args.gpus != 1:
             raise SystemExit("the adaptive-layer-norm workload runs on one GPU with --impl ours")

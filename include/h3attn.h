@@ -103,13 +103,16 @@ typedef struct h3a_attn_params {
                              calls of a forward pass and read once at its end; zero it before the first use */
   int64_t wait_limit_ns;  /* bound for each device-side wait; <= 0 selects 2 s */
   float logit_bound;      /* optional: a value B with |q.k| * softmax_scale <= B for every query/key pair (with
-                             QK-RMSNorm: 128 * max|w_q| * max|w_k| * softmax_scale).  When 0 < B <= 60 the kernel
-                             uses a fixed softmax reference (B up to 30, sliding to 0 at B = 60) instead of a running
-                             row maximum: the result is the same softmax (any reference is exact), without the max
-                             pass and without rescaling.  A bound that is somewhat too small only costs range; one that
-                             is wrong enough for a row sum to under- or overflow is reported through the status
-                             word (code 11, H3A_ERR_BOUND) and that launch's output must not be used.
-                             0, or a value above 60 = no usable bound: online softmax with a running row maximum. */
+                             QK-RMSNorm: 128 * max|w_q| * max|w_k| * softmax_scale).  When 0 < B <= 110 the kernel
+                             uses a fixed softmax reference instead of a running row maximum: the result is the same
+                             softmax (any reference is exact while the terms stay inside fp32's range), without the max
+                             pass and without rescaling.  The reference is B up to 30, slides to 0 at B = 60, stays 0 to
+                             B = 74 and is B - 74 beyond.  Up to B = 64 every row of any data within the bound is served;
+                             from there to 110 every row whose largest logit is at least ref - 64 (-64 up to B = 74, then
+                             B - 138: at least one key not extremely anti-aligned with the query).  A row outside that, or data that violates the
+                             bound far enough for a row sum to under- or overflow, is REPORTED through the status word
+                             (code 11, H3A_ERR_BOUND; pass a status word) and that launch's output must not be used.
+                             0, or a value above 110 = no usable bound: online softmax with a running row maximum. */
   int32_t sparse_heavy_pairs; /* BLOCK_SPARSE scheduling hint: the first this-many pairs of query tiles (256 rows
                              each) list far more key tiles than the rest (the dense audio rows of the joint
                              sequence); their CTAs of all heads are started first.  0 = no hint.  Never affects
@@ -319,6 +322,10 @@ typedef struct h3a_proj_params {
   float eps;              /* <= 0 selects 1e-6 */
   int32_t* status_word;   /* as in h3a_attn_params */
   int64_t wait_limit_ns;
+  const struct h3a_head_scatter* out_to; /* optional (H3A_PROJ_STORE / H3A_PROJ_PREP, head-major output): sequence parallelism,
+                             the rows of output head h go straight to the rank that computes head out_to->head0 + h
+                             (see h3a_qk_prep_scatter) instead of to `out`, which is then ignored; L is this rank's
+                             token shard.  The projection's epilogue is then also the outbound trip of the reshard. */
 } h3a_proj_params;
 int32_t h3a_proj_fwd(const h3a_proj_params* p, void* stream);
 

@@ -95,7 +95,7 @@ class ProjParams(C.Structure):
         ("out_stride_l", C.c_int64), ("out_stride_h", C.c_int64),
         ("L", C.c_int32), ("K", C.c_int32), ("N", C.c_int32), ("R", C.c_int32),
         ("epilogue", C.c_int32), ("rope_mode", C.c_int32), ("eps", C.c_float),
-        ("status_word", C.c_void_p), ("wait_limit_ns", C.c_int64),
+        ("status_word", C.c_void_p), ("wait_limit_ns", C.c_int64), ("out_to", C.c_void_p),
     ]
 
 

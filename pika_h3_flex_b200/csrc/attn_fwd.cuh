@@ -283,12 +283,16 @@ __global__ void wait_selftest_kernel(const AttnArgs args) {
 // kBadBlockIndex | offending query tile << 8: the attention launch that follows then does nothing, exactly as
 // after a wait that gave up.  Without a status word the launch runs on the entries that passed.
 constexpr int kBadBlockIndex = 10;
-// Fixed-reference kernels: a row whose exponentials all underflowed, or overflowed, shows in its row sum (0, inf or
-// NaN).  That can only happen when the caller's logit bound does not hold for the data; it is reported through the
-// status word (once) as kBadLogitBound | CTA << 8 and the stored rows are not to be used.
+// Fixed-reference kernels: a row whose exponentials overflowed, or whose largest term fell below the range the
+// reference serves, shows in its row sum: inf / NaN, or less than 2^-100 (a served row's sum is at least its largest
+// term, 2^-92 or more; a sum of nothing but flushed or clamped terms stays below 2^-109).  That happens when the
+// caller's logit bound does not hold for the data, or (bounds above 69) for a row whose logits all lie far below
+// the bound; it is reported through the status word (once) as kBadLogitBound | CTA << 8 and the launch's output is
+// not to be used.  `zero_is_legal`: an exact zero is a block-sparse row that lists no key tile (or one share of a
+// split row).
 constexpr int kBadLogitBound = 11;
 __device__ __forceinline__ void check_row_sum(const AttnArgs& a, float l, bool zero_is_legal) {
-  const bool bad = !(l < 3.0e38f) || (!zero_is_legal && !(l > 0.0f));  // NaN fails both comparisons
+  const bool bad = !(l < 3.0e38f) || (!(l > 7.8e-31f) && !(zero_is_legal && l == 0.0f));  // NaN fails every comparison
   if (bad && a.status) atomicCAS(a.status, 0, kBadLogitBound | (static_cast<int>(blockIdx.x & 0x7FFFFF) << 8));
 }
 __device__ __forceinline__ int clamp_row_ptr(int v, int nnz) { return max(0, min(v, nnz)); }

@@ -139,9 +139,26 @@ int32_t launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
 constexpr int kPairMinKeyTiles = 16;
 constexpr double kPairMinDensity = 0.12;
 
-constexpr float kMaxLogitBound = 60.f;
+// Fixed softmax reference for a stated logit bound B (logits in [-B, B]).  Every term is 2^((s - ref) log2 e) in fp32
+// (bf16 for P: the same exponent range); a row is exact as long as its LARGEST logit satisfies -64 <= s_max - ref <= 74
+// (74: room for the row sum and the P V products below 2^127; -64: the row's own terms stay far above the flush-to-zero
+// threshold and above the floor 2^-125 at which the polynomial exponential clamps).
+//   B <= 30        ref = B        terms <= 1 (the original rule)
+//   30 < B <= 60   ref = 60 - B   slides down to 0
+//   60 < B <= 74   ref = 0
+//   74 < B <= 110  ref = B - 74
+// No data within the bound can overflow.  Every row is served while B <= 64 (its largest logit is at least -B); beyond
+// that, every row whose largest logit is at least ref - 64 (-28 at B = 110); a row below that line shows in its row sum
+// and is REPORTED (H3A_ERR_BOUND), never returned silently.
+// Above 110 the line would cross the logits ordinary rows have: the online (running maximum) kernels are used.
+constexpr float kMaxLogitBound = 110.f;
 bool fixed_reference_ok(float bound) { return bound > 0.f && bound <= kMaxLogitBound; }
-float fixed_reference(float bound) { return bound <= 30.f ? bound : kMaxLogitBound - bound; }
+float fixed_reference(float bound) {
+  if (bound <= 30.f) return bound;
+  if (bound <= 60.f) return 60.f - bound;
+  if (bound <= 74.f) return 0.f;
+  return bound - 74.f;
+}
 
 // H3A_SCATTER_BULK=0 in the environment (read once) makes h3a_qk_prep_scatter store rows with ordinary 16-byte
 // stores instead of one bulk copy per 128-row tile, for side-by-side measurements.
@@ -154,7 +171,7 @@ bool scatter_bulk_enabled() {
 }
 
 // Column tiles per band of the projection's tile order: the band's rows of W (256 x (K + R) bf16 per column tile)
-// should stay resident in L2 next to the X and output streams: about 16 MB.  H3A_PROJ_BAND in the environment (read
+// should stay resident in L2 next to the X and output streams: up to 28 MB (two bands at N = K = 5,120: measured best of 1, 2, 3, 5 and 10 bands).  H3A_PROJ_BAND in the environment (read
 // once) overrides the choice, for measurements.
 int proj_band_tiles(int n_tiles_n, int k_total) {
   static const int forced = [] {
@@ -163,7 +180,7 @@ int proj_band_tiles(int n_tiles_n, int k_total) {
   }();
   if (forced > 0) return std::min(forced, n_tiles_n);
   const long long per_tile = 256ll * k_total * 2;
-  const int fit = static_cast<int>(std::max(1ll, (16ll << 20) / std::max(1ll, per_tile)));
+  const int fit = static_cast<int>(std::max(1ll, (28ll << 20) / std::max(1ll, per_tile)));
   const int n_bands = (n_tiles_n + fit - 1) / fit;
   return (n_tiles_n + n_bands - 1) / n_bands;
 }
@@ -308,10 +325,7 @@ int32_t attn_fwd_impl(const h3a_attn_params* p, void* workspace, size_t workspac
     a.o_rank_rows = p->o_rank_rows;
     for (int r = 0; r < p->o_n_ranks; ++r) a.o_rank[r] = static_cast<__nv_bfloat16*>(p->o_rank_base[r]);
   }
-  // Fixed softmax reference, in log2 units (x softmax_scale is already in the bound).  Logits lie in [-B, B] and every
-  // term 2^((s - ref) log2 e) must stay inside fp32's range with room for the row sum: |s - ref| <= 60.  Up to B = 30
-  // the reference is B itself (terms <= 1); from there to B = 60 it slides down to 0 (ref = 60 - B), which keeps
-  // s - ref within [-60, 60].  Beyond 60 no fixed reference is safe: the running-maximum kernels are used instead.
+  // fixed softmax reference in log2 units (x softmax_scale is already in the bound): see fixed_reference()
   const bool fixed = fixed_reference_ok(p->logit_bound);
   a.fixed_m = fixed ? fixed_reference(p->logit_bound) * 1.4426950408889634f : 0.f;
 
@@ -663,7 +677,7 @@ int32_t h3a_debug_set_trace(void* dev_buffer) {
 #endif
 
 int32_t h3a_proj_fwd(const h3a_proj_params* p, void* stream) {
-  if (!p || !p->x || !p->w || !p->out) return H3A_ERR_ARG;
+  if (!p || !p->x || !p->w || (!p->out && !p->out_to)) return H3A_ERR_ARG;
   if (p->L <= 0 || p->K <= 0 || p->N <= 0 || p->N % 128 != 0 || p->R < 0) return H3A_ERR_SHAPE;
   if (p->epilogue != H3A_PROJ_STORE && p->epilogue != H3A_PROJ_PREP && p->epilogue != H3A_PROJ_PREP_FP8) return H3A_ERR_ARG;
   if (p->epilogue == H3A_PROJ_PREP_FP8 && !p->out_scale) return H3A_ERR_ARG;
@@ -671,7 +685,7 @@ int32_t h3a_proj_fwd(const h3a_proj_params* p, void* stream) {
   const bool lora = p->R > 0;
   if (lora && (!p->lora_t || !p->lora_bs)) return H3A_ERR_ARG;
   const int64_t out_unit = p->epilogue == H3A_PROJ_PREP_FP8 ? 16 : 8;  // 16-byte stores
-  if (!aligned16(p->out) || (p->out_stride_l % out_unit) || (p->out_stride_h % out_unit) || p->out_stride_l <= 0 || p->out_stride_h <= 0) return H3A_ERR_ALIGN;
+  if (!p->out_to && (!aligned16(p->out) || (p->out_stride_l % out_unit) || (p->out_stride_h % out_unit) || p->out_stride_l <= 0 || p->out_stride_h <= 0)) return H3A_ERR_ALIGN;
   if ((p->bias && !aligned16(p->bias)) || (p->rope && !aligned16(p->rope)) || (p->norm_weight && !aligned16(p->norm_weight))) return H3A_ERR_ALIGN;
   int32_t rc = check_arch();
   if (rc != H3A_OK) return rc;
@@ -700,6 +714,21 @@ int32_t h3a_proj_fwd(const h3a_proj_params* p, void* stream) {
   a.rope_half = p->rope_mode == H3A_ROPE_HALF;
   a.out = p->out;
   a.out_stride_l = p->out_stride_l; a.out_stride_h = p->out_stride_h;
+  if (p->out_to) {
+    const h3a_head_scatter* to = p->out_to;
+    if (p->epilogue == H3A_PROJ_PREP_FP8) return H3A_ERR_ARG;  // block scales need whole blocks of the full sequence
+    if (to->n_ranks < 1 || to->n_ranks > H3A_MAX_RANKS || to->heads_per_rank < 1 || to->head0 < 0 || to->row_offset < 0) return H3A_ERR_ARG;
+    if (static_cast<int64_t>(to->row_offset) + p->L > to->L_total) return H3A_ERR_SHAPE;
+    if (static_cast<int64_t>(to->head0) + p->N / 128 > static_cast<int64_t>(to->heads_per_rank) * to->n_ranks) return H3A_ERR_SHAPE;
+    for (int r = 0; r < to->n_ranks; ++r) {
+      if (!to->base[r]) return H3A_ERR_ARG;
+      if (!aligned16(to->base[r])) return H3A_ERR_ALIGN;
+      a.rank_out[r] = to->base[r];
+    }
+    a.n_ranks = to->n_ranks; a.heads_per_rank = to->heads_per_rank; a.round_robin = to->round_robin != 0;
+    a.head0 = to->head0; a.row_offset = to->row_offset; a.L_total = to->L_total;
+    a.col_rot = to->start_head > 0 ? (to->start_head / 2) % ((p->N + 255) / 256) : 0;  // a column tile holds two heads
+  }
   a.out_scale = p->out_scale;
   a.nblk = (p->L + 127) / 128;
 

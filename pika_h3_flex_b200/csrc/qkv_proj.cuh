@@ -66,6 +66,11 @@ struct ProjArgs {
   long long out_stride_l, out_stride_h;
   float* out_scale;            // kProjPrepFp8: [N / 128][nblk] absmax / 448 per (head, 128-token block)
   int nblk;
+  // Sequence parallelism (n_ranks > 0, bf16 epilogues): the row of output head h goes to the rank that computes
+  // head head0 + h, as in PrepArgs (qk_prep.cuh); col_rot rotates the column-tile order so that the ranks do not
+  // all store to the same owner at the same time.
+  void* rank_out[8];
+  int n_ranks, heads_per_rank, round_robin, head0, row_offset, L_total, col_rot;
 };
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kProjThreads, 1)
@@ -94,6 +99,7 @@ qkv_proj_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
     const int bw = (b == n_bands - 1) ? args.n_tiles_n - b * args.band_n : args.band_n;
     mt = r / bw;
     nt = b * args.band_n + r % bw;
+    if (args.col_rot) nt = (nt + args.col_rot) % args.n_tiles_n;
   };
   auto tile_m0 = [&](int tile) { int mt, nt; tile_mn(tile, mt, nt); return mt * 256 + static_cast<int>(rank) * 128; };  // this CTA's first token
   auto tile_n0 = [&](int tile) { int mt, nt; tile_mn(tile, mt, nt); return nt * 256; };                                 // the pair's first column
@@ -306,6 +312,12 @@ qkv_proj_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
         const long long out_off = static_cast<long long>(n_head0 / 128) * args.out_stride_h + static_cast<long long>(l) * args.out_stride_l;
         if (args.epilogue != kProjPrepFp8) {
           __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(args.out) + out_off;
+          if (args.n_ranks > 0) {  // the head's owning rank: its [heads_per_rank, L_total, 128] buffer, token row_offset + l
+            const int h = args.head0 + n_head0 / 128;
+            const int owner = args.round_robin ? h % args.n_ranks : min(h / args.heads_per_rank, args.n_ranks - 1);
+            const int slot = args.round_robin ? h / args.n_ranks : h - owner * args.heads_per_rank;
+            dst = static_cast<__nv_bfloat16*>(args.rank_out[owner]) + (static_cast<long long>(slot) * args.L_total + args.row_offset + l) * 128;
+          }
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
             float lo[32], hi[32];
@@ -382,6 +394,7 @@ qkv_proj_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
   }
 
   // ---- tear-down
+  if (args.n_ranks > 1) __threadfence_system();  // rows stored into other GPUs' memory
   tc_fence_before_sync();
   __syncthreads();
   if (bars->abort_flag) {

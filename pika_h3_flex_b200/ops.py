@@ -373,13 +373,16 @@ def proj_fwd(
     wait_limit_ns: int = 0,
     token_major: bool = False,
     fp8: bool = False,
+    out_to: Optional[HeadOwners] = None,
 ):
     """One of the Q / K / V (or, with ``token_major``, the output) projections through ``h3a_proj_fwd``: ``x [L, K]`` bf16 times ``weight [N, K]`` bf16
     (``nn.Linear`` layout, N = heads x 128), plus ``lora_t [L, R] @ lora_bs [N, R]^T`` and ``bias [N]`` when given;
     with ``prep`` the per-head RMSNorm (x ``norm_weight``) and the rotation by ``rope [L, 64, 2]`` run in the
     epilogue.  Returns a logical ``[L, heads, 128]`` bf16 view of head-major storage, like :func:`qk_prep`; with
     ``token_major`` a plain contiguous ``[L, N]`` tensor (what ``to_out`` produces).  ``fp8`` (with ``prep``):
-    e4m3 bytes plus per-(head, 128-token block) scales, returned as ``(out_uint8, scale [heads, ceil(L/128)])``."""
+    e4m3 bytes plus per-(head, 128-token block) scales, returned as ``(out_uint8, scale [heads, ceil(L/128)])``.
+    ``out_to`` (sequence parallelism, bf16 head-major epilogues): the rows go straight to the rank that computes their
+    head (as :func:`prep_scatter` does) and the call returns None."""
     _require_cuda(x, weight)
     lib = _lib.load()
     if x.dim() != 2 or weight.dim() != 2 or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
@@ -421,7 +424,15 @@ def proj_fwd(
     p.eps = float(eps)
     p.rope_mode = _lib.ROPE_HALF if rope_half else _lib.ROPE_INTERLEAVED
     H = N // HEAD_DIM
-    if token_major:
+    st_to = None
+    if out_to is not None:
+        if fp8 or token_major:
+            raise ValueError("out_to needs the bf16 head-major epilogue")
+        st_to = out_to.c_struct()
+        keep.append(st_to)
+        p.out_to = C.addressof(st_to)
+        out = None
+    elif token_major:
         out = torch.empty(L, N, dtype=torch.bfloat16, device=x.device)
         p.out, p.out_stride_l, p.out_stride_h = out.data_ptr(), N, HEAD_DIM
     else:
@@ -435,6 +446,8 @@ def proj_fwd(
         p.status_word = status_word.data_ptr()
     p.wait_limit_ns = int(wait_limit_ns)
     check(lib.h3a_proj_fwd(C.byref(p), _stream()), "h3a_proj_fwd")
+    if out_to is not None:
+        return None
     if fp8:
         return out.permute(1, 0, 2), scale
     return out if token_major else out.permute(1, 0, 2)

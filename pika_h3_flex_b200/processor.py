@@ -152,6 +152,10 @@ class B200AttnProcessor:
                   with unit weights all the same (BASELINE's configs), ``None`` (default) refuses such a module, so
                   that a norm-free model is never normalised by accident.  Modules WITH ``norm_q`` / ``norm_k`` must
                   carry a per-head RMSNorm (one ``[128]`` weight, no bias); anything else raises.
+    softmax       ``"auto"`` (default): the logit bound that follows from the QK-RMSNorm weights selects the fixed softmax
+                  reference whenever it is at most 110 (every row served up to 64, beyond that rows whose keys are ALL
+                  strongly anti-aligned with the query are reported through the status word), else the online softmax;
+                  ``"online"``: always the online softmax with a running row maximum (no bound used).
     status        ``ops.StatusWord`` shared by every launch of this processor (default: its own).  A kernel whose
                   bounded wait runs out, or that finds a malformed block index, records it there and every later
                   launch does nothing; :meth:`check_status` (one synchronisation: call it once per forward or per
@@ -170,7 +174,7 @@ class B200AttnProcessor:
     def __init__(self, mode: str = "dense_bf16", block_index: Optional[ops.BlockIndex] = None, rope_half: bool = False,
                  rope_split=ops.ROPE_SPLIT, rope_theta: float = 10000.0, qk_norm: Optional[bool] = None, eps: float = 1e-6,
                  group=None, sequence_parallel: bool = False, fused_projection: bool = False,
-                 status: Optional[ops.StatusWord] = None, check_every_call: bool = False):
+                 status: Optional[ops.StatusWord] = None, check_every_call: bool = False, softmax: str = "auto"):
         if mode not in MODES:
             raise ValueError(f"mode must be one of {sorted(MODES)}")
         if mode == "block_sparse" and block_index is None:
@@ -187,6 +191,9 @@ class B200AttnProcessor:
         self._bounds = {}
         self.fused_projection = fused_projection
         self._scaled_b = {}
+        if softmax not in ("auto", "online"):
+            raise ValueError("softmax must be auto or online")
+        self.softmax = softmax
         self.status = status if status is not None else ops.StatusWord()
         self.check_every_call = check_every_call
         self._ulysses = None
@@ -253,7 +260,7 @@ class B200AttnProcessor:
         bound = self._bounds.get(key)
         if bound is None:
             bound = self._bounds[key] = ops.normed_logit_bound(qw, kw, 0.0, mode == _lib.MODE_FP8_QK)
-        return qw, kw, eps, bound
+        return qw, kw, eps, (0.0 if self.softmax == "online" else bound)
 
     def attention(self, attn, q, k, v, rope, cross: bool):
         """Norm + rotation + attention on ``[L, H, 128]`` projections (one GPU)."""
@@ -276,9 +283,9 @@ class B200AttnProcessor:
             return None
         return parts
 
-    def _fused(self, mod, parts, x2d, prep, rope, norm_w, eps, fp8=False):
+    def _fused(self, mod, parts, x2d, prep, rope, norm_w, eps, fp8=False, out_to=None):
         """One projection through the library's GEMM; the thin LoRA product ``x A^T`` stays a torch matmul.
-        ``fp8``: returns ``(e4m3 bytes, block scales)``."""
+        ``fp8``: returns ``(e4m3 bytes, block scales)``.  ``out_to``: the rows go straight to the heads' owning ranks."""
         w, bias, a, b, scale = parts
         t = bs = None
         if a is not None:
@@ -288,7 +295,7 @@ class B200AttnProcessor:
             if bs is None:  # (alpha / rank) * B, static at inference: scaled once per module
                 bs = self._scaled_b[key] = (b.float() * scale).to(torch.bfloat16).contiguous()
         return ops.proj_fwd(x2d, w, bias, t, bs, prep=prep, rope=rope, norm_weight=norm_w, eps=eps, rope_half=self.rope_half, fp8=fp8,
-                            status_word=self.status.tensor(x2d))
+                            status_word=self.status.tensor(x2d), out_to=out_to)
 
     def attention_fused(self, attn, parts, hidden_states, ctx, rope, cross: bool):
         """Projections with the preparation in their epilogue, then attention (one GPU)."""
@@ -314,6 +321,15 @@ class B200AttnProcessor:
         if parts is not None:
             x2d = hidden_states[0]
             fp8 = MODES[self.mode] == _lib.MODE_FP8_QK
+            if self._ulysses._resolve_transport(x2d) == "peer":
+                # the projections' epilogues store every prepared row at its head's owning rank: the outbound trip of
+                # the reshard costs no pass of its own and overlaps the GEMMs (FP8-QK: the owner quantises)
+                return self._ulysses.run_scattered(
+                    x2d.shape[0], H, x2d.device,
+                    lambda to: self._fused(attn.to_q, parts[0], x2d, True, rope, qw, eps, out_to=to),
+                    lambda to: self._fused(attn.to_k, parts[1], x2d, True, rope, kw, eps, out_to=to),
+                    lambda to: self._fused(attn.to_v, parts[2], x2d, False, None, None, eps, out_to=to),
+                    bound)
             return self._ulysses.run(
                 lambda: self._fused(attn.to_q, parts[0], x2d, True, rope, qw, eps, fp8),
                 lambda: self._fused(attn.to_k, parts[1], x2d, True, rope, kw, eps, fp8),

@@ -283,9 +283,38 @@ class UlyssesAttention:
     def _run_peer(self, q, k_fn, v_fn, rope, q_weight, k_weight, eps, rope_half, logit_bound, prepared, marks):
         """One call on the peer transport (see the module docstring).  The result is a view of this rank's output
         buffer, which the next call of the same shape overwrites."""
-        fp8 = self.mode == _lib.MODE_FP8_QK
         Ls, H, _ = q.shape
-        st = self._peer_state(Ls, H, q.device)
+
+        def producer(name, x_fn):
+            def scatter(owners):
+                x = x_fn()
+                if tuple(x.shape) != (Ls, H, ops.HEAD_DIM):
+                    raise ValueError("q, k, v must be [L/P, H, 128] shards of the same shape")
+                if name == "v" or prepared:
+                    ops.prep_scatter(x, owners, no_norm=True)
+                else:
+                    ops.prep_scatter(x, owners, rope, q_weight if name == "q" else k_weight, eps, rope_half)
+            return scatter
+
+        return self.run_scattered(Ls, H, q.device, producer("q", lambda: q), producer("k", k_fn), producer("v", v_fn),
+                                  logit_bound, marks)
+
+    def run_scattered(self, Ls: int, H: int, device, q_to: Callable, k_to: Callable, v_to: Callable, logit_bound: float,
+                      marks=None) -> torch.Tensor:
+        """The peer transport with the caller's own producers: ``q_to(owners)``, ``k_to(owners)``, ``v_to(owners)`` are
+        called in that order and must store this rank's ``Ls`` tokens of all ``H`` heads, prepared (normalised and
+        rotated; V as it is), at the heads' owners described by ``owners`` (an ``ops.HeadOwners``): for example
+        ``ops.proj_fwd(..., out_to=owners)``, whose epilogue then IS the outbound trip of the reshard and overlaps it
+        with the projection's own math.  Returns this rank's ``[Ls, H, 128]`` output (a view of a buffer that the next
+        call of the same shape overwrites)."""
+        fp8 = self.mode == _lib.MODE_FP8_QK
+        if self._resolve_transport(torch.empty(0, device=device)) != "peer":
+            raise ValueError("run_scattered needs the peer transport")
+        self._validate(Ls, H)
+        st = self._peer_state(Ls, H, device)
+        own_marks = marks is None and self.timeline is not None
+        if own_marks:
+            marks = {"prep": [], "attention": []}
 
         def timed(kind, fn):
             if marks is None:
@@ -297,16 +326,8 @@ class UlyssesAttention:
             marks[kind].append((e0, e1))
             return r
 
-        for name, x in (("q", q), ("k", None), ("v", None)):
-            if x is None:
-                x = (k_fn if name == "k" else v_fn)()
-                if tuple(x.shape) != (Ls, H, ops.HEAD_DIM):
-                    raise ValueError("q, k, v must be [L/P, H, 128] shards of the same shape")
-            if name == "v" or prepared:
-                timed("prep", lambda: ops.prep_scatter(x, st.owners[name], no_norm=True))
-            else:
-                w = q_weight if name == "q" else k_weight
-                timed("prep", lambda: ops.prep_scatter(x, st.owners[name], rope, w, eps, rope_half))
+        for name, fn in (("q", q_to), ("k", k_to), ("v", v_to)):
+            timed("prep", lambda: fn(st.owners[name]))
         st.arena.barrier()  # every rank's rows have landed before an owner reads
         if st.n_local > 0:
             n = st.n_local
@@ -315,8 +336,10 @@ class UlyssesAttention:
             if fp8:  # block scales need whole 128-token blocks of the FULL sequence: quantise here, at the owner
                 qg, kg, qs, ks = timed("prep", lambda: ops.qk_prep(qg, kg, fp8=True, no_norm=True))
             timed("attention", lambda: ops.attn_fwd(qg, kg, vg, self.mode, qs, ks, self.block_index, out_ranks=st.out_ranks,
-                                                    logit_bound=logit_bound, status_word=self.status.tensor(q)))
+                                                    logit_bound=logit_bound, status_word=self.status.tensor(st.o)))
         st.arena.barrier()  # every rank's output rows have landed
+        if own_marks:
+            self.timeline.append(marks)
         return st.o
 
     def _validate(self, Ls: int, H: int) -> None:

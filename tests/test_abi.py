@@ -41,7 +41,7 @@ def test_struct_sizes_match_header(lib):
     assert C.sizeof(_lib.AttnParams) == 216 + 8 * 8 + 8  # + the per-rank output bases of the sequence-parallel return trip
     assert C.sizeof(_lib.HeadScatter) == 8 * 8 + 8 * 4  # seven int32 fields, padded to the pointers' alignment
     assert C.sizeof(_lib.PrepParams) == 144
-    assert C.sizeof(_lib.ProjParams) == 168
+    assert C.sizeof(_lib.ProjParams) == 176
     assert C.sizeof(_lib.AdaLnParams) == 112
 
 

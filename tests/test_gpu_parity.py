@@ -519,6 +519,35 @@ def test_a_logit_bound_that_does_not_hold_is_reported(h, Lk):
     check(out, O.attention(q.double(), k.double(), v.double()).float(), mx=5e-2, mean=4e-3, rel=2e-2)
 
 
+@pytest.mark.parametrize("Lk", [1024, 2304])
+def test_rows_below_the_range_of_a_large_bound_are_reported(h, Lk):
+    """A bound of 104 that HOLDS (|logit| <= 104), but a block of query rows is strongly anti-aligned with every key
+    (all their logits near -57, far below the line B - 138 = -34 the reference serves): their terms fall under fp32's range,
+    which shows in the row sum and is reported (H3A_ERR_BOUND) instead of being returned as garbage; without those rows
+    the same launch is clean and exact, and the online softmax serves all rows."""
+    L, H = 512, 1
+    g = torch.Generator().manual_seed(19)
+    u = torch.zeros(128)
+    u[0] = 1.0
+    k = (0.5 * torch.randn(Lk, H, 128, generator=g) + 16.0 * u).bfloat16()
+    q = (1.5 * torch.randn(L, H, 128, generator=g)).bfloat16()
+    v = torch.randn(Lk, H, 128, generator=g).bfloat16()
+    q_bad = q.clone()
+    q_bad[128:256] = (-40.0 * u + 0.5 * torch.randn(128, H, 128, generator=g)).bfloat16()
+    s = torch.einsum("qhd,khd->hqk", q_bad.float(), k.float()) / 128 ** 0.5
+    assert float(s.abs().max()) < 104.0 and float(s[:, 128:256].max()) < -45.0
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = h.attn_fwd(dev(q), dev(k), dev(v), logit_bound=104.0, status_word=status)
+    assert h.read_status(status) == 0
+    check(out, O.attention(q.double(), k.double(), v.double()).float(), mx=4e-2, mean=3e-3, rel=1.5e-2)
+    h.attn_fwd(dev(q_bad), dev(k), dev(v), logit_bound=104.0, status_word=status)
+    assert h.read_status(status) & 0xFF == 11
+    status.zero_()
+    out = h.attn_fwd(dev(q_bad), dev(k), dev(v), logit_bound=0.0, status_word=status)
+    assert h.read_status(status) == 0
+    check(out, O.attention(q_bad.double(), k.double(), v.double()).float(), mx=4e-2, mean=3e-3, rel=1.5e-2)
+
+
 def test_joint_path_bound_from_norm_weights(h):
     L, H = 700, 2
     q, k, v = bf16_inputs(L, H, 77)

@@ -61,6 +61,39 @@ def test_prepared_rows_land_at_their_heads_owner(h, P, H, round_robin, half):
                 assert bool((bufs[p][slot] == 9.0).all())
 
 
+@pytest.mark.parametrize("P,H,round_robin", [(2, 4, False), (4, 6, False), (3, 6, True)])
+def test_projection_epilogue_stores_rows_at_their_heads_owner(h, P, H, round_robin):
+    """The fused projection with `out_to`: every emulated rank projects its token shard (LoRA, RMSNorm and rotation in
+    the epilogue) and the epilogue stores the rows at the heads' owners; each owner must end up with exactly what the
+    projection of the FULL sequence writes for its heads (same kernel arithmetic per row: bit-identical)."""
+    from pika_h3_flex_b200 import ops
+
+    Ls, K, R = 300, 320, 64
+    L = P * Ls
+    hp = (H + P - 1) // P
+    g = torch.Generator().manual_seed(95)
+    x = torch.randn(L, K, generator=g).bfloat16().cuda()
+    w = (torch.randn(H * 128, K, generator=g) / K ** 0.5).bfloat16().cuda()
+    la = (torch.randn(R, K, generator=g) / K ** 0.5).bfloat16().cuda()
+    lb = (0.5 * torch.randn(H * 128, R, generator=g) / R ** 0.5).bfloat16().cuda()
+    nw = (1 + 0.1 * torch.randn(128, generator=g)).cuda()
+    pos = O.make_positions((L // 16, 4, 4), L - (L // 16) * 16)
+    tab = h.rope_table(pos.cuda())
+    t = torch.nn.functional.linear(x, la)
+    want = h.proj_fwd(x, w, None, t, lb, prep=True, rope=tab, norm_weight=nw)  # logical [L, H, 128]
+    bufs = [torch.full((hp, L, 128), 9.0, dtype=torch.bfloat16, device="cuda") for _ in range(P)]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for r in range(P):
+        sl = slice(r * Ls, (r + 1) * Ls)
+        to = ops.HeadOwners([b.data_ptr() for b in bufs], hp, round_robin, r * Ls, L, start_head=2 * r)
+        assert h.proj_fwd(x[sl], w, None, t[sl].contiguous(), lb, prep=True, rope=tab[sl].contiguous(), norm_weight=nw, out_to=to,
+                          status_word=status) is None
+    assert h.read_status(status) == 0
+    for head in range(H):
+        owner, slot = (head % P, head // P) if round_robin else (head // hp, head % hp)
+        assert torch.equal(bufs[owner][slot], want[:, head]), (head, owner, slot)
+
+
 def test_scatter_argument_checks(h):
     from pika_h3_flex_b200 import _lib, ops
 

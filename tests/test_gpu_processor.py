@@ -179,17 +179,20 @@ def test_processor_refuses_norms_it_does_not_implement(setup):
 
 
 @torch.no_grad()
-def test_learned_norm_weights_beyond_the_fixed_reference_range_use_the_online_kernel():
-    """norm_q / norm_k weights three times the usual size: the bound from the weights (128 * 3 * 3 / sqrt(128) > 100)
-    is outside the fixed-reference range, so the launch is the online softmax, on CTA pairs at this length (18 key
-    tiles), and must match the oracle like any other."""
+@pytest.mark.parametrize("factor,fixed", [(1.5, True), (2.3, True), (4.0, False)])
+def test_learned_norm_weights_of_growing_size(factor, fixed):
+    """norm_q / norm_k weights (1 + 0.1 N(0,1), largest about 1.27) scaled by 1.5, 2.3 and 4: the bound from the weights
+    (128 max|w_q| max|w_k| / sqrt(128)) is about 40, 100 and 290.  Up to 110 the launch keeps the fixed softmax reference
+    (beyond 64 with the row-sum check as its safety net); above, it is the online softmax, on CTA pairs at this length
+    (18 key tiles).  All must match the oracle: up to sixteen times the usual logit scale gives peaked rows and outputs
+    of order one."""
     from pika_h3_flex_b200 import ops
     from pika_h3_flex_b200.processor import B200AttnProcessor
 
     torch.manual_seed(5)
     attn = StubAttention(256, 2).cuda().bfloat16()
-    attn.norm_q.weight.mul_(3.0)
-    attn.norm_k.weight.mul_(3.0)
+    attn.norm_q.weight.mul_(factor)
+    attn.norm_k.weight.mul_(factor)
     grid, n_audio = (8, 16, 16), 256  # 2,304 tokens
     pos = O.make_positions(grid, n_audio)
     x = torch.randn(1, pos.shape[0], 256, device="cuda").bfloat16()
@@ -197,23 +200,13 @@ def test_learned_norm_weights_beyond_the_fixed_reference_range_use_the_online_ke
     y = proc(attn, x, position_ids=pos.cuda())
     proc.check_status()
     bound = ops.normed_logit_bound(attn.norm_q.weight, attn.norm_k.weight)
-    assert bound > 60.0
     ch = ops.kernel_choice(pos.shape[0], pos.shape[0], 2, logit_bound=bound)
-    assert ch["cta_pairs"] and not ch["fixed_reference"]
-    ref = oracle_forward(attn, x, None, pos)
-    # nine times the usual logit scale: peaked rows, outputs of order one; bf16 rounding of such values is 4e-3 per term
-    assert float((y.float() - ref.float()).abs().max()) < 6e-2
-    assert float((y.float() - ref.float()).norm() / ref.float().norm()) < 1e-2
-    # 1.5 x the usual size stays inside the range (bound about 29): fixed reference
-    attn.norm_q.weight.mul_(0.5)
-    attn.norm_k.weight.mul_(0.5)
-    proc2 = B200AttnProcessor()
-    y2 = proc2(attn, x, position_ids=pos.cuda())
-    proc2.check_status()
-    b2 = ops.normed_logit_bound(attn.norm_q.weight, attn.norm_k.weight)
-    assert 20.0 < b2 < 60.0 and ops.kernel_choice(pos.shape[0], pos.shape[0], 2, logit_bound=b2)["fixed_reference"]
-    ref2 = oracle_forward(attn, x, None, pos).float()
-    assert float((y2.float() - ref2).abs().max()) < 4e-2 and float((y2.float() - ref2).norm() / ref2.norm()) < 1e-2
+    assert ch["cta_pairs"] and ch["fixed_reference"] == fixed and (bound <= 110.0) == fixed, (bound, ch)
+    ref = oracle_forward(attn, x, None, pos).float()
+    # logits of up to +-100: the bf16 rounding of the prepared Q and K alone moves a logit by several hundredths, i.e. the
+    # weights of near-tied keys by several per cent; the bounds below are what that allows at outputs of order one
+    assert float((y.float() - ref).abs().max()) < 0.15
+    assert float((y.float() - ref).norm() / ref.norm()) < 2e-2
 
 
 @torch.no_grad()
