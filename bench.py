@@ -51,7 +51,7 @@ WORKLOADS = {
     "prof_dense": ((15, 32, 32), 1024, 16, "dense_bf16", None, 2001),
     "prof_fp8": ((15, 32, 32), 1024, 16, "fp8_qk", None, 2001),
     "prof_sparse": ((31, 32, 32), 1024, 16, "block_sparse", (3, 32, 32), 2003),
-    "prof_sparse7": ((31, 32, 48), 1024, 16, "block_sparse", (2, 8, 8), 2003),
+    "prof_sparse7": ((31, 48, 64), 1024, 8, "block_sparse", (2, 8, 8), 2003),  # 7.3 % of tiles: the single-CTA kernel
     "prof_cross": ((15, 32, 32), 1024, 16, "cross_bf16", None, 2004),
 }
 ALSO = ("cfg2_fp8", "cfg3_sparse", "cfg3_sparse20", "cfg4_cross")  # N = 1: short runs next to the headline workload
