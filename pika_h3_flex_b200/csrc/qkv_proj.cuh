@@ -32,7 +32,8 @@ namespace h3a {
 constexpr int kProjStages = H3A_PROJ_STAGES;
 constexpr int kProjStageBytes = 32768;  // 16 KB of X rows + 16 KB of W rows
 constexpr int kProjThreads = 320;
-constexpr int kProjSmemBytes = kProjStages * kProjStageBytes + 1024 + 256;
+constexpr int kProjStoreStageBytes = 2048;  // per epilogue warp: 32 rows x 64 bytes, to turn per-row stores into coalesced ones
+constexpr int kProjSmemBytes = kProjStages * kProjStageBytes + 1024 + 256 + 8 * kProjStoreStageBytes;
 
 enum : int { kProjStore = 0, kProjPrep = 1, kProjPrepFp8 = 2 };
 enum : int { kWaitProjEmpty = 16, kWaitProjFull = 17, kWaitProjAcc = 18, kWaitProjDrain = 19, kWaitProjAccEmpty = 20, kWaitProjMax = 21 };
@@ -215,6 +216,7 @@ qkv_proj_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
       const int quarter = warp & 3, hsel = warp >> 2;
       const int row = quarter * 32 + lane;
       const uint32_t empty_bar0 = at0(&bars->acc_empty[0]);
+      uint8_t* stg = smem + kProjStages * kProjStageBytes + 256 + warp * kProjStoreStageBytes;  // this warp's store staging
       const bool prep = args.epilogue != kProjStore;
       bool ok = true;
       int it = 0;
@@ -318,23 +320,39 @@ qkv_proj_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant_
             const int slot = args.round_robin ? h / args.n_ranks : h - owner * args.heads_per_rank;
             dst = static_cast<__nv_bfloat16*>(args.rank_out[owner]) + (static_cast<long long>(slot) * args.L_total + args.row_offset + l) * 128;
           }
+          // A thread holds 64-byte pieces of ITS row; stored as they are, a warp instruction would write 32 separate
+          // 16-byte chunks 256 bytes apart.  Each piece goes through 2 KB of shared memory (16-byte chunks XOR-swizzled
+          // by the row so that neither side has bank conflicts) and leaves as 8 rows x 64 contiguous bytes per
+          // instruction: fewer, larger transactions - what NVLink needs when the owner is another GPU, and kinder to
+          // the local L2 as well.
+          const int l_warp = tile_m0(tile) + quarter * 32;            // first token of this warp's 32 rows
+          const long long row_step = args.n_ranks > 0 ? 128 : args.out_stride_l;
+          __nv_bfloat16* dst_warp = dst - static_cast<long long>(lane) * row_step;  // row 0 of the warp (same head for all lanes)
+          auto store_piece = [&](const float (&x)[32], int col0) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint4 w;
+              w.x = pack_bf16x2(x[8 * c], x[8 * c + 1]); w.y = pack_bf16x2(x[8 * c + 2], x[8 * c + 3]);
+              w.z = pack_bf16x2(x[8 * c + 4], x[8 * c + 5]); w.w = pack_bf16x2(x[8 * c + 6], x[8 * c + 7]);
+              *reinterpret_cast<uint4*>(stg + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) = w;
+            }
+            __syncwarp();
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int rr = (lane >> 2) + 8 * k, b = lane & 3;
+              const uint4 w = *reinterpret_cast<const uint4*>(stg + rr * 64 + ((b ^ ((rr >> 1) & 3)) << 4));
+              if (l_warp + rr < args.L && n_head0 < args.N)
+                *reinterpret_cast<uint4*>(dst_warp + static_cast<long long>(rr) * row_step + col0 + 8 * b) = w;
+            }
+            __syncwarp();
+          };
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
             float lo[32], hi[32];
             prepare(g, lo, hi);
             if (g == 1) release();
-            if (live) {
-#pragma unroll
-              for (int c = 0; c < 32; c += 8) {
-                uint4 w;
-                w.x = pack_bf16x2(lo[c], lo[c + 1]); w.y = pack_bf16x2(lo[c + 2], lo[c + 3]);
-                w.z = pack_bf16x2(lo[c + 4], lo[c + 5]); w.w = pack_bf16x2(lo[c + 6], lo[c + 7]);
-                *reinterpret_cast<uint4*>(dst + 32 * g + c) = w;
-                w.x = pack_bf16x2(hi[c], hi[c + 1]); w.y = pack_bf16x2(hi[c + 2], hi[c + 3]);
-                w.z = pack_bf16x2(hi[c + 4], hi[c + 5]); w.w = pack_bf16x2(hi[c + 6], hi[c + 7]);
-                *reinterpret_cast<uint4*>(dst + 64 + 32 * g + c) = w;
-              }
-            }
+            store_piece(lo, 32 * g);
+            store_piece(hi, 64 + 32 * g);
           }
         } else {
           // e4m3 with one absmax scale per (head, 128-token block) = this warpgroup's 128 rows x 128 columns: a pass
