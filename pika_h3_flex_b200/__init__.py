@@ -10,6 +10,7 @@ from ._lib import (
     MODE_FP8_QK,
     H3AError,
 )
+from .graphs import StepGraph, renoise_sample
 from .host_path import HostJointAttention
 from .layout import position_grid
 from .ops import (
@@ -32,5 +33,5 @@ from .ops import (
 __all__ = [
     "_lib", "ops", "H3AError", "MODE_DENSE_BF16", "MODE_FP8_QK", "MODE_BLOCK_SPARSE",
     "BlockIndex", "adaln_norm", "attn_fwd", "attn_fwd_sparse_static", "static_scratch_capacity", "build_block_index", "joint_attention", "proj_fwd", "qk_prep",
-    "read_status", "check_status", "StatusWord", "rope_table", "rope_table_from_cos_sin", "position_grid", "HostJointAttention",
+    "read_status", "check_status", "StatusWord", "rope_table", "rope_table_from_cos_sin", "position_grid", "HostJointAttention", "StepGraph", "renoise_sample",
 ]
