@@ -762,7 +762,8 @@ def run_ours(args):
             "config": {"workload": name, "L": L, "Lk": c.Lk, "H": H, "d": 128, "mode": c.mode_name, "density": c.density,
                        "flops_per_step": c.flops, "step": "qk_prep(RMSNorm+RoPE) + attention forward",
                        "softmax_reference": "running row maximum" if c.bound == 0.0 else "fixed logit bound %.2f from QK-RMSNorm" % c.bound,
-                       "parallelism": "single GPU" if world == 1 else f"ulysses{world} (seq<->head reshard, transport: {ua.transport})",
+                       "parallelism": "single GPU" if world == 1 else f"ulysses{world} (seq<->head reshard, transport: {ua.transport}"
+                                      + (f"; peer memory unavailable: {ua.peer_unavailable}" if ua.peer_unavailable else "") + ")",
                        "l2": "inputs (Q,K,V = %.0f MB per rank) exceed the 126 MB L2; no flush" % (3 * Ls * H * 256 / 1e6)},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks, "parity": parity,
             "ms_per_step_sustained": ms_sustained, "sustained_steps": n_sus, "clocks_sustained": clocks_sus,

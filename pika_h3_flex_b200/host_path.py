@@ -136,6 +136,8 @@ class HostUlyssesAttention:
         if transport not in ("auto", "peer", "nccl"):
             raise ValueError("transport must be auto, peer or nccl")
         self.transport = "peer" if transport == "auto" else transport
+        self._auto = transport == "auto"
+        self.peer_unavailable = None
         if self.transport == "nccl" and mode == _lib.MODE_FP8_QK:
             raise NotImplementedError("FP8-QK under the host-buffer Ulysses path needs the peer transport")
         self.status = status if status is not None else ops.StatusWord(self.device)
@@ -160,14 +162,22 @@ class HostUlyssesAttention:
         self._marks = None
         self.arena = None
         if self.transport == "peer":
-            from .peer import Carver, PeerArena
+            from .peer import Carver, PeerArena, PeerUnavailable
 
             c = Carver()
             L = P * Ls
             nb = self.hp * L * ops.HEAD_DIM * 2
             self._off = {n: c.take(nb) for n in ("q", "k", "v")}
             self._off["o"] = c.take(Ls * H * ops.HEAD_DIM * 2)
-            self.arena = PeerArena(c.size, group, self.device)
+            try:
+                self.arena = PeerArena(c.size, group, self.device)  # fails on every rank alike
+            except PeerUnavailable as exc:
+                if not self._auto or mode == _lib.MODE_FP8_QK:
+                    raise
+                self.transport, self.peer_unavailable = "nccl", str(exc)
+                if slot_groups is None:
+                    self.slot_groups = default_head_groups(self.hp)
+        if self.transport == "peer":
             self.qh, self.kh, self.vh = (self.arena.tensor(self._off[n], (self.hp, L, ops.HEAD_DIM), torch.bfloat16) for n in ("q", "k", "v"))
             self.do = self.arena.tensor(self._off["o"], (Ls, H, ops.HEAD_DIM), torch.bfloat16)
         else:

@@ -21,7 +21,11 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from ._lib import check
+
+
+class PeerUnavailable(RuntimeError):
+    """The ranks could not share device memory (allocation or inter-process mapping failed on some rank); raised on
+    EVERY rank of the group, so that all of them can fall back to an exchange through the communication library."""
 
 
 class _Raw:
@@ -49,27 +53,47 @@ class PeerArena:
         self.nbytes = int(nbytes)
         lib = _lib.load()
         self._lib = lib
+        # Set-up is collective and must FAIL collectively: a rank whose allocation or mapping fails still takes part in
+        # every exchange below, and all ranks raise PeerUnavailable together instead of leaving the others blocked.
+        self._own = 0
+        self._opened: List[int] = []
+        self.ptrs: List[int] = [0] * self.world
+        problem = None
         ptr = C.c_void_p(0)
         handle = C.create_string_buffer(_lib.PEER_HANDLE_BYTES)
         with torch.cuda.device(self.device):
-            check(lib.h3a_peer_alloc(self.nbytes, C.byref(ptr), handle), "h3a_peer_alloc")
-        self._own = int(ptr.value)
-        self.ptrs: List[int] = [0] * self.world
-        self.ptrs[self.rank] = self._own
-        self._opened: List[int] = []
+            rc = lib.h3a_peer_alloc(self.nbytes, C.byref(ptr), handle)
+        if rc != _lib.H3A_OK:
+            problem = f"rank {self.rank}: h3a_peer_alloc of {self.nbytes} bytes: {_lib.status_string(rc)}"
+        else:
+            self._own = int(ptr.value)
+            self.ptrs[self.rank] = self._own
         if self.world > 1:
-            handles: List[Optional[Tuple[bytes, int]]] = [None] * self.world
-            dist.all_gather_object(handles, (handle.raw, self.nbytes), group=group)
-            if any(h[1] != self.nbytes for h in handles):
-                raise ValueError(f"ranks disagree on the arena size: {[h[1] for h in handles]}")
-            with torch.cuda.device(self.device):
-                for r, (raw, _) in enumerate(handles):
-                    if r == self.rank:
-                        continue
-                    p = C.c_void_p(0)
-                    check(lib.h3a_peer_open(raw, C.byref(p)), f"h3a_peer_open(rank {r})")
-                    self.ptrs[r] = int(p.value)
-                    self._opened.append(int(p.value))
+            handles: List[Optional[Tuple[Optional[bytes], int, Optional[str]]]] = [None] * self.world
+            dist.all_gather_object(handles, (handle.raw if problem is None else None, self.nbytes, problem), group=group)
+            problems = [h[2] for h in handles if h[2]]
+            if not problems and any(h[1] != self.nbytes for h in handles):
+                problems = [f"ranks disagree on the arena size: {[h[1] for h in handles]}"]
+            if not problems:
+                with torch.cuda.device(self.device):
+                    for r, (raw, _, _) in enumerate(handles):
+                        if r == self.rank:
+                            continue
+                        p = C.c_void_p(0)
+                        rc = lib.h3a_peer_open(raw, C.byref(p))
+                        if rc != _lib.H3A_OK:
+                            problem = f"rank {self.rank}: h3a_peer_open(rank {r}): {_lib.status_string(rc)}"
+                            break
+                        self.ptrs[r] = int(p.value)
+                        self._opened.append(int(p.value))
+                verdicts: List[Optional[str]] = [None] * self.world
+                dist.all_gather_object(verdicts, problem, group=group)
+                problems = [v for v in verdicts if v]
+            if problems:  # every rank is here with the same verdict
+                self._release(meet=True)
+                raise PeerUnavailable("; ".join(problems))
+        elif problem is not None:
+            raise PeerUnavailable(problem)
         self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._raw = _Raw(self._own, self.nbytes, self)
         self._bytes = torch.as_tensor(self._raw, device=self.device)
@@ -93,20 +117,25 @@ class PeerArena:
         if self.world > 1:
             dist.all_reduce(self._flag, group=self.group)
 
+    def _release(self, meet: bool = False) -> None:
+        with torch.cuda.device(self.device):
+            for p in self._opened:
+                self._lib.h3a_peer_close(p)
+            self._opened = []
+            if meet and self.world > 1 and dist.is_initialized():
+                dist.barrier(group=self.group)  # no rank frees while another still has it mapped
+            self._bytes = None
+            if self._own:
+                self._lib.h3a_peer_free(self._own)
+                self._own = 0
+
     def close(self) -> None:
         """Unmap the peers' arenas, meet, then free the own one (no rank may free while another still has it mapped)."""
         if self._closed:
             return
         self._closed = True
         torch.cuda.synchronize(self.device)
-        with torch.cuda.device(self.device):
-            for p in self._opened:
-                self._lib.h3a_peer_close(p)
-            self._opened = []
-            if self.world > 1 and dist.is_initialized():
-                dist.barrier(group=self.group)
-            self._bytes = None
-            self._lib.h3a_peer_free(self._own)
+        self._release(meet=True)
 
 
 class Carver:

@@ -32,6 +32,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib, ops
+from .peer import PeerUnavailable
 
 
 def padded_heads(n_heads: int, world: int) -> int:
@@ -194,6 +195,7 @@ class UlyssesAttention:
         if transport not in ("auto", "peer", "nccl"):
             raise ValueError("transport must be auto, peer or nccl")
         self._transport_arg = transport
+        self.peer_unavailable = None  # why the automatic choice fell back from the peer transport, if it did
         self.transport = None  # resolved at the first call: "peer" or "nccl" (which also names the gloo path of the CPU tests)
         self._peer = {}
         self.group = group
@@ -264,7 +266,7 @@ class UlyssesAttention:
             nb = st.hp * st.L * ops.HEAD_DIM * 2
             st.off = {n: c.take(nb) for n in ("q", "k", "v")}
             st.off["o"] = c.take(Ls * H * ops.HEAD_DIM * 2)
-            st.arena = PeerArena(c.size, self.group, device)
+            st.arena = PeerArena(c.size, self.group, device)  # raises PeerUnavailable on EVERY rank when any rank cannot share
             for n in ("q", "k", "v"):
                 setattr(st, n, st.arena.tensor(st.off[n], (st.hp, st.L, ops.HEAD_DIM), torch.bfloat16))
             st.o = st.arena.tensor(st.off["o"], (Ls, H, ops.HEAD_DIM), torch.bfloat16)
@@ -446,7 +448,17 @@ class UlyssesAttention:
         if transport == "peer" and not (prepared and fp8):  # prepared e4m3 operands carry per-shard scales: exchanged below
             if logit_bound is None:
                 logit_bound = ops.normed_logit_bound(q_weight, k_weight, 0.0, fp8)
-            out = self._run_peer(q, k_fn, v_fn, rope, q_weight, k_weight, eps, rope_half, logit_bound, prepared, marks)
+            try:
+                out = self._run_peer(q, k_fn, v_fn, rope, q_weight, k_weight, eps, rope_half, logit_bound, prepared, marks)
+            except PeerUnavailable as exc:
+                # raised on every rank alike, before anything was launched: an explicit request fails, the automatic
+                # choice falls back to the exchange through the communication library
+                if self._transport_arg == "peer":
+                    raise
+                self.transport = "nccl"
+                self.peer_unavailable = str(exc)
+                q = (lambda t: (lambda: t))(q)  # the projection has been computed already
+                return self.run(q, k_fn, v_fn, rope, q_weight, k_weight, eps, rope_half, logit_bound, prepared)
             if marks is not None:
                 self.timeline.append(marks)
             return out
