@@ -321,7 +321,7 @@ class B200AttnProcessor:
         if parts is not None:
             x2d = hidden_states[0]
             fp8 = MODES[self.mode] == _lib.MODE_FP8_QK
-            if self._ulysses._resolve_transport(x2d) == "peer":
+            if self._ulysses.peer_ready(x2d.shape[0], H, x2d):
                 # the projections' epilogues store every prepared row at its head's owning rank: the outbound trip of
                 # the reshard costs no pass of its own and overlaps the GEMMs (FP8-QK: the owner quantises)
                 return self._ulysses.run_scattered(

@@ -247,6 +247,22 @@ class UlyssesAttention:
     class _PeerState:
         pass
 
+    def peer_ready(self, Ls: int, H: int, like: torch.Tensor) -> bool:
+        """True when calls of this shard shape go over the peer transport: resolves the transport and, the first time,
+        builds the shared buffers (a collective step).  When the ranks cannot share memory every rank learns so here:
+        an explicit ``transport="peer"`` raises ``PeerUnavailable``, the automatic choice falls back to ``nccl``."""
+        if self._resolve_transport(like) != "peer":
+            return False
+        try:
+            self._peer_state(Ls, H, like.device)
+        except PeerUnavailable as exc:
+            if self._transport_arg == "peer":
+                raise
+            self.transport = "nccl"
+            self.peer_unavailable = str(exc)
+            return False
+        return True
+
     def _peer_state(self, Ls: int, H: int, device) -> "_PeerState":
         """Buffers of one shard shape, shared with the other ranks: this rank's heads of Q, K, V over ALL tokens
         (written by every rank's preparation kernels) and this rank's tokens of the output for all heads (written by
@@ -310,9 +326,9 @@ class UlyssesAttention:
         with the projection's own math.  Returns this rank's ``[Ls, H, 128]`` output (a view of a buffer that the next
         call of the same shape overwrites)."""
         fp8 = self.mode == _lib.MODE_FP8_QK
-        if self._resolve_transport(torch.empty(0, device=device)) != "peer":
-            raise ValueError("run_scattered needs the peer transport")
         self._validate(Ls, H)
+        if not self.peer_ready(Ls, H, torch.empty(0, device=device)):
+            raise ValueError("run_scattered needs the peer transport (see peer_ready)")
         st = self._peer_state(Ls, H, device)
         own_marks = marks is None and self.timeline is not None
         if own_marks:
@@ -444,21 +460,11 @@ class UlyssesAttention:
         q = q_fn()
         Ls, H, _ = (q[0] if isinstance(q, tuple) else q).shape
         self._validate(Ls, H)
-        transport = self._resolve_transport(q[0] if isinstance(q, tuple) else q)
-        if transport == "peer" and not (prepared and fp8):  # prepared e4m3 operands carry per-shard scales: exchanged below
+        # prepared e4m3 operands carry per-shard scales: they are exchanged below, whatever the transport
+        if not (prepared and fp8) and self.peer_ready(Ls, H, q[0] if isinstance(q, tuple) else q):
             if logit_bound is None:
                 logit_bound = ops.normed_logit_bound(q_weight, k_weight, 0.0, fp8)
-            try:
-                out = self._run_peer(q, k_fn, v_fn, rope, q_weight, k_weight, eps, rope_half, logit_bound, prepared, marks)
-            except PeerUnavailable as exc:
-                # raised on every rank alike, before anything was launched: an explicit request fails, the automatic
-                # choice falls back to the exchange through the communication library
-                if self._transport_arg == "peer":
-                    raise
-                self.transport = "nccl"
-                self.peer_unavailable = str(exc)
-                q = (lambda t: (lambda: t))(q)  # the projection has been computed already
-                return self.run(q, k_fn, v_fn, rope, q_weight, k_weight, eps, rope_half, logit_bound, prepared)
+            out = self._run_peer(q, k_fn, v_fn, rope, q_weight, k_weight, eps, rope_half, logit_bound, prepared, marks)
             if marks is not None:
                 self.timeline.append(marks)
             return out
