@@ -295,11 +295,14 @@ def make_case(name, world, rank, dev, online_max=False):
 
 def kernel_name(c, online_max, world=1):
     """Which attention kernel the library launches for this case (asked of the library itself)."""
-    from pika_h3_flex_b200.ops import kernel_choice
+    from pika_h3_flex_b200.ops import kernel_choice, split_workspace_bytes
 
     nnz = 0 if c.bi_host is None else c.bi_host.nnz
-    ch = kernel_choice(c.L, c.Lk, max(1, c.H // world), c.mode, c.bound, nnz)
-    return ch["kernel"] + ("" if ch["fixed_reference"] else " (online softmax)")
+    heads = max(1, c.H // world)
+    ch = kernel_choice(c.L, c.Lk, heads, c.mode, c.bound, nnz, workspace_bytes=split_workspace_bytes(c.L, c.Lk, heads, c.mode, c.bound))
+    if ch["fixed_reference"]:
+        return ch["kernel"]
+    return ch["kernel"] + (" (online softmax: per-row reference, then the running maximum where needed)" if ch["online_two_launch"] else " (online softmax)")
 
 
 def single_gpu_step(c, status):

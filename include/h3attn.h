@@ -95,7 +95,8 @@ typedef struct h3a_attn_params {
   float* lse;             /* optional [H, Lq] fp32 natural-log-sum-exp out, or NULL */
   void* workspace;        /* device scratch of h3a_attn_workspace_bytes() bytes: required for BLOCK_SPARSE
                              (merged tile plan); optional for the dense modes (partial sums of a split last
-                             wave of CTAs: without it, or when it is too small, the launch simply does not split) */
+                             wave of CTAs, or the redo list of the two-launch online softmax: without it, or when
+                             it is too small, the launch simply does without) */
   size_t workspace_bytes;
   int32_t* status_word;   /* optional device int32; a kernel that gives up a bounded wait (or finds a malformed
                              block index) writes a non-zero code here and returns; while it is non-zero every
@@ -155,9 +156,10 @@ int32_t h3a_version(int32_t* major, int32_t* minor);
 const char* h3a_status_string(int32_t status);
 
 /* Bytes of device scratch for these params on the current device.  BLOCK_SPARSE: what h3a_attn_fwd needs.
- * Dense modes: what lets the launch split its last wave of CTAs over the key range (0 when that does not pay:
- * no logit bound, short key range, or a CTA count that already fills whole waves); needs Lq, Lk, H, mode and
- * logit_bound only. */
+ * Dense modes (optional scratch): with a logit bound, what lets the launch split its last wave of CTAs over the key
+ * range (0 when that does not pay: short key range, or a CTA count that already fills whole waves); without a usable
+ * bound, the redo list of the two-launch online softmax (without it the launch is the running-maximum kernel alone,
+ * about 15 % slower).  Needs Lq, Lk, H, mode and logit_bound only. */
 int32_t h3a_attn_workspace_bytes(const h3a_attn_params* p, size_t* bytes);
 
 /* Which kernel h3a_attn_fwd would launch for these params on the current device (needs Lq, Lk, H, mode, logit_bound,
@@ -165,6 +167,8 @@ int32_t h3a_attn_workspace_bytes(const h3a_attn_params* p, size_t* bytes);
 #define H3A_KERNEL_CTA_PAIRS 1        /* attn_fwd_pair_kernel (two CTAs per MMA) instead of attn_fwd_kernel */
 #define H3A_KERNEL_FIXED_REFERENCE 2  /* fixed softmax reference from logit_bound instead of the running row maximum */
 #define H3A_KERNEL_SPLIT_LAST_WAVE 4  /* the CTA pairs of the last wave split the key range (+ combine_partials_kernel) */
+#define H3A_KERNEL_ONLINE_TWO_LAUNCH 8 /* online softmax as two launches: per-row fixed reference from the first key tile,
+                                          then the running-maximum kernel over the few CTA pairs that outgrew it */
 int32_t h3a_attn_kernel_choice(const h3a_attn_params* p, int32_t* choice);
 
 /* Launch the attention forward on `stream` (a cudaStream_t passed as void*). */

@@ -169,6 +169,12 @@ struct AttnArgs {
   // (the rank that holds token g: its own memory or a peer GPU's, stored to only) instead of in `o`.
   __nv_bfloat16* o_rank[8];
   int o_n_ranks, o_rank_rows;
+  // Online softmax in two launches (CTA pairs, no logit bound).  First the fixed-reference kernel with a PER-ROW
+  // reference taken from the row's first key tile; a pair in which some later logit outgrows what that reference can
+  // represent appends its number to redo_list (redo_count counts).  Then the running-maximum kernel with the same two
+  // pointers as redo_list / redo_count: pair i of its grid handles entry i of the list, pairs beyond the count leave at once.
+  int* redo_count;
+  int* redo_list;
 };
 
 // address of output row `q_row` of (local) head `head`

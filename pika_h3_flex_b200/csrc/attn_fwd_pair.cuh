@@ -61,10 +61,12 @@ struct PairBars {
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
   uint32_t early_exit;
+  volatile uint32_t redo;          // kRowRef: a row of this pair outgrew its reference (rank 1 also raises rank 0's)
 };
 static_assert(sizeof(PairBars) <= 512, "barrier block too large");
 
-constexpr int kPairSmemBytes = 2 * kQTileBytes + kPairStages * kPairStageBytes + 1024 /*align slack*/ + 512 /*barriers*/;
+constexpr int kPairRowRefBytes = 2 * 2 * 128 * 4;  // kRowRef: first-tile maxima, [stream][half][row] fp32
+constexpr int kPairSmemBytes = 2 * kQTileBytes + kPairStages * kPairStageBytes + 1024 /*align slack*/ + 512 /*barriers*/ + kPairRowRefBytes;
 static_assert(kPairSmemBytes <= 232448, "shared memory budget");
 
 enum : int { kWaitDrain = 8 };
@@ -161,7 +163,12 @@ __global__ void combine_partials_kernel(const AttnArgs args, int n_clusters) {
   if (args.o_n_ranks > 1) __threadfence_system();  // rows stored into other GPUs' memory
 }
 
-template <bool kFp8, bool kSparse, bool kFixed = true>
+// kRowRef (with kFixed, dense): no caller-supplied bound.  The reference of a row is the maximum of ITS logits over the
+// first key tile (the two warpgroups that share the row exchange their halves' maxima once, through shared memory), and
+// stays fixed: every term is then at most 2^(growth of the row maximum after the first tile), exact in floating point
+// until that growth passes about 60 in log2 units.  A half tile whose terms sum to more than 2^60 marks the pair for
+// the second launch (AttnArgs::redo_list), which recomputes its four query tiles with the running-maximum kernel.
+template <bool kFp8, bool kSparse, bool kFixed = true, bool kRowRef = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(AttnLayout<kFixed>::kThreads, 1)
 attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const AttnArgs args) {
@@ -174,6 +181,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   PairBars* bars = reinterpret_cast<PairBars*>(smem + 2 * kQTileBytes + kPairStages * kPairStageBytes);
 
   static_assert(kFixed || (!kSparse && !kPairFullS), "the running-maximum pair kernel is dense, with N = 64 S groups");
+  static_assert(!kRowRef || (kFixed && !kSparse && !kPairFullS), "per-row references: dense, on the fixed-reference structure");
   using LY = AttnLayout<kFixed>;
   constexpr int kHelperRegs = kFixed ? kPairHelperRegs : LY::kHelperRegs;
   constexpr int kSoftmaxRegs = kFixed ? kPairSoftmaxRegs : LY::kSoftmaxRegs;
@@ -184,6 +192,14 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const uint32_t rank = cluster_ctarank();
   const int n_clusters = (args.Lq + 4 * kTile - 1) / (4 * kTile);
   int cid = blockIdx.x >> 1;
+  if constexpr (!kFixed) {
+    // second launch of the two-launch online softmax: only the listed pairs are redone.  Both CTAs of a pair read the
+    // same count and leave together, before any cluster-wide state exists.
+    if (args.redo_count != nullptr) {
+      if (cid >= *args.redo_count) return;
+      cid = args.redo_list[cid];
+    }
+  }
   // dense: the pairs from split_begin on share their group of query tiles with kv_splits - 1 others
   int split = 0, n_splits = 1, part_slot = -1;
   if constexpr (!kSparse) {
@@ -255,6 +271,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_init(smem_u32(&bars->drain[t]), 1);
     }
     bars->abort_flag = 0;
+    bars->redo = 0;
     bars->early_exit = (args.status != nullptr && *reinterpret_cast<volatile int*>(args.status) != 0) ? 1u : 0u;
     fence_mbar_init();
   }
@@ -464,10 +481,13 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const int qb = min(q_tile(t), args.nqb - 1);
       qs = args.q_scale[head * args.nqb + qb];
     }
-    const float m_ref = args.fixed_m;
+    float m_ref = args.fixed_m;
     float l_sum = 0.0f;
     uint32_t j = 0;
     bool ok = true;
+    bool met = false;   // kRowRef: this warp has been to the exchange of the first-tile maxima
+    bool over = false;  // kRowRef: a half tile of this row summed past what its reference can represent
+    float* rowref = reinterpret_cast<float*>(smem + 2 * kQTileBytes + kPairStages * kPairStageBytes + 512);
     uint32_t s[64];
     for (int it = 0; ok && it < n_it; ++it) {
       const int e = entry_at(it);
@@ -504,7 +524,31 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         for (int i = 0; i < 64; ++i)
           if (i >= valid) s[i] = 0xFF800000u;  // -inf
       }
-      l_sum += exp_half_tile<kFp8>(s, c, m_ref);
+      if constexpr (kRowRef) {
+        if (j == 0) {
+          // the row's reference: the maximum of its logits over the first key tile, both halves
+          float mx0 = fmax3(__uint_as_float(s[0]), __uint_as_float(s[1]), __uint_as_float(s[2]));
+          float mx1 = fmax3(__uint_as_float(s[3]), __uint_as_float(s[4]), __uint_as_float(s[5]));
+#pragma unroll
+          for (int i = 6; i < 60; i += 6) {
+            mx0 = fmax3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+            mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+            mx0 = fmax3(mx0, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+          }
+          mx0 = fmax3(mx0, __uint_as_float(s[60]), __uint_as_float(s[61]));
+          mx1 = fmax3(mx1, __uint_as_float(s[62]), __uint_as_float(s[63]));
+          const float hm = fmaxf(mx0, mx1) * c;
+          rowref[(t * 2 + hf) * 128 + row] = hm;
+          asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");  // the stream's two warpgroups
+          met = true;
+          m_ref = fmaxf(hm, rowref[(t * 2 + (hf ^ 1)) * 128 + row]);
+        }
+      }
+      const float l_half = exp_half_tile<kFp8>(s, c, m_ref);
+      l_sum += l_half;
+      if constexpr (kRowRef) {
+        over |= !(l_half < 1.0e18f);  // 2^60: a logit far above the row's reference (or inf / NaN): redo with the running maximum
+      }
       if (row == 0 && t == 0) H3A_STAMP(hf, j, 4);
       tmem_st32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_wait_st();
@@ -513,6 +557,9 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (lane == 0) mbar_arrive_cluster(p_bar);  // rank 0's barrier: its own CTA's or the peer's
       if (row == 0 && t == 0) H3A_STAMP(hf, j, 5);
       ++j;
+    }
+    if constexpr (kRowRef) {
+      if (!met) asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");  // a wait gave up before the exchange: the partner must not block there
     }
     // ---- epilogue: as in the single-CTA kernel (own last P V, named barrier, row sums through the Q tile)
     bool have = ok && j > 0;
@@ -529,7 +576,12 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     __nv_bfloat16* orow = out_row_ptr(args, q_row, head) + 64 * hf;
     const float l_tot = l_sum + lbuf[(hf ^ 1) * 128 + row];
     // block-sparse: a row whose query tile lists nothing legitimately sums to zero; a share of a split row may too
-    if (have && hf == 0 && row_valid) check_row_sum(args, l_tot, kSparse || part_slot >= 0);
+    if constexpr (kRowRef) {
+      over |= have && !(l_tot < 1.0e30f);
+      if (__any_sync(0xFFFFFFFFu, over) && lane == 0) bars->redo = 1u;
+    } else {
+      if (have && hf == 0 && row_valid) check_row_sum(args, l_tot, kSparse || part_slot >= 0);
+    }
     if (!kSparse && part_slot >= 0) {
       // a share of the key tiles: leave the un-normalised sums for the combining kernel
       if (have) {
@@ -546,8 +598,11 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         if (hf == 0) args.part[part_slots(args, n_clusters) * 4 * 128 * 128 + rix] = l_tot;
       }
-    } else if (have && l_tot > 0.0f) {
-      const float inv = 1.0f / l_tot;
+    } else if (have) {
+      // `have` is uniform over the warp, which the TMEM loads below require; whether a ROW has anything to divide by
+      // is not (a row of a listed key tile can sum to zero, and after an overflow to NaN), so that is a select
+      const bool live = l_tot > 0.0f;
+      const float inv = live ? 1.0f / l_tot : 0.0f;
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         uint32_t o[32];
@@ -556,17 +611,20 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         if (row_valid) {
 #pragma unroll
           for (int x = 0; x < 32; x += 8) {
+            float f[8];
+#pragma unroll
+            for (int y = 0; y < 8; ++y) f[y] = live ? __uint_as_float(o[x + y]) * inv : 0.0f;
             uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(o[x]) * inv, __uint_as_float(o[x + 1]) * inv);
-            w.y = pack_bf16x2(__uint_as_float(o[x + 2]) * inv, __uint_as_float(o[x + 3]) * inv);
-            w.z = pack_bf16x2(__uint_as_float(o[x + 4]) * inv, __uint_as_float(o[x + 5]) * inv);
-            w.w = pack_bf16x2(__uint_as_float(o[x + 6]) * inv, __uint_as_float(o[x + 7]) * inv);
+            w.x = pack_bf16x2(f[0], f[1]);
+            w.y = pack_bf16x2(f[2], f[3]);
+            w.z = pack_bf16x2(f[4], f[5]);
+            w.w = pack_bf16x2(f[6], f[7]);
             *reinterpret_cast<uint4*>(orow + 32 * i + x) = w;
           }
         }
       }
       if (row_valid && args.lse && hf == 0)
-        args.lse[static_cast<long long>(head) * args.Lq + q_row] = (m_ref + log2f(l_tot)) * 0.6931471805599453f;
+        args.lse[static_cast<long long>(head) * args.Lq + q_row] = live ? (m_ref + log2f(l_tot)) * 0.6931471805599453f : -INFINITY;
     } else if (ok && row_valid && (j == 0 || have)) {
       // no key tile listed for this query tile (the stream may still have run for the peer's tile): zero rows
       const uint4 z = make_uint4(0, 0, 0, 0);
@@ -744,7 +802,13 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
   }
+  if constexpr (kRowRef) {
+    if (threadIdx.x == 0 && rank == 1 && bars->redo) st_shared_cluster_u32(mapa_shared(smem_u32(const_cast<const uint32_t*>(&bars->redo)), 0), 1u);
+  }
   cluster_sync_all();  // neither CTA frees TMEM or leaves while the other may still use it or signal its barriers
+  if constexpr (kRowRef) {
+    if (threadIdx.x == 0 && rank == 0 && bars->redo && args.redo_count != nullptr) args.redo_list[atomicAdd(args.redo_count, 1)] = cid;
+  }
   if (run && warp == kIssuerWarp) {
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem, 512);

@@ -185,6 +185,18 @@ int proj_band_tiles(int n_tiles_n, int k_total) {
   return (n_tiles_n + n_bands - 1) / n_bands;
 }
 
+// Scratch of the two-launch online softmax: a counter (padded to 16 bytes) and one entry per CTA pair.
+size_t redo_list_bytes(int64_t Lq, int64_t H) { return (4 + static_cast<size_t>((Lq + 511) / 512 * H)) * sizeof(int); }
+// H3A_ONLINE_TWO_LAUNCH=0 in the environment (read once) keeps launches without a logit bound on the running-maximum
+// kernel alone, for side-by-side measurements.
+bool two_launch_online_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("H3A_ONLINE_TWO_LAUNCH");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
+
 bool pair_kernel_enabled() {
   static const bool on = [] {
     const char* e = std::getenv("H3A_PAIR");
@@ -240,17 +252,17 @@ SplitPlan plan_split(int64_t Lq, int64_t Lk, int64_t H) {
   return sp;
 }
 
-template <bool kFp8, bool kSparse = false, bool kFixed = true>
+template <bool kFp8, bool kSparse = false, bool kFixed = true, bool kRowRef = false>
 int32_t launch_attn_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a, cudaStream_t st) {
   static std::once_flag once[kMaxDevices];
   static cudaError_t attr_err[kMaxDevices];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return H3A_ERR_LAUNCH;
   std::call_once(once[dev], [dev] {
-    cudaError_t e = cudaFuncSetAttribute(h3a::attn_fwd_pair_kernel<kFp8, kSparse, kFixed>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(h3a::attn_fwd_pair_kernel<kFp8, kSparse, kFixed, kRowRef>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          h3a::kPairSmemBytes);
     cudaFuncAttributes fa;
-    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, h3a::attn_fwd_pair_kernel<kFp8, kSparse, kFixed>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, h3a::attn_fwd_pair_kernel<kFp8, kSparse, kFixed, kRowRef>);
     if (e == cudaSuccess && fa.numRegs < h3a::AttnLayout<kFixed>::kLaunchRegs) e = cudaErrorLaunchOutOfResources;
     attr_err[dev] = e;
   });
@@ -259,7 +271,7 @@ int32_t launch_attn_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUt
   unsigned pairs = n_clusters * static_cast<unsigned>(a.H);
   const bool split = !kSparse && a.kv_splits > 1;
   if (split) pairs = static_cast<unsigned>(a.split_begin) + (pairs - static_cast<unsigned>(a.split_begin)) * static_cast<unsigned>(a.kv_splits);
-  h3a::attn_fwd_pair_kernel<kFp8, kSparse, kFixed><<<2u * pairs, h3a::AttnLayout<kFixed>::kThreads, h3a::kPairSmemBytes, st>>>(mq, mk, mv, a);  // cluster shape (2,1,1) is the kernel's
+  h3a::attn_fwd_pair_kernel<kFp8, kSparse, kFixed, kRowRef><<<2u * pairs, h3a::AttnLayout<kFixed>::kThreads, h3a::kPairSmemBytes, st>>>(mq, mk, mv, a);  // cluster shape (2,1,1) is the kernel's
   if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
   if (split) {
     const unsigned groups = n_clusters * static_cast<unsigned>(a.H) - static_cast<unsigned>(a.split_begin);
@@ -373,11 +385,23 @@ int32_t attn_fwd_impl(const h3a_attn_params* p, void* workspace, size_t workspac
     return fp8 ? launch_attn_pair<true>(mq, mk, mv, a, st) : launch_attn_pair<false>(mq, mk, mv, a, st);
   }
   if (!fixed && pair_kernel_enabled() && a.n_kv_tiles >= kPairMinKeyTiles) {
-    // no usable logit bound: the online softmax (running row maximum), also on CTA pairs; no split of the last wave
-    // (partial rows of different maxima are not directly addable)
+    // no usable logit bound: the online softmax, also on CTA pairs; no split of the last wave (partial rows of
+    // different references are not directly addable)
     a.split_begin = static_cast<int>((p->Lq + 511) / 512 * p->H);
     a.kv_splits = 1;
     if ((rc = make_map(&mk, p->k, fp8, p->Lk, p->H, p->k_stride_l, p->k_stride_h, h3a::kPairKBoxRows)) != H3A_OK) return rc;
+    if (two_launch_online_enabled() && workspace && aligned16(workspace) && workspace_bytes >= redo_list_bytes(p->Lq, p->H)) {
+      // Two launches.  (1) The fixed-reference kernel with a per-row reference taken from the row's first key tile:
+      // four MMA -> softmax -> MMA chains per CTA and no maximum pass after the first tile; a pair in which a later
+      // logit outgrows what that reference can represent puts itself on the list.  (2) The running-maximum kernel
+      // over the listed pairs only (all others leave at once), which overwrites their rows.  The result is the exact
+      // online softmax for any input.
+      a.redo_count = static_cast<int*>(workspace);
+      a.redo_list = a.redo_count + 4;
+      if (cudaMemsetAsync(a.redo_count, 0, sizeof(int), st) != cudaSuccess) return H3A_ERR_LAUNCH;
+      rc = fp8 ? launch_attn_pair<true, false, true, true>(mq, mk, mv, a, st) : launch_attn_pair<false, false, true, true>(mq, mk, mv, a, st);
+      if (rc != H3A_OK) return rc;
+    }
     return fp8 ? launch_attn_pair<true, false, false>(mq, mk, mv, a, st) : launch_attn_pair<false, false, false>(mq, mk, mv, a, st);
   }
   if (fp8) return fixed ? launch_attn<true, false, true>(mq, mk, mv, a, st) : launch_attn<true, false, false>(mq, mk, mv, a, st);
@@ -481,8 +505,10 @@ int32_t h3a_attn_workspace_bytes(const h3a_attn_params* p, size_t* bytes) {
     // optional: partial sums of the split last wave (dense launches with a logit bound); without it the launch
     // simply does not split
     const bool fixed = fixed_reference_ok(p->logit_bound);
-    const bool pairs = fixed && pair_kernel_enabled() && p->Lq > 0 && p->H > 0 && (p->Lk + 127) / 128 >= kPairMinKeyTiles;
-    *bytes = pairs ? plan_split(p->Lq, p->Lk, p->H).bytes : 0;
+    const bool pairs = pair_kernel_enabled() && p->Lq > 0 && p->H > 0 && (p->Lk + 127) / 128 >= kPairMinKeyTiles;
+    if (pairs && fixed) *bytes = plan_split(p->Lq, p->Lk, p->H).bytes;
+    else if (pairs && two_launch_online_enabled()) *bytes = redo_list_bytes(p->Lq, p->H);  // no bound: list of pairs to redo
+    else *bytes = 0;
   }
   return H3A_OK;
 }
@@ -502,6 +528,9 @@ int32_t h3a_attn_kernel_choice(const h3a_attn_params* p, int32_t* choice) {
     const SplitPlan sp = plan_split(p->Lq, p->Lk, p->H);
     if (sp.kv_splits > 1 && p->workspace_bytes >= sp.bytes) c |= H3A_KERNEL_SPLIT_LAST_WAVE;
   }
+  if (pairs && !fixed && p->mode != H3A_MODE_BLOCK_SPARSE && two_launch_online_enabled() && p->workspace && aligned16(p->workspace) &&
+      p->workspace_bytes >= redo_list_bytes(p->Lq, p->H))
+    c |= H3A_KERNEL_ONLINE_TWO_LAUNCH;
   *choice = c;
   return H3A_OK;
 }

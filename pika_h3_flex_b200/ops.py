@@ -318,8 +318,9 @@ def attn_fwd(
         p.status_word = status_word.data_ptr()
     p.wait_limit_ns = int(wait_limit_ns)
     p.logit_bound = float(logit_bound)
-    if mode != _lib.MODE_BLOCK_SPARSE and logit_bound > 0:
-        # optional scratch: lets the launch split the key range for the CTAs of its last, partly filled wave
+    if mode != _lib.MODE_BLOCK_SPARSE:
+        # optional scratch: lets the launch split the key range for the CTAs of its last, partly filled wave (with a logit
+        # bound), or run the online softmax as two launches (without one)
         need = C.c_size_t(0)
         check(lib.h3a_attn_workspace_bytes(C.byref(p), C.byref(need)), "h3a_attn_workspace_bytes")
         if need.value:
@@ -331,10 +332,11 @@ def attn_fwd(
 
 
 def split_workspace_bytes(Lq: int, Lk: int, H: int, mode: int = _lib.MODE_DENSE_BF16, logit_bound: float = 0.0) -> int:
-    """Bytes of optional scratch with which a dense / FP8-QK launch of this shape splits the key range for the CTA
-    pairs of its last, partly filled wave on the current device (0: such a launch does not split).  ``attn_fwd``
-    allocates it per call when no ``workspace`` is given; callers in a loop can allocate it once."""
-    if mode == _lib.MODE_BLOCK_SPARSE or logit_bound <= 0:
+    """Bytes of optional scratch for a dense / FP8-QK launch of this shape on the current device: with a logit bound,
+    what lets it split the key range for the CTA pairs of its last, partly filled wave; without one, the redo list of
+    the two-launch online softmax (0: neither applies).  ``attn_fwd`` allocates it per call when no ``workspace`` is
+    given; callers in a loop can allocate it once."""
+    if mode == _lib.MODE_BLOCK_SPARSE:
         return 0
     p = AttnParams()
     p.Lq, p.Lk, p.H, p.d, p.B, p.mode, p.logit_bound = int(Lq), int(Lk), int(H), HEAD_DIM, 1, int(mode), float(logit_bound)
@@ -355,7 +357,8 @@ def kernel_choice(Lq: int, Lk: int, H: int, mode: int = _lib.MODE_DENSE_BF16, lo
     check(_lib.load().h3a_attn_kernel_choice(C.byref(p), C.byref(c)), "h3a_attn_kernel_choice")
     pairs = bool(c.value & _lib.KERNEL_CTA_PAIRS)
     return {"kernel": "attn_fwd_pair_kernel" if pairs else "attn_fwd_kernel", "cta_pairs": pairs,
-            "fixed_reference": bool(c.value & _lib.KERNEL_FIXED_REFERENCE), "split_last_wave": bool(c.value & _lib.KERNEL_SPLIT_LAST_WAVE)}
+            "fixed_reference": bool(c.value & _lib.KERNEL_FIXED_REFERENCE), "split_last_wave": bool(c.value & _lib.KERNEL_SPLIT_LAST_WAVE),
+            "online_two_launch": bool(c.value & _lib.KERNEL_ONLINE_TWO_LAUNCH)}
 
 
 def proj_fwd(

@@ -548,6 +548,52 @@ def test_rows_below_the_range_of_a_large_bound_are_reported(h, Lk):
     check(out, O.attention(q_bad.double(), k.double(), v.double()).float(), mx=4e-2, mean=3e-3, rel=1.5e-2)
 
 
+def test_online_softmax_in_two_launches(h):
+    """No logit bound, 18 key tiles: the launch is the fixed-reference kernel with a per-row reference from the first key
+    tile, followed by the running-maximum kernel over the CTA pairs that put themselves on the redo list.  Ordinary data
+    redoes nothing; rows whose later logits outgrow the first tile's maximum by more than 2^60 (here by about 49 in
+    natural units) are redone and come out exact; with a workspace too small for the list the launch is the
+    running-maximum kernel alone, and both agree with the oracle."""
+    L, Lk, H = 1024, 2304, 2
+    g = torch.Generator().manual_seed(21)
+    q = torch.randn(L, H, 128, generator=g).bfloat16()
+    k = torch.randn(Lk, H, 128, generator=g).bfloat16()
+    v = torch.randn(Lk, H, 128, generator=g).bfloat16()
+    need = h.ops.split_workspace_bytes(L, Lk, H)
+    assert need >= 4 * (4 + 2 * H)
+    ch = h.ops.kernel_choice(L, Lk, H, workspace_bytes=need)
+    assert ch["cta_pairs"] and not ch["fixed_reference"] and ch["online_two_launch"]
+    assert not h.ops.kernel_choice(L, Lk, H, workspace_bytes=16)["online_two_launch"]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ref = O.attention(q.double(), k.double(), v.double()).float()
+    ws = torch.full((need,), 0x77, dtype=torch.uint8, device="cuda")
+    out, lse = h.attn_fwd(dev(q), dev(k), dev(v), workspace=ws, status_word=status, return_lse=True)
+    assert h.read_status(status) == 0 and int(ws.view(torch.int32)[0]) == 0  # nothing to redo
+    check(out, ref)
+    lse_ref = O.attention(q.double(), k.double(), v.double(), return_lse=True)[1]
+    assert float((lse.cpu().t().double() - lse_ref).abs().max()) < 2e-3
+    single = h.attn_fwd(dev(q), dev(k), dev(v), workspace=torch.empty(16, dtype=torch.uint8, device="cuda"), status_word=status)
+    check(single, ref)
+    # rows 256..383 of both heads: tiny logits against the first key tile, then a handful of keys 49 above
+    u = torch.zeros(128)
+    u[5] = 1.0
+    q2, k2 = q.clone(), k.clone()
+    q2[256:384] = (24.0 * u + 0.3 * torch.randn(128, H, 128, generator=g)).bfloat16()
+    k2[:128] = (0.3 * torch.randn(128, H, 128, generator=g)).bfloat16()
+    k2[1000:1010] = (24.0 * u + 0.3 * torch.randn(10, H, 128, generator=g)).bfloat16()
+    s = torch.einsum("qhd,khd->hqk", q2.float(), k2.float()) / 128 ** 0.5
+    assert float((s[:, 256:384, 1000:1010].amax(-1) - s[:, 256:384, :128].amax(-1)).min()) > 45.0
+    ref2 = O.attention(q2.double(), k2.double(), v.double()).float()
+    ws.fill_(0x77)
+    out2 = h.attn_fwd(dev(q2), dev(k2), dev(v), workspace=ws, status_word=status)
+    assert h.read_status(status) == 0
+    words = ws.view(torch.int32)
+    assert int(words[0]) == H and sorted(words[4 : 4 + H].tolist()) == [0, 2]  # pair 0 (rows 0..511) of each head: pairs 0 and 2
+    check(out2, ref2, mx=4e-2, mean=3e-3, rel=1.5e-2)
+    single2 = h.attn_fwd(dev(q2), dev(k2), dev(v), workspace=torch.empty(16, dtype=torch.uint8, device="cuda"), status_word=status)
+    check(single2, ref2, mx=4e-2, mean=3e-3, rel=1.5e-2)
+
+
 def test_joint_path_bound_from_norm_weights(h):
     L, H = 700, 2
     q, k, v = bf16_inputs(L, H, 77)
