@@ -130,12 +130,16 @@ struct AttnBars {
   uint64_t s_full[2][2];  // [stream][half]
   uint64_t p_full[2][2];
   uint64_t o_full[2][2];  // completion of the P V of (stream, half): one phase per key tile
+  uint64_t q_empty;       // every S MMA of a group of query tiles has completed: the next group's Q may be loaded
+  uint64_t o_free[2];     // the stream's softmax warps have read O of a group: its next group may overwrite it
   uint32_t tmem_base;
   volatile uint32_t abort_flag;
   uint32_t early_exit;
+  volatile uint32_t stop[2];  // per stream: one thread's reading of abort_flag, so that both warpgroups leave together
 };
 
-constexpr int kAttnSmemBytes = 2 * kQTileBytes + kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int kRowSumBytes = 2 * 128 * 4;  // fixed-reference softmax: the row sums the two warpgroups of a stream exchange
+constexpr int kAttnSmemBytes = 2 * kQTileBytes + kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/ + kRowSumBytes;
 static_assert(sizeof(AttnBars) <= 256, "barrier block too large");
 static_assert(kAttnSmemBytes <= 232448, "shared memory budget");
 
@@ -192,7 +196,8 @@ __device__ __forceinline__ __nv_bfloat16* out_row_ptr(const AttnArgs& a, int q_r
 // status word layout: bits [0,8) code, bits [8,32) blockIdx.x (truncated)
 enum : int {
   kWaitQFull = 1, kWaitKvEmpty = 2, kWaitKvFullK = 3, kWaitKvFullV = 4,
-  kWaitSFull = 5, kWaitPFull = 6, kWaitOFull = 7
+  kWaitSFull = 5, kWaitPFull = 6, kWaitOFull = 7,
+  kWaitQEmpty = 12, kWaitOFree = 13  // persistent CTAs (8 = drain of a CTA pair, 9 = self-test, 10 / 11 = bad index / bound)
 };
 
 // Optional timeline trace (debug builds only, -DH3A_TRACE): CTA 0 stamps clock64() at phase boundaries.
@@ -363,45 +368,50 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr int kIssuerWarp = LY::kSoftmaxWarps + 1;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // CTA -> (head, pair): head-major, so that the CTAs running at the same time share one head's K/V in L2.
-  // Block-sparse: the few pairs with long key lists (dense audio rows) of ALL heads come first, otherwise the
-  // ones of the last heads would start late and run on alone at the end.
-  int head, pair;
-  if (kSparse && args.heavy_pairs > 0) {
-    const int n_heavy_ctas = args.heavy_pairs * args.H;
-    if (static_cast<int>(blockIdx.x) < n_heavy_ctas) {
-      head = blockIdx.x / args.heavy_pairs;
-      pair = blockIdx.x % args.heavy_pairs;
-    } else {
-      const int r = blockIdx.x - n_heavy_ctas, n_light = args.n_qpairs - args.heavy_pairs;
-      head = r / n_light;
-      pair = args.heavy_pairs + r % n_light;
-    }
-  } else {
-    head = blockIdx.x / args.n_qpairs;
-    pair = blockIdx.x % args.n_qpairs;
-  }
-  const int q0 = pair * 2 * kTile;
-
-  constexpr uint32_t kQBytes = kFp8 ? kHalfBytes : kQTileBytes;  // bytes per Q tile
-  constexpr uint32_t kKBytes = kFp8 ? kHalfBytes : kStageBytes;  // bytes per K tile
-  constexpr uint32_t kVBytes = kStageBytes;
-
-  // ---- plan: which key tiles, for which streams
-  int n_it;
+  // Work items: one per (head, pair of query tiles), head-major, so that the CTAs running at the same time share one
+  // head's K/V in L2.  Block-sparse: the few pairs with long key lists (dense audio rows) of ALL heads come first,
+  // otherwise the ones of the last heads would start late and run on alone at the end.
+  // A CTA handles items blockIdx.x, blockIdx.x + gridDim.x, ...: with one CTA per item that is one item; with fewer
+  // CTAs (fixed-reference kernels, one CTA per SM) the CTA is persistent: barriers, TMEM and the K/V ring are set up
+  // once, and the Q load, S MMAs and K/V loads of the next item run under the epilogue of the current one.  Every
+  // role walks the same item sequence on its own; no item number is passed between warps.
+  const int n_items = args.n_qpairs * args.H;
+  int head = 0, pair = 0, q0 = 0, n_it = 0, dense_flags = 3;
   const int32_t* plan = nullptr;
-  int dense_flags = 3;
-  if constexpr (kSparse) {
-    plan = args.plan + clamp_row_ptr(args.row_ptr[2 * pair], args.nnz);
-    n_it = args.plan_cnt[pair];
-  } else {
-    n_it = args.n_kv_tiles;
-    dense_flags = (q0 + kTile < args.Lq) ? 3 : 1;
-  }
+  auto set_item = [&](int item) {
+    if (kSparse && args.heavy_pairs > 0) {
+      const int n_heavy = args.heavy_pairs * args.H;
+      if (item < n_heavy) {
+        head = item / args.heavy_pairs;
+        pair = item % args.heavy_pairs;
+      } else {
+        const int r = item - n_heavy, n_light = args.n_qpairs - args.heavy_pairs;
+        head = r / n_light;
+        pair = args.heavy_pairs + r % n_light;
+      }
+    } else {
+      head = item / args.n_qpairs;
+      pair = item % args.n_qpairs;
+    }
+    q0 = pair * 2 * kTile;
+    // the plan: which key tiles, for which streams
+    if constexpr (kSparse) {
+      plan = args.plan + clamp_row_ptr(args.row_ptr[2 * pair], args.nnz);
+      n_it = args.plan_cnt[pair];
+    } else {
+      n_it = args.n_kv_tiles;
+      dense_flags = (q0 + kTile < args.Lq) ? 3 : 1;
+    }
+  };
   auto entry_at = [&](int it) -> int {
     if constexpr (kSparse) return plan[it];
     else return (it << 2) | dense_flags;
   };
+  set_item(blockIdx.x);
+
+  constexpr uint32_t kQBytes = kFp8 ? kHalfBytes : kQTileBytes;  // bytes per Q tile
+  constexpr uint32_t kKBytes = kFp8 ? kHalfBytes : kStageBytes;  // bytes per K tile
+  constexpr uint32_t kVBytes = kStageBytes;
 
   // ---- set-up
   if (threadIdx.x == 0) {
@@ -410,12 +420,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(smem_u32(&bars->kv_empty[i]), 2);  // released by both issuer warps
     }
     mbar_init(smem_u32(&bars->q_full), 1);
+    mbar_init(smem_u32(&bars->q_empty), 2);  // one commit from each issuer warp
     for (int t = 0; t < 2; ++t) {
       for (int hf = 0; hf < 2; ++hf) {
         mbar_init(smem_u32(&bars->s_full[t][hf]), 1);
         mbar_init(smem_u32(&bars->p_full[t][hf]), 128);
         mbar_init(smem_u32(&bars->o_full[t][hf]), 1);
       }
+      mbar_init(smem_u32(&bars->o_free[t]), 8);  // one arrive per softmax warp of the stream (fixed reference: 8 warps)
+      bars->stop[t] = 0;
     }
     bars->abort_flag = 0;
     bars->early_exit = (args.status != nullptr && *reinterpret_cast<volatile int*>(args.status) != 0) ? 1u : 0u;
@@ -445,18 +458,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // =========================================================== producer
     // The whole warp walks the loop (uniform control flow, uniform operands); one elected lane issues.
     const uint32_t leader = elect_one();
-    {
-      const uint32_t qbar = smem_u32(&bars->q_full);
-      mbar_arrive_expect_tx_if(leader, qbar, 2 * kQBytes);
-#pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        tma_load_3d_if(leader, q_smem + t * kQTileBytes, &tm_q, qbar, 0, q0 + t * kTile, head);
-        if constexpr (!kFp8) tma_load_3d_if(leader, q_smem + t * kQTileBytes + kHalfBytes, &tm_q, qbar, 64, q0 + t * kTile, head);
-      }
-    }
-    int cnt = 0;
+    int cnt = 0;     // K / V tiles loaded so far: the ring runs on across items
+    uint32_t g = 0;  // items with work so far: the phase of q_full / q_empty
     bool ok = true;
+    for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+    set_item(item);
+    if (n_it == 0) continue;
+    // The Q tiles are free when every S MMA of the previous item has completed, which is late in that item; its K / V
+    // ring slots free up earlier.  So the first two key tiles of an item are requested ahead of its Q tiles unless those
+    // happen to be free already; the wait for them blocks only from the third key tile on (or the last, if sooner).
+    const int q_at = g > 0 ? min(2, n_it - 1) : 0;
+    bool q_loaded = false;
     for (int it = 0; ok && it < n_it; ++it) {
+      if (!q_loaded) {
+        bool q_free = g == 0;
+        if (!q_free) q_free = __all_sync(0xFFFFFFFFu, mbar_test_wait(smem_u32(&bars->q_empty), (g - 1) & 1));
+        if (!q_free && it >= q_at) {
+          ok = warp_wait(wc, smem_u32(&bars->q_empty), (g - 1) & 1, kWaitQEmpty);
+          if (!ok) break;
+          q_free = true;
+        }
+        if (q_free) {
+          const uint32_t qbar = smem_u32(&bars->q_full);
+          mbar_arrive_expect_tx_if(leader, qbar, 2 * kQBytes);
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            tma_load_3d_if(leader, q_smem + t * kQTileBytes, &tm_q, qbar, 0, q0 + t * kTile, head);
+            if constexpr (!kFp8) tma_load_3d_if(leader, q_smem + t * kQTileBytes + kHalfBytes, &tm_q, qbar, 64, q0 + t * kTile, head);
+          }
+          q_loaded = true;
+        }
+      }
       const int tile = entry_at(it) >> 2;
 #pragma unroll
       for (int kv = 0; kv < 2; ++kv) {  // K tile, then V tile
@@ -478,6 +510,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ++cnt;
       }
     }
+    ++g;
+    }  // items
     __syncwarp();
   } else if (warp == kIssuerWarp || warp == kIssuerWarp + 1) {
     // =========================================================== MMA issuers, one warp per stream
@@ -485,17 +519,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // tracks the MMAs of the thread that executes it, and the election is the same lane every time).
     // Each issuer walks every plan entry, also those that do not list its stream: a K/V stage is released
     // by one commit from each issuer, and waiting for the stage first keeps the two in step.
-    if (n_it > 0) {
+    {
       const int t = warp - kIssuerWarp;
       const uint32_t leader = elect_one();
       constexpr uint32_t kSN = kFullS ? 128 : 64;
       constexpr uint32_t idesc_s = kFp8 ? umma_idesc(UMMA_FMT_E4M3, UMMA_FMT_E4M3, 0, 0, 128, kSN)
                                         : umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 0, 128, kSN);
       constexpr uint32_t idesc_pv = umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 1, 128, 128);
-      bool ok = warp_wait(wc, smem_u32(&bars->q_full), 0, kWaitQFull);
-      tc_fence_after_sync();
-      uint32_t p_cnt[2] = {0, 0};
-      uint32_t pv_cnt = 0;
+      bool ok = true;
+      uint32_t p_cnt[2] = {0, 0};  // P halves consumed so far (all items): the phase of p_full
+      uint32_t pv_cnt = 0;         // P V groups issued for the current item: the first one overwrites O
+      uint32_t g = 0;              // items with work so far: the phase of q_full / q_empty / o_free
+      int c0 = 0;                  // K / V tiles of the ring consumed before the current item
       // the descriptor of the Q tile never changes; K/V descriptors are a per-stage base plus constants
       const uint64_t q_desc = umma_desc_sw128(q_smem + t * kQTileBytes, 16, 1024);
       const uint64_t k_desc0 = umma_desc_sw128(ring_smem, 16, 1024);
@@ -533,25 +568,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_commit_if(leader, smem_u32(&bars->o_full[t][hf]));
       };
 
-      if (ok) {  // prologue: both S halves of entry 0
+      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+      set_item(item);
+      if (n_it == 0) continue;
+      ok = warp_wait(wc, smem_u32(&bars->q_full), g & 1, kWaitQFull);
+      if (!ok) break;
+      tc_fence_after_sync();
+      pv_cnt = 0;
+      {  // prologue: both S halves of entry 0 (in TMEM they follow the previous item's last P V: MMAs run in issue order)
         const int f0 = entry_at(0) & 3;
-        ok = warp_wait(wc, smem_u32(&bars->kv_full[0]), 0, kWaitKvFullK);
+        const int s0 = c0 % kStages;
+        ok = warp_wait(wc, smem_u32(&bars->kv_full[s0]), (c0 / kStages) & 1, kWaitKvFullK);
         if (ok) {
           tc_fence_after_sync();
           if ((f0 >> t) & 1) {
-            issue_s(0, 0);
-            if constexpr (!kFullS) issue_s(1, 0);
+            issue_s(0, s0);
+            if constexpr (!kFullS) issue_s(1, s0);
           }
-          umma_commit_if(leader, smem_u32(&bars->kv_empty[0]));
+          umma_commit_if(leader, smem_u32(&bars->kv_empty[s0]));
         }
       }
       for (int it = 0; ok && it < n_it; ++it) {
         const int f = entry_at(it) & 3;
         const bool has_next = (it + 1 < n_it);
         const int fn = has_next ? (entry_at(it + 1) & 3) : 0;
-        const int cv = 2 * it + 1, ck = 2 * it + 2;
+        const int cv = c0 + 2 * it + 1, ck = c0 + 2 * it + 2;
         const int sv = cv % kStages, sk = ck % kStages;
         const bool mine = (f >> t) & 1, mine_next = (fn >> t) & 1;
+        // every S MMA of the item has been issued (the last one with the previous entry): when they complete, the Q
+        // tiles may be reloaded for the next item
+        if (!has_next) umma_commit_if(leader, smem_u32(&bars->q_empty));
         ok = warp_wait(wc, smem_u32(&bars->kv_full[sv]), (cv / kStages) & 1, kWaitKvFullV);
         if (!ok) break;
         bool k_ready = false;
@@ -560,6 +606,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (ok && mine) {
             H3A_STAMP(2 + t, 2 * it + hf, 0);
             ok = warp_wait(wc, smem_u32(&bars->p_full[t][hf]), p_cnt[hf] & 1, kWaitPFull);
+            if (ok && pv_cnt == 0 && g > 0) {
+              // the first P V of an item overwrites O: the stream's softmax warps must have read the previous item's.
+              // They arrive once per item with work, and cannot pass this item before its MMAs are issued, so the
+              // barrier is never more than one phase ahead of this wait.
+              ok = warp_wait(wc, smem_u32(&bars->o_free[t]), (g - 1) & 1, kWaitOFree);
+            }
             if (ok) {
               ++p_cnt[hf];
               tc_fence_after_sync();
@@ -584,6 +636,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_commit_if(leader, smem_u32(&bars->kv_empty[sv]));
         if (has_next) umma_commit_if(leader, smem_u32(&bars->kv_empty[sk]));
       }
+      c0 += 2 * n_it;
+      ++g;
+      }  // items
     }
     __syncwarp();
    }
@@ -599,19 +654,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t sb = tmem + lane_base + t * kTile + hf * 64;
     const uint32_t o_addr = tmem + lane_base + 256 + t * kTile + hf * 64;  // epilogue: this warpgroup's 64 O columns
-    const int q_row = q0 + t * kTile + row;
     const int last_tile = args.n_kv_tiles - 1;
     const int tail = args.Lk - last_tile * kTile;
+    const float m_ref = args.fixed_m;
+    // row sums of the stream's two warpgroups meet here (one slot per row, used in turn by the two halves)
+    float* lbuf = reinterpret_cast<float*>(smem + 2 * kQTileBytes + kStages * kStageBytes + 256) + t * 128;
+    uint32_t j = 0;  // key tiles this warpgroup has processed, over all items: the phase of s_full / o_full
+    bool ok = true;
+    uint32_t s[64];
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    set_item(item);
+    const int q_row = q0 + t * kTile + row;
+    const bool row_valid = q_row < args.Lq;
+    __nv_bfloat16* orow = out_row_ptr(args, q_row, head) + 64 * hf;
+    if (n_it == 0) {  // (block-sparse) neither query tile lists a key tile: zero rows, and no other role does anything
+      if (row_valid) {
+        const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int x = 0; x < 64; x += 8) *reinterpret_cast<uint4*>(orow + x) = z;
+        if (args.lse && hf == 0) args.lse[static_cast<long long>(head) * args.Lq + q_row] = -INFINITY;
+      }
+      continue;
+    }
     float qs = 1.0f;
     if constexpr (kFp8) {
       const int qb = min(q0 / kTile + t, args.nqb - 1);
       qs = args.q_scale[head * args.nqb + qb];
     }
-    const float m_ref = args.fixed_m;
     float l_sum = 0.0f;
-    uint32_t j = 0;
-    bool ok = true;
-    uint32_t s[64];
+    const uint32_t j0 = j;
     for (int it = 0; ok && it < n_it; ++it) {
       const int e = entry_at(it);
       if (!((e >> t) & 1)) continue;
@@ -644,52 +715,66 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (row == 0 && t == 0) H3A_STAMP(hf, j, 5);
       ++j;
     }
-    // ---- epilogue: the two warpgroups of a stream add their row sums through shared memory and each stores 64
-    //      of the 128 output columns.  The exchange buffer is the stream's Q tile, which is free only when EVERY
-    //      MMA of the stream has completed.  A warpgroup may be up to a tile ahead of its partner, so it must
-    //      not judge that by the partner's barrier (a parity wait two phases behind passes at once): each waits
-    //      for its OWN last P V (never more than one phase away), then a named barrier joins the two.
-    bool have = ok && j > 0;
+    // ---- epilogue: the two warpgroups of a stream add their row sums through shared memory and each stores 64 of
+    //      the 128 output columns.  A warpgroup may be up to a tile ahead of its partner, so it waits for its OWN
+    //      last P V (never more than one phase away); two named barriers, which every thread of both warpgroups
+    //      always reaches, carry the exchange: half 0 leaves its sum, half 1 swaps it for its own.  Between them ONE
+    //      thread reads the abort flag for the stream, so that both warpgroups leave the item loop together (a
+    //      warpgroup that went on alone would wait at the next item's named barrier for ever).
+    bool have = ok && j > j0;
     if (have) {
       have = warp_wait(wc, smem_u32(&bars->o_full[t][hf]), (j - 1) & 1, kWaitOFull);
       if (have) tc_fence_after_sync();
     }
-    asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");  // every thread of both warpgroups, always
-    float* lbuf = reinterpret_cast<float*>(smem + t * kQTileBytes);
-    lbuf[hf * 128 + row] = l_sum;
+    if (hf == 0) lbuf[row] = l_sum;
     asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");
-    if (have) tc_fence_after_sync();
-    const bool row_valid = q_row < args.Lq;
-    __nv_bfloat16* orow = out_row_ptr(args, q_row, head) + 64 * hf;
+    float l_other = 0.0f;
+    if (hf == 1) {
+      l_other = lbuf[row];
+      lbuf[row] = l_sum;
+    } else if (row == 0) {
+      bars->stop[t] = bars->abort_flag;
+    }
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");
+    if (hf == 0) l_other = lbuf[row];
+    const bool stop = bars->stop[t] != 0u;
     if (have) {
-      const float l_tot = l_sum + lbuf[(hf ^ 1) * 128 + row];
+      // O leaves TMEM first: the next item's first P V may overwrite it while the rows are converted and stored
+      tc_fence_after_sync();
+      tmem_ld32(o_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_ld32(o_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      tmem_wait_ld();
+      reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+    }
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&bars->o_free[t]));  // once per item with work, whether or not the stream had tiles
+    if (have) {
+      const float l_tot = l_sum + l_other;
       if (hf == 0 && row_valid) check_row_sum(args, l_tot, false);
       const float inv = 1.0f / l_tot;
+      if (row_valid) {
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        uint32_t o[32];
-        tmem_ld32(o_addr + 32 * i, o);
-        tmem_wait_ld();
-        if (row_valid) {
-#pragma unroll
-          for (int x = 0; x < 32; x += 8) {
-            uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(o[x]) * inv, __uint_as_float(o[x + 1]) * inv);
-            w.y = pack_bf16x2(__uint_as_float(o[x + 2]) * inv, __uint_as_float(o[x + 3]) * inv);
-            w.z = pack_bf16x2(__uint_as_float(o[x + 4]) * inv, __uint_as_float(o[x + 5]) * inv);
-            w.w = pack_bf16x2(__uint_as_float(o[x + 6]) * inv, __uint_as_float(o[x + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + 32 * i + x) = w;
-          }
+        for (int x = 0; x < 64; x += 8) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(s[x]) * inv, __uint_as_float(s[x + 1]) * inv);
+          w.y = pack_bf16x2(__uint_as_float(s[x + 2]) * inv, __uint_as_float(s[x + 3]) * inv);
+          w.z = pack_bf16x2(__uint_as_float(s[x + 4]) * inv, __uint_as_float(s[x + 5]) * inv);
+          w.w = pack_bf16x2(__uint_as_float(s[x + 6]) * inv, __uint_as_float(s[x + 7]) * inv);
+          *reinterpret_cast<uint4*>(orow + x) = w;
         }
+        if (args.lse && hf == 0)
+          args.lse[static_cast<long long>(head) * args.Lq + q_row] = (m_ref + log2f(l_tot)) * 0.6931471805599453f;
       }
-      if (row_valid && args.lse && hf == 0)
-        args.lse[static_cast<long long>(head) * args.Lq + q_row] = (m_ref + log2f(l_tot)) * 0.6931471805599453f;
-    } else if (ok && j == 0 && row_valid) {
+    } else if (ok && j == j0 && row_valid) {
       const uint4 z = make_uint4(0, 0, 0, 0);  // no key tile listed for this query tile: the output row is zero
 #pragma unroll
       for (int x = 0; x < 64; x += 8) *reinterpret_cast<uint4*>(orow + x) = z;
       if (args.lse && hf == 0) args.lse[static_cast<long long>(head) * args.Lq + q_row] = -INFINITY;
     }
+    if (stop) break;
+    }  // items
     } else {
     // =========================================================== softmax / rescale / epilogue
     const int t = warp >> 2;            // stream

@@ -110,6 +110,22 @@ size_t sparse_workspace_bytes(const h3a_attn_params* p) {
 
 constexpr int kMaxDevices = 64;
 
+int sm_count_of_current_device();
+// Persistent CTAs for the single-CTA kernel with a fixed softmax reference: one CTA per SM walks the (head, query
+// tile pair) items, so that barriers, TMEM and the K/V ring are set up once per SM and the loads and S MMAs of the
+// next item run under the epilogue of the current one.  It pays where an item is short (cross-attention to 512 text
+// tokens: 4 key tiles per item).  H3A_PERSIST in the environment, read once: 0 = one CTA per item everywhere,
+// 1 = persistent also for block-sparse launches, unset = dense launches only (block-sparse items differ in length
+// by up to 30 x, which the hardware's CTA scheduler balances better than a fixed stride does).
+int persist_mode() {
+  static const int mode = [] {
+    const char* e = std::getenv("H3A_PERSIST");
+    if (e == nullptr || e[0] == '\0') return 2;
+    return e[0] == '0' ? 0 : 1;
+  }();
+  return mode;
+}
+
 template <bool kFp8, bool kSparse, bool kFixed = false>
 int32_t launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a, cudaStream_t st) {
   // function attributes belong to a device's context: set them once per device this process launches on
@@ -127,7 +143,12 @@ int32_t launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensor
     attr_err[dev] = e;
   });
   if (attr_err[dev] != cudaSuccess) return H3A_ERR_LAUNCH;
-  const unsigned grid = static_cast<unsigned>(a.n_qpairs) * static_cast<unsigned>(a.H);
+  unsigned grid = static_cast<unsigned>(a.n_qpairs) * static_cast<unsigned>(a.H);
+  if (kFixed) {  // the running-maximum kernel handles one item per CTA
+    const int mode = persist_mode();
+    const unsigned sms = static_cast<unsigned>(sm_count_of_current_device());
+    if (sms > 0 && grid > sms && (mode == 1 || (mode == 2 && !kSparse))) grid = sms;
+  }
   h3a::attn_fwd_kernel<kFp8, kSparse, kFixed><<<grid, h3a::AttnLayout<kFixed>::kThreads, h3a::kAttnSmemBytes, st>>>(mq, mk, mv, a);
   return cudaGetLastError() == cudaSuccess ? H3A_OK : H3A_ERR_LAUNCH;
 }

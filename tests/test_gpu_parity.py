@@ -628,6 +628,96 @@ def test_config4_cross_attention_shape(h):
     assert float((o1.float() - 1).abs().max()) <= 8e-3
 
 
+# ------------------------------------------------------------------------------------------ persistent CTAs
+_PERSIST_CASES = [  # (Lq, Lk, heads, fp8): more (head, query-tile pair) items than SMs, the last pair of a head half empty
+    (15360, 640, 6, False),   # 360 items of 5 key tiles: the 5-stage K/V ring wraps inside and across items
+    (10000, 552, 5, False),   # 79 query tiles: every head ends on a pair with one tile; key tail of 40
+    (9000, 130, 9, False),    # 2 key tiles per item, the second nearly empty
+    (8192, 1024, 8, True),    # FP8-QK below the CTA-pair threshold
+]
+_PERSIST_CHILD = r"""
+import sys, torch
+sys.path.insert(0, %(root)r)
+import pika_h3_flex_b200 as h
+outs = []
+for i, (Lq, Lk, H, fp8) in enumerate(%(cases)r):
+    g = torch.Generator().manual_seed(500 + i)
+    q = torch.randn(Lq, H, 128, generator=g).bfloat16().cuda()
+    k = torch.randn(Lk, H, 128, generator=g).bfloat16().cuda()
+    v = torch.randn(Lk, H, 128, generator=g).bfloat16().cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = h.joint_attention(q, k, v, None, mode=h.MODE_FP8_QK if fp8 else h.MODE_DENSE_BF16, status_word=status)
+    assert h.read_status(status) == 0
+    outs.append(out.cpu())
+torch.save(outs, %(path)r)
+"""
+
+
+def test_persistent_ctas_give_the_same_rows_as_one_cta_per_item(h, tmp_path):
+    """Single-CTA kernel with a fixed softmax reference (few key tiles per item: cross-attention shapes): by default one
+    CTA per SM walks the items; H3A_PERSIST=0 (read once per process, so a child process runs it) launches one CTA per
+    item.  Both do the same arithmetic per row in the same order: the outputs must be bit-identical, and match the
+    oracle on sampled rows."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = tmp_path / "per_item.pt"
+    code = _PERSIST_CHILD % {"root": root, "cases": _PERSIST_CASES, "path": str(path)}
+    subprocess.run([sys.executable, "-c", code], check=True, env=dict(os.environ, H3A_PERSIST="0"), timeout=300)
+    per_item = torch.load(path)
+    for i, (Lq, Lk, H, fp8) in enumerate(_PERSIST_CASES):
+        g = torch.Generator().manual_seed(500 + i)
+        q = torch.randn(Lq, H, 128, generator=g).bfloat16()
+        k = torch.randn(Lk, H, 128, generator=g).bfloat16()
+        v = torch.randn(Lk, H, 128, generator=g).bfloat16()
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        out = h.joint_attention(dev(q), dev(k), dev(v), None, mode=h.MODE_FP8_QK if fp8 else h.MODE_DENSE_BF16, status_word=status)
+        assert h.read_status(status) == 0
+        assert torch.equal(out.cpu(), per_item[i]), (Lq, Lk, H, fp8)
+        rows = torch.cat([torch.arange(0, Lq, 397), torch.tensor([Lq - 1, Lq - 129, 255, 256])])
+        ref = O.attention(O.rms_norm(q[rows].float()), O.rms_norm(k.float()), v.float())
+        if fp8:
+            check(out[rows], ref, mx=FP8_MAX, mean=FP8_MEAN, rel=FP8_REL)
+        else:
+            check(out[rows], ref)
+        o1 = h.joint_attention(dev(q), dev(k), torch.ones_like(dev(v)), None, mode=h.MODE_FP8_QK if fp8 else h.MODE_DENSE_BF16)
+        assert float((o1.float() - 1).abs().max()) <= 8e-3
+
+
+def test_persistent_ctas_on_block_sparse_lists(h, tmp_path):
+    """Block-sparse launches keep one CTA per item by default; H3A_PERSIST=1 makes them persistent too (items of very
+    different length, and items that list nothing).  Same rows, bit for bit."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = tmp_path / "persistent.pt"
+    grid, n_audio, H, window = (24, 20, 30), 256, 3, (1, 2, 3)  # 58 pairs of query tiles x 3 heads, below 12 % density
+    code = (
+        "import sys, torch; sys.path.insert(0, %r)\n"
+        "import pika_h3_flex_b200 as h\n"
+        "bi = h.build_block_index(%r, %r, %r).to('cuda')\n"
+        "L = %d\n"
+        "g = torch.Generator().manual_seed(91)\n"
+        "q, k, v = (torch.randn(L, %d, 128, generator=g).bfloat16().cuda() for _ in range(3))\n"
+        "st = torch.zeros(1, dtype=torch.int32, device='cuda')\n"
+        "out = h.attn_fwd(q, k, v, mode=h.MODE_BLOCK_SPARSE, block_index=bi, logit_bound=%r, status_word=st)\n"
+        "assert h.read_status(st) == 0\n"
+        "torch.save(out.cpu(), %r)\n" % (root, grid, n_audio, window, grid[0] * grid[1] * grid[2] + n_audio, H, PAIR_BOUND, str(path))
+    )
+    subprocess.run([sys.executable, "-c", code], check=True, env=dict(os.environ, H3A_PERSIST="1"), timeout=300)
+    bih = h.build_block_index(grid, n_audio, window)
+    nqb = bih.row_ptr.numel() - 1
+    assert bih.col_idx.numel() < 0.12 * nqb * nqb  # the single-CTA kernel's range
+    bi = bih.to("cuda")
+    L = grid[0] * grid[1] * grid[2] + n_audio
+    g = torch.Generator().manual_seed(91)
+    q, k, v = (torch.randn(L, H, 128, generator=g).bfloat16().cuda() for _ in range(3))
+    out = h.attn_fwd(q, k, v, mode=h.MODE_BLOCK_SPARSE, block_index=bi, logit_bound=PAIR_BOUND)
+    assert torch.equal(out.cpu(), torch.load(path))
+
+
 # ------------------------------------------------------------------------------------------ bounded waits
 def test_wait_that_nothing_signals_runs_out_and_is_reported(h):
     """The bounded wait of the attention kernels, on a barrier nothing ever signals: it must give up after the
