@@ -62,12 +62,23 @@ struct PairBars {
   volatile uint32_t abort_flag;
   uint32_t early_exit;
   volatile uint32_t redo;          // kRowRef: a row of this pair outgrew its reference (rank 1 also raises rank 0's)
+  // kResident (persistent pairs, K / V of a head kept in shared memory)
+  uint64_t q_empty;                // both CTAs: every S MMA of an item has completed (one commit from each issuer)
+  uint64_t o_free[2];              // rank 0: the softmax warps of stream t in BOTH CTAs have read O of an item (16 arrives)
+  volatile uint32_t stop[2];       // per stream: one thread's reading of abort_flag, so that both warpgroups leave together
 };
 static_assert(sizeof(PairBars) <= 512, "barrier block too large");
 
 constexpr int kPairRowRefBytes = 2 * 2 * 128 * 4;  // kRowRef: first-tile maxima, [stream][half][row] fp32
 constexpr int kPairSmemBytes = 2 * kQTileBytes + kPairStages * kPairStageBytes + 1024 /*align slack*/ + 512 /*barriers*/ + kPairRowRefBytes;
 static_assert(kPairSmemBytes <= 232448, "shared memory budget");
+// kResident: between the ring and the barrier block, two 1 KB buffers per softmax warp (8 rows x 128 bytes each, in the
+// 128-byte swizzle, hence 1024-byte aligned) through which the output rows leave as TMA tile stores
+constexpr int kPairStoreStageBytes = 1024;
+constexpr int kPairStoreStages = 2;
+constexpr int kPairResidentStageBytes = 16 * kPairStoreStages * kPairStoreStageBytes;
+constexpr int kPairResidentSmemBytes = kPairSmemBytes - kPairRowRefBytes / 2 + kPairResidentStageBytes;  // row sums need 1 KB
+static_assert(kPairResidentSmemBytes <= 232448, "shared memory budget");
 
 enum : int { kWaitDrain = 8 };
 // S production: 0 = one N = 64 MMA group per 64-key half (32 key rows from each CTA); 1 = one N = 128 group per key
@@ -168,20 +179,29 @@ __global__ void combine_partials_kernel(const AttnArgs args, int n_clusters) {
 // stays fixed: every term is then at most 2^(growth of the row maximum after the first tile), exact in floating point
 // until that growth passes about 60 in log2 units.  A half tile whose terms sum to more than 2^60 marks the pair for
 // the second launch (AttnArgs::redo_list), which recomputes its four query tiles with the running-maximum kernel.
-template <bool kFp8, bool kSparse, bool kFixed = true, bool kRowRef = false>
+//
+// kResident (with kFixed, dense bf16, at most kPairStages / 2 key tiles: cross-attention to a few hundred text tokens):
+// the ring holds ALL of a head's K and V (each CTA its halves), loaded once per head, and the pair is persistent: the
+// launch has one pair per two SMs, pair c walks the contiguous items [T c / C, T (c + 1) / C) of the head-major list
+// of (head, group of four query tiles), so the head changes at most a few times per pair.  Per item only the Q tiles
+// are loaded and the O rows stored; the Q load and the first S MMAs of the next item run under the epilogue of the
+// current one (q_empty: the Q tiles are free; o_free: O has been read out of TMEM).
+template <bool kFp8, bool kSparse, bool kFixed = true, bool kRowRef = false, bool kResident = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(AttnLayout<kFixed>::kThreads, 1)
 attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                     const __grid_constant__ CUtensorMap tm_v, const AttnArgs args) {
+                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const AttnArgs args) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;  // the same offset in both CTAs: MMA descriptors are shared
   uint8_t* smem = smem_raw + (base - raw_addr);
   const uint32_t q_smem = base;
   const uint32_t ring_smem = base + 2 * kQTileBytes;
-  PairBars* bars = reinterpret_cast<PairBars*>(smem + 2 * kQTileBytes + kPairStages * kPairStageBytes);
+  constexpr int kBarsOff = 2 * kQTileBytes + kPairStages * kPairStageBytes + (kResident ? kPairResidentStageBytes : 0);
+  PairBars* bars = reinterpret_cast<PairBars*>(smem + kBarsOff);
 
   static_assert(kFixed || (!kSparse && !kPairFullS), "the running-maximum pair kernel is dense, with N = 64 S groups");
   static_assert(!kRowRef || (kFixed && !kSparse && !kPairFullS), "per-row references: dense, on the fixed-reference structure");
+  static_assert(!kResident || (kFixed && !kSparse && !kRowRef && !kFp8 && !kPairFullS), "resident K / V: dense bf16, fixed reference");
   using LY = AttnLayout<kFixed>;
   constexpr int kHelperRegs = kFixed ? kPairHelperRegs : LY::kHelperRegs;
   constexpr int kSoftmaxRegs = kFixed ? kPairSoftmaxRegs : LY::kSoftmaxRegs;
@@ -192,6 +212,13 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const uint32_t rank = cluster_ctarank();
   const int n_clusters = (args.Lq + 4 * kTile - 1) / (4 * kTile);
   int cid = blockIdx.x >> 1;
+  int item_begin = 0, item_end = 0;  // kResident: this pair's share of the items
+  if constexpr (kResident) {
+    const long long total = static_cast<long long>(n_clusters) * args.H, n_pairs = gridDim.x >> 1;
+    item_begin = static_cast<int>(total * cid / n_pairs);
+    item_end = static_cast<int>(total * (cid + 1) / n_pairs);
+    cid = item_begin;
+  }
   if constexpr (!kFixed) {
     // second launch of the two-launch online softmax: only the listed pairs are redone.  Both CTAs of a pair read the
     // same count and leave together, before any cluster-wide state exists.
@@ -269,7 +296,10 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_init(smem_u32(&bars->o_done[t][0]), 1);
       mbar_init(smem_u32(&bars->o_done[t][1]), 1);
       mbar_init(smem_u32(&bars->drain[t]), 1);
+      mbar_init(smem_u32(&bars->o_free[t]), 16);
+      bars->stop[t] = 0;
     }
+    mbar_init(smem_u32(&bars->q_empty), 2);
     bars->abort_flag = 0;
     bars->redo = 0;
     bars->early_exit = (args.status != nullptr && *reinterpret_cast<volatile int*>(args.status) != 0) ? 1u : 0u;
@@ -305,6 +335,47 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
    if (warp == kProducerWarp) {
     // =========================================================== producer (both CTAs)
     const uint32_t leader = elect_one();
+    if constexpr (kResident) {
+      bool ok = true;
+      uint32_t g = 0, hl = 0;  // items so far (phase of q_full / q_empty); heads loaded so far (phase of kv_full / kv_empty[0])
+      int prev_head = -1;
+      for (int item = item_begin; ok && item < item_end; ++item) {
+        head = item / n_clusters;
+        cl = item % n_clusters;
+        if (head != prev_head) {
+          if (prev_head >= 0) {  // every MMA that reads the previous head's K / V has completed
+            ok = warp_wait(wc, smem_u32(&bars->kv_empty[0]), (hl - 1) & 1, kWaitKvEmpty);
+            if (!ok) break;
+          }
+          for (int it = 0; it < n_it; ++it) {  // key tile `it`: K halves in stage 2 it, V columns in stage 2 it + 1
+            const int sk = 2 * it, sv = 2 * it + 1;
+            if (rank == 0) mbar_arrive_expect_tx_if(leader, smem_u32(&bars->kv_full[sk]), 2 * kKHalfBytes);
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              const int key0 = it * kTile + 64 * hf + 32 * static_cast<int>(rank);
+              tma_load_3d_pair_if(leader, ring_smem + sk * kPairStageBytes + hf * 4096, &tm_k, at0(&bars->kv_full[sk]), 0, key0, head);
+              tma_load_3d_pair_if(leader, ring_smem + sk * kPairStageBytes + 8192 + hf * 4096, &tm_k, at0(&bars->kv_full[sk]), 64, key0, head);
+            }
+            if (rank == 0) mbar_arrive_expect_tx_if(leader, smem_u32(&bars->kv_full[sv]), 2 * kVHalfBytes);
+            tma_load_3d_pair_if(leader, ring_smem + sv * kPairStageBytes, &tm_v, at0(&bars->kv_full[sv]), 64 * static_cast<int>(rank), it * kTile, head);
+          }
+          ++hl;
+          prev_head = head;
+        }
+        if (g > 0) {  // the Q tiles are free when every S MMA of the previous item has completed
+          ok = warp_wait(wc, smem_u32(&bars->q_empty), (g - 1) & 1, kWaitQEmpty);
+          if (!ok) break;
+        }
+        if (rank == 0) mbar_arrive_expect_tx_if(leader, smem_u32(&bars->q_full), 2 * 2 * kQBytes);
+        const uint32_t qbar = at0(&bars->q_full);
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          tma_load_3d_pair_if(leader, q_smem + t * kQTileBytes, &tm_q, qbar, 0, q_tile(t) * kTile, head);
+          tma_load_3d_pair_if(leader, q_smem + t * kQTileBytes + kHalfBytes, &tm_q, qbar, 64, q_tile(t) * kTile, head);
+        }
+        ++g;
+      }
+    } else {
     {
       if (rank == 0) mbar_arrive_expect_tx_if(leader, smem_u32(&bars->q_full), 2 * 2 * kQBytes);  // Q tiles of both CTAs
       const uint32_t qbar = at0(&bars->q_full);
@@ -347,9 +418,114 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         ++cnt;
       }
     }
+    }  // !kResident
     __syncwarp();
   } else if ((warp == kIssuerWarp || warp == kIssuerWarp + 1) && rank == 0) {
     // =========================================================== MMA issuers of the pair (rank 0), one warp per stream
+    if constexpr (kResident) {
+      const int t = warp - kIssuerWarp;
+      const uint32_t leader = elect_one();
+      constexpr uint32_t idesc_s = umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 0, 256, 64);
+      constexpr uint32_t idesc_pv = umma_idesc(UMMA_FMT_BF16, UMMA_FMT_BF16, 0, 1, 256, 128);
+      const uint64_t q_desc = umma_desc_sw128(q_smem + t * kQTileBytes, 16, 1024);
+      const uint64_t kv_desc0 = umma_desc_sw128(ring_smem, 16, 1024);
+      const uint32_t s_tmem = tmem + t * kTile;
+      const uint32_t o_tmem = tmem + 256 + t * kTile;
+      uint32_t p_cnt[2] = {0, 0};  // P halves consumed so far (all items): the phase of p_full
+      uint32_t pv_cnt = 0;         // P V groups of the current item: the first overwrites O
+      uint32_t g = 0, hl = 0;
+      int prev_head = -1;
+      bool ok = true;
+      auto commit_both = [&](const void* local) {
+        umma_pair_commit_if(leader, smem_u32(local));
+        umma_pair_commit_if(leader, at_peer(local));
+      };
+      auto issue_s = [&](int hf, int sk) {
+        const uint64_t kd = kv_desc0 + static_cast<uint64_t>((sk * kPairStageBytes + hf * 4096) >> 4);
+        const uint32_t d = s_tmem + hf * 64;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t offq = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
+          const uint32_t offk = ((k >> 2) * 8192 + (k & 3) * 32) >> 4;
+          umma_pair_bf16_ss_if(leader, d, q_desc + offq, kd + offk, idesc_s, k > 0);
+        }
+        commit_both(&bars->s_full[t][hf]);
+      };
+      auto issue_pv = [&](int hf, int sv) {
+        const uint64_t vd = kv_desc0 + static_cast<uint64_t>((sv * kPairStageBytes + hf * 8192) >> 4);
+        const uint32_t a = s_tmem + hf * 64;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_pair_bf16_ts_if(leader, o_tmem, a + k * 8, vd + (k * 2048 >> 4), idesc_pv, (pv_cnt > 0 || k > 0) ? 1u : 0u);
+        ++pv_cnt;
+      };
+      for (int item = item_begin; ok && item < item_end; ++item) {
+        head = item / n_clusters;
+        cl = item % n_clusters;
+        const bool fresh = head != prev_head;  // this head's K / V is being loaded: wait for each stage at its first use
+        if (fresh) {
+          ++hl;
+          prev_head = head;
+        }
+        const uint32_t kv_par = (hl - 1) & 1;
+        const bool last_of_head = item + 1 < item_end && (item + 1) / n_clusters != head;
+        H3A_STAMP(2 + t, g * n_it * 2, 4);
+        ok = warp_wait(wc, smem_u32(&bars->q_full), g & 1, kWaitQFull);
+        if (!ok) break;
+        H3A_STAMP(2 + t, g * n_it * 2, 5);
+        if (fresh) {
+          ok = warp_wait(wc, smem_u32(&bars->kv_full[0]), kv_par, kWaitKvFullK);
+          if (!ok) break;
+        }
+        tc_fence_after_sync();
+        pv_cnt = 0;
+        issue_s(0, 0);  // in TMEM these follow the previous item's last P V: MMAs run in issue order
+        issue_s(1, 0);
+        for (int it = 0; ok && it < n_it; ++it) {
+          const bool has_next = (it + 1 < n_it);
+          const int sv = 2 * it + 1, sk = 2 * it + 2;
+          if (!has_next) commit_both(&bars->q_empty);  // every S MMA of the item has been issued
+          if (fresh) {
+            ok = warp_wait(wc, smem_u32(&bars->kv_full[sv]), kv_par, kWaitKvFullV);
+            if (!ok) break;
+            tc_fence_after_sync();
+          }
+          bool k_ready = !fresh;
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            H3A_STAMP(2 + t, (g * n_it + it) * 2 + hf, 0);
+            ok = warp_wait(wc, smem_u32(&bars->p_full[t][hf]), p_cnt[hf] & 1, kWaitPFull);
+            if (!ok) break;
+            H3A_STAMP(2 + t, (g * n_it + it) * 2 + hf, 1);
+            ++p_cnt[hf];
+            if (pv_cnt == 0 && g > 0) {
+              // the first P V of an item overwrites O in both CTAs: their softmax warps must have read the previous item's
+              ok = warp_wait(wc, smem_u32(&bars->o_free[t]), (g - 1) & 1, kWaitOFree);
+              if (!ok) break;
+            }
+            tc_fence_after_sync();
+            H3A_STAMP(2 + t, (g * n_it + it) * 2 + hf, 2);
+            issue_pv(hf, sv);
+            H3A_STAMP(2 + t, (g * n_it + it) * 2 + hf, 3);
+            if (has_next && !k_ready) {
+              ok = warp_wait(wc, smem_u32(&bars->kv_full[sk]), kv_par, kWaitKvFullK);
+              if (!ok) break;
+              k_ready = true;
+              tc_fence_after_sync();
+            }
+            if (has_next) issue_s(hf, sk);
+          }
+        }
+        if (!ok) break;
+        commit_both(&bars->o_full[t]);  // one phase per item: every MMA of the stream's item has completed
+        if (last_of_head) commit_both(&bars->kv_empty[0]);  // ... and with it every reader of this head's K / V
+        ++g;
+      }
+      if (ok) {  // nothing of this issuer is still on its way to the peer CTA once this has arrived
+        umma_pair_commit_if(leader, smem_u32(&bars->drain[t]));
+        warp_wait(wc, smem_u32(&bars->drain[t]), 0, kWaitDrain);
+      }
+    } else
     if (n_it > 0) {
       const int t = warp - kIssuerWarp;
       const uint32_t leader = elect_one();
@@ -461,6 +637,167 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
    }
   } else {
     setmaxnreg_inc<kSoftmaxRegs>();
+    if constexpr (kResident) {
+    // =========================================================== softmax, fixed reference, persistent over items
+    const int wg = warp >> 2;
+    const int t = wg & 1;
+    const int hf = wg >> 1;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t sb = tmem + lane_base + t * kTile + hf * 64;
+    const uint32_t o_addr = tmem + lane_base + 256 + t * kTile + hf * 64;
+    const int last_tile = args.n_kv_tiles - 1;
+    const int tail = args.Lk - last_tile * kTile;
+    const uint32_t p_bar = at0(&bars->p_full[t][hf]);
+    const uint32_t free_bar = at0(&bars->o_free[t]);
+    const float m_ref = args.fixed_m;
+    const float c = args.scale_log2;
+    // the row sums of the stream's two warpgroups meet here (the Q tiles are being reloaded at that time)
+    float* lbuf = reinterpret_cast<float*>(smem + kBarsOff + 512) + t * 128;
+    uint32_t j = 0;  // key tiles processed so far, all items: the phase of s_full
+    uint32_t g = 0;  // items so far: the phase of o_full / o_free
+    bool ok = true;
+    uint32_t s[64];
+    for (int item = item_begin; item < item_end; ++item) {
+      head = item / n_clusters;
+      cl = item % n_clusters;
+      const int q_row = q_tile(t) * kTile + row;
+      const bool row_valid = q_row < args.Lq;
+      __nv_bfloat16* orow = out_row_ptr(args, q_row, head) + 64 * hf;
+      float l_sum = 0.0f;
+      for (int it = 0; ok && it < n_it; ++it) {
+        if (row == 0 && t == 0) H3A_STAMP(hf, j, 0);
+        ok = warp_wait(wc, smem_u32(&bars->s_full[t][hf]), j & 1, kWaitSFull);
+        if (!ok) break;
+        if (row == 0 && t == 0) H3A_STAMP(hf, j, 1);
+        tc_fence_after_sync();
+        tmem_ld32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tmem_ld32(sb + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+        tmem_wait_ld();
+        reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+        if (it == last_tile && tail < kTile) {
+          const int valid = tail - hf * 64;
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (i >= valid) s[i] = 0xFF800000u;  // -inf
+        }
+        if (row == 0 && t == 0) H3A_STAMP(hf, j, 2);
+        l_sum += exp_half_tile<false>(s, c, m_ref);
+        if (row == 0 && t == 0) H3A_STAMP(hf, j, 3);
+        tmem_st32(sb, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(p_bar);
+        if (row == 0 && t == 0) H3A_STAMP(hf, j, 4);
+        ++j;
+      }
+      // ---- epilogue of the item.  Two named barriers that every thread of the stream's two warpgroups always reaches
+      //      carry the exchange of the row sums (half 0 leaves its sum, half 1 swaps it for its own); between them ONE
+      //      thread reads the abort flag for the stream, so that both warpgroups leave the item loop together.
+      bool have = ok;
+      if (row == 0 && t == 0) H3A_STAMP(hf, 32 + g, 0);
+      if (have) {
+        have = warp_wait(wc, smem_u32(&bars->o_full[t]), g & 1, kWaitOFull);
+        if (have) tc_fence_after_sync();
+      }
+      if (row == 0 && t == 0) H3A_STAMP(hf, 32 + g, 1);
+      if (hf == 0) lbuf[row] = l_sum;
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");
+      float l_other = 0.0f;
+      if (hf == 1) {
+        l_other = lbuf[row];
+        lbuf[row] = l_sum;
+      } else if (row == 0) {
+        bars->stop[t] = bars->abort_flag;
+      }
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(256) : "memory");
+      if (hf == 0) l_other = lbuf[row];
+      const bool stop = bars->stop[t] != 0u;
+      if (row == 0 && t == 0) H3A_STAMP(hf, 32 + g, 2);
+      if (have) {
+        // O leaves TMEM first: the next item's first P V may overwrite it while the rows are converted and stored
+        tmem_ld32(o_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tmem_ld32(o_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+        tmem_wait_ld();
+        reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        reg_fence32(*reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      }
+      if (row == 0 && t == 0) H3A_STAMP(hf, 32 + g, 3);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(free_bar);
+      if (row == 0 && t == 0) H3A_STAMP(hf, 32 + g, 4);
+      if (have) {
+        const float l_tot = l_sum + l_other;
+        if (hf == 0 && row_valid) check_row_sum(args, l_tot, false);
+        const float inv = 1.0f / l_tot;
+        if (row_valid && args.lse && hf == 0)
+          args.lse[static_cast<long long>(head) * args.Lq + q_row] = (m_ref + log2f(l_tot)) * 0.6931471805599453f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)  // 64 columns of this row as 8 chunks of 16 bytes (slot i <= 2 i: already consumed)
+          s[i] = pack_bf16x2(__uint_as_float(s[2 * i]) * inv, __uint_as_float(s[2 * i + 1]) * inv);
+        if (row == 0 && t == 0) H3A_STAMP(hf, 32 + g, 5);
+        // A thread owns a row, so a plain store instruction of the warp would touch 32 rows = 32 lines with 16 bytes
+        // each, and the warps would sit in the store queue: an SM moves only about 18 bytes per cycle towards L2
+        // (measured: 3,600 to 4,600 cycles per item for its 64 KB, however the stores are grouped).  So the rows leave
+        // through the copy engine instead: 8 rows at a time the warp writes its 128-byte half rows into one of its two
+        // 1 KB buffers (16-byte slots swizzled by the row, which is the tensor map's 128-byte swizzle and free of bank
+        // conflicts), one lane issues a TMA tile store of 8 rows x 64 columns and goes on; a buffer is rewritten once
+        // the copy engine has read it.  Rows beyond Lq are clipped by the tensor map.
+        const uint32_t stg = smem_u32(smem + 2 * kQTileBytes + kPairStages * kPairStageBytes) + warp * (kPairStoreStages * kPairStoreStageBytes);
+        const int tile_row0 = q_tile(t) * kTile + quarter * 32;
+        if (args.o_n_ranks <= 1) {
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const uint32_t buf = stg + (p & 1) * kPairStoreStageBytes;
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // the store that last used this buffer
+            __syncwarp();
+            if ((lane >> 3) == p) {
+              const uint32_t r8 = lane & 7;
+#pragma unroll
+              for (uint32_t ch = 0; ch < 8; ++ch)
+                st_shared_v4(buf + r8 * 128 + ((ch ^ r8) << 4), s[4 * ch], s[4 * ch + 1], s[4 * ch + 2], s[4 * ch + 3]);
+              fence_proxy_async_smem();  // these rows are read by the copy engine
+            }
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&tm_o, buf, 64 * hf, tile_row0 + p * 8, head);
+              tma_store_commit();
+            }
+          }
+        } else {
+          // rows that go to other GPUs' memory (one base pointer per rank): plain stores, regrouped through the buffer
+          // so that an instruction writes 4 whole half rows
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            if ((lane >> 3) == p) {
+              const uint32_t r8 = lane & 7;
+#pragma unroll
+              for (uint32_t ch = 0; ch < 8; ++ch)
+                st_shared_v4(stg + r8 * 128 + ((ch ^ r8) << 4), s[4 * ch], s[4 * ch + 1], s[4 * ch + 2], s[4 * ch + 3]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const uint32_t r8 = (lane >> 3) + 4 * i, ch = lane & 7;
+              uint4 w;
+              ld_shared_v4(stg + r8 * 128 + ((ch ^ r8) << 4), w);
+              const int rg = tile_row0 + p * 8 + static_cast<int>(r8);
+              if (rg < args.Lq) *reinterpret_cast<uint4*>(out_row_ptr(args, rg, head) + 64 * hf + ch * 8) = w;
+            }
+            __syncwarp();
+          }
+        }
+      }
+      if (row == 0 && t == 0) H3A_STAMP(hf, 32 + g, 7);
+      if (stop) break;
+      ++g;
+    }
+    if (lane == 0) tma_store_wait_all();  // this lane's tile stores are complete before the CTA's shared memory goes away
+    } else
     if constexpr (kFixed) {
     // =========================================================== softmax, fixed reference: one warpgroup per (stream, half)
     const int wg = warp >> 2;
@@ -487,7 +824,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     bool ok = true;
     bool met = false;   // kRowRef: this warp has been to the exchange of the first-tile maxima
     bool over = false;  // kRowRef: a half tile of this row summed past what its reference can represent
-    float* rowref = reinterpret_cast<float*>(smem + 2 * kQTileBytes + kPairStages * kPairStageBytes + 512);
+    float* rowref = reinterpret_cast<float*>(smem + kBarsOff + 512);
     uint32_t s[64];
     for (int it = 0; ok && it < n_it; ++it) {
       const int e = entry_at(it);

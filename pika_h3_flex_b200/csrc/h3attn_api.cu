@@ -273,26 +273,48 @@ SplitPlan plan_split(int64_t Lq, int64_t Lk, int64_t H) {
   return sp;
 }
 
-template <bool kFp8, bool kSparse = false, bool kFixed = true, bool kRowRef = false>
-int32_t launch_attn_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a, cudaStream_t st) {
+// Dense bf16 launches with a logit bound and at most kPairStages / 2 key tiles (cross-attention to a few hundred text
+// tokens) keep a head's K / V in the shared memory of a persistent CTA pair (attn_fwd_pair.cuh, kResident), once there
+// are at least as many groups of four query tiles as CTA pairs fit the device.  H3A_RESIDENT=0 in the environment
+// (read once) sends them to the single-CTA kernel instead, for side-by-side measurements.
+bool resident_kernel_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("H3A_RESIDENT");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
+bool resident_kernel_applies(int32_t mode, bool fixed, int64_t Lq, int64_t Lk, int64_t H) {
+  if (mode != H3A_MODE_DENSE_BF16 || !fixed || !pair_kernel_enabled() || !resident_kernel_enabled()) return false;
+  const int64_t n_kv = (Lk + 127) / 128, items = (Lq + 511) / 512 * H;
+  const int sms = sm_count_of_current_device();
+  return n_kv >= 1 && n_kv <= h3a::kPairStages / 2 && sms >= 2 && items >= sms / 2;
+}
+
+// `mo`: tensor map of the output for the kernels that store through the copy engine (kResident); the others ignore it
+template <bool kFp8, bool kSparse = false, bool kFixed = true, bool kRowRef = false, bool kResident = false>
+int32_t launch_attn_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& a, cudaStream_t st,
+                         const CUtensorMap* mo = nullptr) {
+  constexpr int kSmem = kResident ? h3a::kPairResidentSmemBytes : h3a::kPairSmemBytes;
   static std::once_flag once[kMaxDevices];
   static cudaError_t attr_err[kMaxDevices];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return H3A_ERR_LAUNCH;
   std::call_once(once[dev], [dev] {
-    cudaError_t e = cudaFuncSetAttribute(h3a::attn_fwd_pair_kernel<kFp8, kSparse, kFixed, kRowRef>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         h3a::kPairSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(h3a::attn_fwd_pair_kernel<kFp8, kSparse, kFixed, kRowRef, kResident>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmem);
     cudaFuncAttributes fa;
-    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, h3a::attn_fwd_pair_kernel<kFp8, kSparse, kFixed, kRowRef>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, h3a::attn_fwd_pair_kernel<kFp8, kSparse, kFixed, kRowRef, kResident>);
     if (e == cudaSuccess && fa.numRegs < h3a::AttnLayout<kFixed>::kLaunchRegs) e = cudaErrorLaunchOutOfResources;
     attr_err[dev] = e;
   });
   if (attr_err[dev] != cudaSuccess) return H3A_ERR_LAUNCH;
   const unsigned n_clusters = static_cast<unsigned>((a.Lq + 511) / 512);
   unsigned pairs = n_clusters * static_cast<unsigned>(a.H);
-  const bool split = !kSparse && a.kv_splits > 1;
+  const bool split = !kSparse && !kResident && a.kv_splits > 1;
+  if (kResident) pairs = std::min(pairs, static_cast<unsigned>(sm_count_of_current_device() / 2));  // persistent: one pair per two SMs
   if (split) pairs = static_cast<unsigned>(a.split_begin) + (pairs - static_cast<unsigned>(a.split_begin)) * static_cast<unsigned>(a.kv_splits);
-  h3a::attn_fwd_pair_kernel<kFp8, kSparse, kFixed, kRowRef><<<2u * pairs, h3a::AttnLayout<kFixed>::kThreads, h3a::kPairSmemBytes, st>>>(mq, mk, mv, a);  // cluster shape (2,1,1) is the kernel's
+  h3a::attn_fwd_pair_kernel<kFp8, kSparse, kFixed, kRowRef, kResident><<<2u * pairs, h3a::AttnLayout<kFixed>::kThreads, kSmem, st>>>(mq, mk, mv, mo ? *mo : mq, a);  // cluster shape (2,1,1) is the kernel's
   if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
   if (split) {
     const unsigned groups = n_clusters * static_cast<unsigned>(a.H) - static_cast<unsigned>(a.split_begin);
@@ -389,6 +411,14 @@ int32_t attn_fwd_impl(const h3a_attn_params* p, void* workspace, size_t workspac
                                                                                          a.n_qpairs, p->nnz, a.nkb, plan, plan_cnt, p->status_word);
     if (cudaGetLastError() != cudaSuccess) return H3A_ERR_LAUNCH;
     return fixed ? launch_attn<false, true, true>(mq, mk, mv, a, st) : launch_attn<false, true, false>(mq, mk, mv, a, st);
+  }
+  if (resident_kernel_applies(p->mode, fixed, p->Lq, p->Lk, p->H)) {
+    a.split_begin = static_cast<int>((p->Lq + 511) / 512 * p->H);
+    a.kv_splits = 1;
+    if ((rc = make_map(&mk, p->k, false, p->Lk, p->H, p->k_stride_l, p->k_stride_h, h3a::kPairKBoxRows)) != H3A_OK) return rc;
+    CUtensorMap mo;  // output rows leave as tile stores of 8 rows x 64 columns (not used when they go to several ranks)
+    if ((rc = make_map(&mo, p->o, false, p->Lq, p->H, p->o_stride_l, p->o_stride_h, 8)) != H3A_OK) return rc;
+    return launch_attn_pair<false, false, true, false, true>(mq, mk, mv, a, st, &mo);
   }
   if (fixed && pair_kernel_enabled() && a.n_kv_tiles >= kPairMinKeyTiles) {
     a.split_begin = static_cast<int>((p->Lq + 511) / 512 * p->H);
@@ -539,13 +569,14 @@ int32_t h3a_attn_kernel_choice(const h3a_attn_params* p, int32_t* choice) {
   if (p->Lq <= 0 || p->Lk <= 0 || p->H <= 0) return H3A_ERR_SHAPE;
   const bool fixed = fixed_reference_ok(p->logit_bound);
   const int64_t nqb = (p->Lq + 127) / 128, nkb = (p->Lk + 127) / 128;
-  bool pairs = pair_kernel_enabled() && nkb >= kPairMinKeyTiles;
+  const bool resident = resident_kernel_applies(p->mode, fixed, p->Lq, p->Lk, p->H);
+  bool pairs = (pair_kernel_enabled() && nkb >= kPairMinKeyTiles) || resident;
   if (p->mode == H3A_MODE_BLOCK_SPARSE)
     pairs = pairs && fixed && static_cast<double>(p->nnz) / (static_cast<double>(nqb) * static_cast<double>(nkb)) >= kPairMinDensity;
   int32_t c = 0;
   if (pairs) c |= H3A_KERNEL_CTA_PAIRS;
   if (fixed) c |= H3A_KERNEL_FIXED_REFERENCE;
-  if (pairs && fixed && p->mode != H3A_MODE_BLOCK_SPARSE && p->workspace && aligned16(p->workspace)) {
+  if (pairs && fixed && !resident && p->mode != H3A_MODE_BLOCK_SPARSE && p->workspace && aligned16(p->workspace)) {
     const SplitPlan sp = plan_split(p->Lq, p->Lk, p->H);
     if (sp.kv_splits > 1 && p->workspace_bytes >= sp.bytes) c |= H3A_KERNEL_SPLIT_LAST_WAVE;
   }

@@ -629,11 +629,15 @@ def test_config4_cross_attention_shape(h):
 
 
 # ------------------------------------------------------------------------------------------ persistent CTAs
-_PERSIST_CASES = [  # (Lq, Lk, heads, fp8): more (head, query-tile pair) items than SMs, the last pair of a head half empty
+_PERSIST_CASES = [  # (Lq, Lk, heads, fp8): more (head, query-tile group) items than SMs, the last pair of a head half empty
     (15360, 640, 6, False),   # 360 items of 5 key tiles: the 5-stage K/V ring wraps inside and across items
     (10000, 552, 5, False),   # 79 query tiles: every head ends on a pair with one tile; key tail of 40
-    (9000, 130, 9, False),    # 2 key tiles per item, the second nearly empty
     (8192, 1024, 8, True),    # FP8-QK below the CTA-pair threshold
+    # at most 4 key tiles: K / V resident in a persistent CTA pair, which changes head a few times
+    (20000, 512, 4, False),   # 160 groups of four query tiles on 74 pairs; the last group of a head is short
+    (16000, 300, 5, False),   # 3 key tiles, the last with 44 keys
+    (33000, 100, 3, False),   # one key tile with a tail
+    (9000, 130, 9, False),    # 2 key tiles, the second nearly empty
 ]
 _PERSIST_CHILD = r"""
 import sys, torch
@@ -654,17 +658,18 @@ torch.save(outs, %(path)r)
 
 
 def test_persistent_ctas_give_the_same_rows_as_one_cta_per_item(h, tmp_path):
-    """Single-CTA kernel with a fixed softmax reference (few key tiles per item: cross-attention shapes): by default one
-    CTA per SM walks the items; H3A_PERSIST=0 (read once per process, so a child process runs it) launches one CTA per
-    item.  Both do the same arithmetic per row in the same order: the outputs must be bit-identical, and match the
-    oracle on sampled rows."""
+    """Fixed softmax reference with few key tiles per item (cross-attention shapes): by default the CTAs are persistent -
+    one CTA per SM walks the items of the single-CTA kernel, and with at most 4 key tiles a CTA pair keeps a head's K / V
+    in shared memory.  H3A_PERSIST=0 H3A_RESIDENT=0 (read once per process, so a child process runs it) launches one
+    single-CTA block per item.  The single-CTA kernel does the same arithmetic per row in the same order either way
+    (bit-identical outputs); the pair kernel agrees to rounding; all match the oracle on sampled rows."""
     import subprocess
     import sys
 
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     path = tmp_path / "per_item.pt"
     code = _PERSIST_CHILD % {"root": root, "cases": _PERSIST_CASES, "path": str(path)}
-    subprocess.run([sys.executable, "-c", code], check=True, env=dict(os.environ, H3A_PERSIST="0"), timeout=300)
+    subprocess.run([sys.executable, "-c", code], check=True, env=dict(os.environ, H3A_PERSIST="0", H3A_RESIDENT="0"), timeout=300)
     per_item = torch.load(path)
     for i, (Lq, Lk, H, fp8) in enumerate(_PERSIST_CASES):
         g = torch.Generator().manual_seed(500 + i)
@@ -674,8 +679,11 @@ def test_persistent_ctas_give_the_same_rows_as_one_cta_per_item(h, tmp_path):
         status = torch.zeros(1, dtype=torch.int32, device="cuda")
         out = h.joint_attention(dev(q), dev(k), dev(v), None, mode=h.MODE_FP8_QK if fp8 else h.MODE_DENSE_BF16, status_word=status)
         assert h.read_status(status) == 0
-        assert torch.equal(out.cpu(), per_item[i]), (Lq, Lk, H, fp8)
-        rows = torch.cat([torch.arange(0, Lq, 397), torch.tensor([Lq - 1, Lq - 129, 255, 256])])
+        if Lk > 512:  # the same kernel, persistent or not: the same arithmetic in the same order
+            assert torch.equal(out.cpu(), per_item[i]), (Lq, Lk, H, fp8)
+        else:         # CTA pairs with resident K / V against the single-CTA kernel
+            assert float((out.cpu().float() - per_item[i].float()).abs().max()) <= 1e-3, (Lq, Lk, H)
+        rows = torch.cat([torch.arange(0, Lq, 397), torch.tensor([Lq - 1, Lq - 129, 255, 256, 511, 512])])
         ref = O.attention(O.rms_norm(q[rows].float()), O.rms_norm(k.float()), v.float())
         if fp8:
             check(out[rows], ref, mx=FP8_MAX, mean=FP8_MEAN, rel=FP8_REL)
