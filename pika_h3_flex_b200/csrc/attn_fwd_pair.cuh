@@ -340,8 +340,10 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       uint32_t g = 0, hl = 0;  // items so far (phase of q_full / q_empty); heads loaded so far (phase of kv_full / kv_empty[0])
       int prev_head = -1;
       for (int item = item_begin; ok && item < item_end; ++item) {
-        head = item / n_clusters;
-        cl = item % n_clusters;
+        if (item > item_begin && ++cl == n_clusters) {  // (head, cl) = (item / n_clusters, item % n_clusters), without dividing
+          cl = 0;
+          ++head;
+        }
         if (head != prev_head) {
           if (prev_head >= 0) {  // every MMA that reads the previous head's K / V has completed
             ok = warp_wait(wc, smem_u32(&bars->kv_empty[0]), (hl - 1) & 1, kWaitKvEmpty);
@@ -460,15 +462,17 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         ++pv_cnt;
       };
       for (int item = item_begin; ok && item < item_end; ++item) {
-        head = item / n_clusters;
-        cl = item % n_clusters;
+        if (item > item_begin && ++cl == n_clusters) {
+          cl = 0;
+          ++head;
+        }
         const bool fresh = head != prev_head;  // this head's K / V is being loaded: wait for each stage at its first use
         if (fresh) {
           ++hl;
           prev_head = head;
         }
         const uint32_t kv_par = (hl - 1) & 1;
-        const bool last_of_head = item + 1 < item_end && (item + 1) / n_clusters != head;
+        const bool last_of_head = item + 1 < item_end && cl + 1 == n_clusters;
         H3A_STAMP(2 + t, g * n_it * 2, 4);
         ok = warp_wait(wc, smem_u32(&bars->q_full), g & 1, kWaitQFull);
         if (!ok) break;
@@ -660,8 +664,10 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     bool ok = true;
     uint32_t s[64];
     for (int item = item_begin; item < item_end; ++item) {
-      head = item / n_clusters;
-      cl = item % n_clusters;
+      if (item > item_begin && ++cl == n_clusters) {
+        cl = 0;
+        ++head;
+      }
       const int q_row = q_tile(t) * kTile + row;
       const bool row_valid = q_row < args.Lq;
       __nv_bfloat16* orow = out_row_ptr(args, q_row, head) + 64 * hf;

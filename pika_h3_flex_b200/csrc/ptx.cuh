@@ -126,6 +126,14 @@ __device__ __forceinline__ void tma_load_3d_if(uint32_t pred, uint32_t dst, cons
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(pred)
       : "memory");
 }
+// ask for one box of a 3-D tensor to be brought into L2 (no destination, no completion to wait for)
+__device__ __forceinline__ void tma_prefetch_3d_if(uint32_t pred, const CUtensorMap* m, int c0, int c1, int c2) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %4, 0;\n\t"
+      "@q cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n\t}"
+      ::"l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(c2), "r"(pred)
+      : "memory");
+}
 // 3-D tiled store shared -> global (bulk group); rows beyond the tensor extent are clipped.
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, uint32_t src, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
