@@ -63,6 +63,11 @@ ALSO = ("cfg2_fp8", "cfg3_sparse", "cfg3_sparse20", "cfg4_cross")  # N = 1: shor
 # captured one; otherwise `traffic` is null.
 NCU_TRAFFIC = {
     "dense_bf16": ("attn_fwd_pair_kernel", 250.9e6, 16384 * 16, "profiles/attn_fwd_dense_bf16_prof_dense.md"),
+    "fp8_qk": ("attn_fwd_pair_kernel", 176.4e6, 16384 * 16, "profiles/attn_fwd_pair_fp8_prof_fp8.md"),
+    "cross_bf16": ("attn_fwd_pair_kernel", 94.6e6, 16384 * 16, "profiles/attn_fwd_cross_attention_prof_cross.md"),
+    # block-sparse: only the literal-rule mask at about 7 % density on the single-CTA kernel has a capture; a launch on
+    # CTA pairs (denser masks) reports null
+    "block_sparse": ("attn_fwd_kernel", 1113.8e6, 96256 * 8, "profiles/attn_fwd_block_sparse_7pct_prof_sparse7.md"),
 }
 
 
