@@ -722,6 +722,9 @@ def run_ours(args):
             e2e["copy_floor"] = ("plain asynchronous copies of the same shards, both directions at once, every rank at once (slowest rank); "
                                  "per rank H2D alone %.1f GB/s, D2H alone %.1f GB/s" % (h2d_gbs, d2h_gbs))
             e2e["ms_over_copy_floor"] = e2e_ms / floor_ms
+            e2e["bound"] = "copy" if floor_ms >= ms_per_step else "compute"  # which of the two the call cannot beat: the plain copies or the resident step
+            if hasattr(host_attn, "bound"):
+                e2e["bound_estimated_from_shape"] = host_attn.bound
             stages = getattr(host_attn, "stage_ms", None)
             if stages is not None:
                 e2e["stages_ms"] = stages()

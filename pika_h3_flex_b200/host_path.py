@@ -48,16 +48,35 @@ def default_head_groups(H: int, copy_to_compute: float = 0.75) -> list:
     return groups
 
 
+def copy_to_compute_estimate(L: int, mode: int = _lib.MODE_DENSE_BF16, density: float = 1.0, link_gbs: float = 50.0) -> float:
+    """Time to bring one head's Q, K and V over the host link / time to compute that head, from the shape alone.
+    Rates measured on B200 under its power cap: 1.3 PFLOP/s dense bf16, 1.5 FP8-QK, 1.1 on the kept tiles of a
+    block-sparse mask; ``link_gbs`` is what one direction of the host link gives this rank (about 50 GB/s alone on
+    PCIe 5 x16, half that with four ranks copying at once).  Dense bf16 at the 480p-like length: 0.79 (0.75 measured);
+    the literal block-sparse rule at the 720p-like length (7 % of the tiles): 3.6 - the call is bound by the copies,
+    whatever the kernel does."""
+    rate = {_lib.MODE_DENSE_BF16: 1.3e15, _lib.MODE_FP8_QK: 1.5e15, _lib.MODE_BLOCK_SPARSE: 1.1e15}.get(mode, 1.3e15)
+    copy_s = 3.0 * L * ops.HEAD_DIM * 2 / (link_gbs * 1e9)
+    compute_s = 4.0 * L * L * ops.HEAD_DIM * max(density, 1e-6) / rate
+    return copy_s / compute_s
+
+
 class HostJointAttention:
     """``out_host = HostJointAttention(L, H)(q_host, k_host, v_host, rope, out_host)`` with pinned ``[L, H, 128]``
-    bf16 host tensors.  Device staging buffers and streams are created once and reused."""
+    bf16 host tensors.  Device staging buffers and streams are created once and reused.  ``copy_to_compute`` (default:
+    estimated from the length, the mode and the block index's density) sizes the head groups of the pipeline;
+    ``bound`` says which side the call waits for, "copy" or "compute"."""
 
     def __init__(self, L: int, H: int, mode: int = _lib.MODE_DENSE_BF16, block_index: Optional[ops.BlockIndex] = None,
-                 head_groups: Optional[Sequence[int]] = None, device=None, copy_to_compute: float = 0.75,
+                 head_groups: Optional[Sequence[int]] = None, device=None, copy_to_compute: Optional[float] = None,
                  status: Optional[ops.StatusWord] = None):
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.status = status if status is not None else ops.StatusWord(self.device)
         self.L, self.H, self.mode, self.block_index = L, H, mode, block_index
+        if copy_to_compute is None:
+            copy_to_compute = copy_to_compute_estimate(L, mode, block_index.density if block_index is not None else 1.0)
+        self.copy_to_compute = float(copy_to_compute)
+        self.bound = "copy" if self.copy_to_compute >= 1.0 else "compute"
         if head_groups is None:
             head_groups = default_head_groups(H, copy_to_compute)
         if sum(head_groups) != H:

@@ -181,3 +181,22 @@ def test_memcpy2d_argument_validation(lib):
     assert lib.h3a_memcpy2d_async(None, 16, a, 16, 16, 1, 0, None) == _lib.H3A_ERR_ARG
     assert lib.h3a_memcpy2d_async(a, 8, a, 16, 16, 1, 0, None) == _lib.H3A_ERR_ARG  # width beyond the pitch
     assert lib.h3a_memcpy2d_async(a, 16, a, 16, 0, 1, 0, None) == _lib.H3A_ERR_ARG
+
+
+def test_host_buffer_path_knows_when_the_copies_bound_it(lib):
+    """Head groups of the host-buffer pipeline follow the ratio of copy time to compute time per head, estimated from
+    the length, the mode and the mask's density: dense bf16 at the 480p-like length is bound by the kernel (0.79; 0.75
+    measured), the literal block-sparse rule at the 720p-like length (7 % of the tiles) by the copies."""
+    from pika_h3_flex_b200.host_path import copy_to_compute_estimate, default_head_groups
+
+    dense = copy_to_compute_estimate(49384)
+    assert 0.7 < dense < 0.9
+    bi = ops.build_block_index((31, 48, 84), 1024, (2, 8, 8))
+    sparse = copy_to_compute_estimate(31 * 48 * 84 + 1024, _lib.MODE_BLOCK_SPARSE, bi.density)
+    assert sparse > 3.0
+    assert copy_to_compute_estimate(49384, link_gbs=25.0) > 1.5  # four ranks sharing the host link
+    for ratio in (dense, sparse):
+        groups = default_head_groups(40, ratio)
+        assert sum(groups) == 40 and min(groups) >= 1
+    # bound by the copies: nothing to hide a long copy behind, so the groups stay small
+    assert max(default_head_groups(40, sparse)) <= 4

@@ -858,6 +858,31 @@ def test_pair_kernel_skips_work_when_the_status_word_is_already_set(h):
     check(out, O.attention(q.float(), k.float(), v.float()))
 
 
+@pytest.mark.parametrize("Lq,Lk,H", [(20000, 512, 4), (15360, 640, 6)])
+def test_persistent_kernels_skip_work_when_the_status_word_is_already_set(h, Lq, Lk, H):
+    """The same for the persistent forms (CTA pairs with resident K / V; one single-CTA block per SM): every block leaves
+    before it touches TMEM or the output, and the next launch on a cleared word is complete."""
+    g = torch.Generator().manual_seed(971)
+    q = torch.randn(Lq, H, 128, generator=g).bfloat16()
+    k = torch.randn(Lk, H, 128, generator=g).bfloat16()
+    v = torch.randn(Lk, H, 128, generator=g).bfloat16()
+    st = torch.full((1,), 0x105, dtype=torch.int32, device="cuda")
+    out = torch.full((Lq, H, 128), 7.0, dtype=torch.bfloat16, device="cuda")
+    h.attn_fwd(dev(q), dev(k), dev(v), out=out, logit_bound=PAIR_BOUND, status_word=st)
+    torch.cuda.synchronize()
+    assert bool((out == 7.0).all())
+    assert int(st.item()) == 0x105
+    st.zero_()
+    h.attn_fwd(dev(q), dev(k), dev(v), out=out, logit_bound=PAIR_BOUND, status_word=st)
+    assert h.read_status(st) == 0
+    rows = torch.cat([torch.arange(0, Lq, 509), torch.tensor([Lq - 1])])
+    check(out[rows], O.attention(q[rows].float(), k.float(), v.float()))
+    out2, lse = h.attn_fwd(dev(q), dev(k), dev(v), logit_bound=PAIR_BOUND, return_lse=True)  # the log-sum-exp of the persistent forms
+    assert torch.equal(out2, out)
+    sc = (q[rows].float().transpose(0, 1) @ k.float().transpose(0, 1).transpose(1, 2)) / 128 ** 0.5  # [H, rows, Lk]
+    assert float((lse[:, rows].cpu() - torch.logsumexp(sc, dim=-1)).abs().max()) <= 2e-3
+
+
 def test_pair_kernel_repeated_launches_are_bit_identical(h):
     q, k, v = bf16_inputs(2304, 4, 980, 3000)
     qd, kd, vd = dev(q), dev(k), dev(v)
