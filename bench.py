@@ -64,7 +64,7 @@ ALSO = ("cfg2_fp8", "cfg3_sparse", "cfg3_sparse20", "cfg4_cross")  # N = 1: shor
 NCU_TRAFFIC = {
     "dense_bf16": ("attn_fwd_pair_kernel", 250.9e6, 16384 * 16, "profiles/attn_fwd_dense_bf16_prof_dense.md"),
     "fp8_qk": ("attn_fwd_pair_kernel", 176.4e6, 16384 * 16, "profiles/attn_fwd_pair_fp8_prof_fp8.md"),
-    "cross_bf16": ("attn_fwd_pair_kernel", 94.6e6, 16384 * 16, "profiles/attn_fwd_cross_attention_prof_cross.md"),
+    "cross_bf16": ("attn_fwd_pair_kernel (persistent pairs, K/V resident)", 94.6e6, 16384 * 16, "profiles/attn_fwd_cross_attention_prof_cross.md"),
     # block-sparse: only the literal-rule mask at about 7 % density on the single-CTA kernel has a capture; a launch on
     # CTA pairs (denser masks) reports null
     "block_sparse": ("attn_fwd_kernel", 1113.8e6, 96256 * 8, "profiles/attn_fwd_block_sparse_7pct_prof_sparse7.md"),
@@ -306,6 +306,8 @@ def kernel_name(c, online_max, world=1):
     heads = max(1, c.H // world)
     ch = kernel_choice(c.L, c.Lk, heads, c.mode, c.bound, nnz, workspace_bytes=split_workspace_bytes(c.L, c.Lk, heads, c.mode, c.bound))
     if ch["fixed_reference"]:
+        if ch.get("persistent"):
+            return ch["kernel"] + (" (persistent pairs, K/V resident)" if ch["cta_pairs"] else " (persistent, one block per SM)")
         return ch["kernel"]
     return ch["kernel"] + (" (online softmax: per-row reference, then the running maximum where needed)" if ch["online_two_launch"] else " (online softmax)")
 

@@ -169,6 +169,10 @@ int32_t h3a_attn_workspace_bytes(const h3a_attn_params* p, size_t* bytes);
 #define H3A_KERNEL_SPLIT_LAST_WAVE 4  /* the CTA pairs of the last wave split the key range (+ combine_partials_kernel) */
 #define H3A_KERNEL_ONLINE_TWO_LAUNCH 8 /* online softmax as two launches: per-row fixed reference from the first key tile,
                                           then the running-maximum kernel over the few CTA pairs that outgrew it */
+#define H3A_KERNEL_PERSISTENT 16       /* short key ranges with a logit bound: persistent blocks walk the query tiles (with
+                                          CTA_PAIRS: a head's K / V stays in shared memory, up to 4 key tiles; without:
+                                          one single-CTA block per SM).  H3A_RESIDENT=0 / H3A_PERSIST=0 in the environment,
+                                          read once per process, switch these forms off; H3A_PAIR=0 all CTA-pair kernels */
 int32_t h3a_attn_kernel_choice(const h3a_attn_params* p, int32_t* choice);
 
 /* Launch the attention forward on `stream` (a cudaStream_t passed as void*). */

@@ -24,7 +24,7 @@ MODE_DENSE_BF16, MODE_FP8_QK, MODE_BLOCK_SPARSE = 0, 1, 2
 ROPE_INTERLEAVED, ROPE_HALF = 0, 1
 PREP_FP8 = 1
 PREP_NO_NORM = 2
-KERNEL_CTA_PAIRS, KERNEL_FIXED_REFERENCE, KERNEL_SPLIT_LAST_WAVE, KERNEL_ONLINE_TWO_LAUNCH = 1, 2, 4, 8
+KERNEL_CTA_PAIRS, KERNEL_FIXED_REFERENCE, KERNEL_SPLIT_LAST_WAVE, KERNEL_ONLINE_TWO_LAUNCH, KERNEL_PERSISTENT = 1, 2, 4, 8, 16
 MAX_RANKS = 8
 PEER_HANDLE_BYTES = 64
 

@@ -583,6 +583,11 @@ int32_t h3a_attn_kernel_choice(const h3a_attn_params* p, int32_t* choice) {
   if (pairs && !fixed && p->mode != H3A_MODE_BLOCK_SPARSE && two_launch_online_enabled() && p->workspace && aligned16(p->workspace) &&
       p->workspace_bytes >= redo_list_bytes(p->Lq, p->H))
     c |= H3A_KERNEL_ONLINE_TWO_LAUNCH;
+  // persistent blocks: the resident pairs, or one single-CTA block per SM (dense and FP8-QK launches with a bound and
+  // more items than SMs; block-sparse launches only with H3A_PERSIST=1, which is not reported here)
+  if (resident || (!pairs && fixed && p->mode != H3A_MODE_BLOCK_SPARSE && persist_mode() != 0 &&
+                   ((p->Lq + 255) / 256) * p->H > sm_count_of_current_device()))
+    c |= H3A_KERNEL_PERSISTENT;
   *choice = c;
   return H3A_OK;
 }

@@ -348,7 +348,7 @@ def split_workspace_bytes(Lq: int, Lk: int, H: int, mode: int = _lib.MODE_DENSE_
 def kernel_choice(Lq: int, Lk: int, H: int, mode: int = _lib.MODE_DENSE_BF16, logit_bound: float = 0.0, nnz: int = 0,
                   workspace_bytes: int = 0) -> dict:
     """Which attention kernel the library launches for this shape on the current device (``h3a_attn_kernel_choice``):
-    ``{"kernel", "cta_pairs", "fixed_reference", "split_last_wave"}``."""
+    ``{"kernel", "cta_pairs", "fixed_reference", "split_last_wave", "online_two_launch", "persistent"}``."""
     p = AttnParams()
     p.Lq, p.Lk, p.H, p.d, p.B, p.mode, p.logit_bound, p.nnz = int(Lq), int(Lk), int(H), HEAD_DIM, 1, int(mode), float(logit_bound), int(nnz)
     if workspace_bytes:
@@ -358,7 +358,7 @@ def kernel_choice(Lq: int, Lk: int, H: int, mode: int = _lib.MODE_DENSE_BF16, lo
     pairs = bool(c.value & _lib.KERNEL_CTA_PAIRS)
     return {"kernel": "attn_fwd_pair_kernel" if pairs else "attn_fwd_kernel", "cta_pairs": pairs,
             "fixed_reference": bool(c.value & _lib.KERNEL_FIXED_REFERENCE), "split_last_wave": bool(c.value & _lib.KERNEL_SPLIT_LAST_WAVE),
-            "online_two_launch": bool(c.value & _lib.KERNEL_ONLINE_TWO_LAUNCH)}
+            "online_two_launch": bool(c.value & _lib.KERNEL_ONLINE_TWO_LAUNCH), "persistent": bool(c.value & _lib.KERNEL_PERSISTENT)}
 
 
 def proj_fwd(

@@ -679,6 +679,8 @@ def test_persistent_ctas_give_the_same_rows_as_one_cta_per_item(h, tmp_path):
         status = torch.zeros(1, dtype=torch.int32, device="cuda")
         out = h.joint_attention(dev(q), dev(k), dev(v), None, mode=h.MODE_FP8_QK if fp8 else h.MODE_DENSE_BF16, status_word=status)
         assert h.read_status(status) == 0
+        ch = h.ops.kernel_choice(Lq, Lk, H, h.MODE_FP8_QK if fp8 else h.MODE_DENSE_BF16, logit_bound=11.4)
+        assert ch["persistent"] and ch["fixed_reference"] and ch["cta_pairs"] == (Lk <= 512 and not fp8), ch
         if Lk > 512:  # the same kernel, persistent or not: the same arithmetic in the same order
             assert torch.equal(out.cpu(), per_item[i]), (Lq, Lk, H, fp8)
         else:         # CTA pairs with resident K / V against the single-CTA kernel
