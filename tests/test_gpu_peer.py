@@ -61,7 +61,8 @@ def test_prepared_rows_land_at_their_heads_owner(h, P, H, round_robin, half):
                 assert bool((bufs[p][slot] == 9.0).all())
 
 
-@pytest.mark.parametrize("P,H,round_robin", [(2, 4, False), (4, 6, False), (3, 6, True)])
+@pytest.mark.parametrize("P,H,round_robin", [(2, 4, False), (4, 6, False), (3, 6, True), (2, 6, False), (8, 40, False)])  # the last two: an odd
+# number of heads per rank, so a 256-column tile (two heads) belongs to two owners
 def test_projection_epilogue_stores_rows_at_their_heads_owner(h, P, H, round_robin):
     """The fused projection with `out_to`: every emulated rank projects its token shard (LoRA, RMSNorm and rotation in
     the epilogue) and the epilogue stores the rows at the heads' owners; each owner must end up with exactly what the
