@@ -109,7 +109,10 @@ def test_scatter_argument_checks(h):
 
 
 @pytest.mark.parametrize("L,Lk,H,P,bound,sparse", [(600, 600, 3, 3, 0.0, False), (1000, 2200, 3, 4, 12.0, False), (4096, 4096, 4, 8, 12.0, False),
-                                                    (2304, 2304, 2, 2, 12.0, True), (1024, 1024, 2, 4, 0.0, True)])
+                                                    (2304, 2304, 2, 2, 12.0, True), (1024, 1024, 2, 4, 0.0, True),
+                                                    # short key ranges on persistent blocks: CTA pairs with resident K / V (whose
+                                                    # rows otherwise leave as TMA tile stores) and one single-CTA block per SM
+                                                    (9600, 512, 4, 3, 12.0, False), (40000, 640, 2, 2, 12.0, False)])
 def test_output_rows_land_at_their_tokens_owner(h, L, Lk, H, P, bound, sparse):
     """The attention launch stores query row g at the emulated rank g // rows: single-CTA kernels (running maximum and
     fixed reference), CTA pairs with the split last wave (whose combining kernel stores too) and block-sparse.  The rows
