@@ -63,6 +63,9 @@ ALSO = ("cfg2_fp8", "cfg3_sparse", "cfg3_sparse20", "cfg4_cross")  # N = 1: shor
 # captured one; otherwise `traffic` is null.
 NCU_TRAFFIC = {
     "dense_bf16": ("attn_fwd_pair_kernel", 250.9e6, 16384 * 16, "profiles/attn_fwd_dense_bf16_prof_dense.md"),
+    # without a logit bound: both launches of the two-launch online softmax together
+    "dense_bf16_online": ("attn_fwd_pair_kernel (online softmax: per-row reference, then the running maximum where needed)", 250.4e6,
+                          16384 * 16, "profiles/attn_fwd_pair_online_softmax_prof_dense.md"),
     "fp8_qk": ("attn_fwd_pair_kernel", 176.4e6, 16384 * 16, "profiles/attn_fwd_pair_fp8_prof_fp8.md"),
     "cross_bf16": ("attn_fwd_pair_kernel (persistent pairs, K/V resident)", 94.6e6, 16384 * 16, "profiles/attn_fwd_cross_attention_prof_cross.md"),
     # block-sparse: only the literal-rule mask at about 7 % density on the single-CTA kernel has a capture; a launch on
@@ -443,7 +446,7 @@ def roofline_of(c, attn_ms, online_max, world=1):
     achieved = c.flops / world / (attn_ms * 1e-3) / 1e12
     kern = kernel_name(c, online_max, world)
     traffic, traffic_src = None, None
-    cap = NCU_TRAFFIC.get(c.mode_name)
+    cap = NCU_TRAFFIC.get(c.mode_name + ("_online" if online_max else ""))
     if cap is not None and cap[0] == kern:  # only a capture of the kernel variant that ran counts
         traffic = cap[1] * (c.L * c.H / world) / cap[2]
         traffic_src = f"{cap[3]} (captured workload scaled by L*H per launch)"
