@@ -169,12 +169,20 @@ class B200AttnProcessor:
                   (+ e4m3 quantisation in FP8-QK mode) in its epilogue: plain or LoRA-wrapped Linears that
                   ``_linear_parts`` recognises, bf16 weights and activations.  Anything else goes through the module
                   call and the separate preparation kernel.
+    merge_lora    (with ``fused_projection``) fold a LoRA update into a copy of the base weight once per module,
+                  ``W' = bf16(W + (alpha / r) B A)``, so that a projection is ONE launch with no LoRA term left (the
+                  default keeps the update apart, as the reference's un-merged PEFT wrappers do: ``x A^T`` as a thin
+                  matmul in front, 128 more columns of the contraction inside the GEMM).  The merged weight is rounded
+                  to bf16, so results differ from the un-merged form by that rounding; it costs one more copy of each
+                  wrapped weight in device memory.  Weights are taken as static (inference): re-create the processor,
+                  or call :meth:`forget_merged`, after changing them.
     """
 
     def __init__(self, mode: str = "dense_bf16", block_index: Optional[ops.BlockIndex] = None, rope_half: bool = False,
                  rope_split=ops.ROPE_SPLIT, rope_theta: float = 10000.0, qk_norm: Optional[bool] = None, eps: float = 1e-6,
                  group=None, sequence_parallel: bool = False, fused_projection: bool = False,
-                 status: Optional[ops.StatusWord] = None, check_every_call: bool = False, softmax: str = "auto"):
+                 status: Optional[ops.StatusWord] = None, check_every_call: bool = False, softmax: str = "auto",
+                 merge_lora: bool = False):
         if mode not in MODES:
             raise ValueError(f"mode must be one of {sorted(MODES)}")
         if mode == "block_sparse" and block_index is None:
@@ -190,7 +198,9 @@ class B200AttnProcessor:
         self._rope_cache = RopeCache()
         self._bounds = {}
         self.fused_projection = fused_projection
+        self.merge_lora = merge_lora
         self._scaled_b = {}
+        self._merged_w = {}
         if softmax not in ("auto", "online"):
             raise ValueError("softmax must be auto or online")
         self.softmax = softmax
@@ -283,19 +293,36 @@ class B200AttnProcessor:
             return None
         return parts
 
+    def _lora_operands(self, mod, parts, x2d):
+        """``(weight, bias, x A^T or None, scaled B or None)`` for ``ops.proj_fwd``: the LoRA update either merged into
+        a bf16 copy of the weight (``merge_lora``) or kept apart with ``(alpha / rank) B`` scaled once per module."""
+        w, bias, a, b, scale = parts
+        if a is None:
+            return w, bias, None, None
+        if self.merge_lora:
+            key = (id(mod), w.data_ptr(), a.data_ptr(), b.data_ptr(), scale)
+            wm = self._merged_w.get(key)
+            if wm is None:  # W + (alpha / rank) B A in fp32, rounded once
+                wm = self._merged_w[key] = torch.addmm(w.float(), b.float() * scale, a.float()).to(torch.bfloat16).contiguous()
+            return wm, bias, None, None
+        t = torch.nn.functional.linear(x2d, a.to(torch.bfloat16))
+        key = (id(mod), b.data_ptr(), scale)
+        bs = self._scaled_b.get(key)
+        if bs is None:  # static at inference
+            bs = self._scaled_b[key] = (b.float() * scale).to(torch.bfloat16).contiguous()
+        return w, bias, t, bs
+
     def _fused(self, mod, parts, x2d, prep, rope, norm_w, eps, fp8=False, out_to=None):
         """One projection through the library's GEMM; the thin LoRA product ``x A^T`` stays a torch matmul.
         ``fp8``: returns ``(e4m3 bytes, block scales)``.  ``out_to``: the rows go straight to the heads' owning ranks."""
-        w, bias, a, b, scale = parts
-        t = bs = None
-        if a is not None:
-            t = torch.nn.functional.linear(x2d, a.to(torch.bfloat16))
-            key = (id(mod), b.data_ptr(), scale)
-            bs = self._scaled_b.get(key)
-            if bs is None:  # (alpha / rank) * B, static at inference: scaled once per module
-                bs = self._scaled_b[key] = (b.float() * scale).to(torch.bfloat16).contiguous()
+        w, bias, t, bs = self._lora_operands(mod, parts, x2d)
         return ops.proj_fwd(x2d, w, bias, t, bs, prep=prep, rope=rope, norm_weight=norm_w, eps=eps, rope_half=self.rope_half, fp8=fp8,
                             status_word=self.status.tensor(x2d), out_to=out_to)
+
+    def forget_merged(self) -> None:
+        """Drop the merged and scaled LoRA weights this processor keeps (call after the wrapped weights changed)."""
+        self._merged_w.clear()
+        self._scaled_b.clear()
 
     def attention_fused(self, attn, parts, hidden_states, ctx, rope, cross: bool):
         """Projections with the preparation in their epilogue, then attention (one GPU)."""
@@ -373,15 +400,9 @@ class B200AttnProcessor:
         out_parts = _linear_parts(to_out[0]) if (self.fused_projection and o.dtype == torch.bfloat16) else None
         if out_parts is not None and out_parts[0].dtype == torch.bfloat16 and out_parts[0].shape[0] % ops.HEAD_DIM == 0:
             # the output projection through the same GEMM (plain epilogue, token-major rows)
-            w, bias, a, b, scale = out_parts
-            t = bs = None
-            if a is not None:
-                t = torch.nn.functional.linear(o[0], a.to(torch.bfloat16))
-                key = (id(to_out[0]), b.data_ptr(), scale)
-                bs = self._scaled_b.get(key)
-                if bs is None:
-                    bs = self._scaled_b[key] = (b.float() * scale).to(torch.bfloat16).contiguous()
-            o = ops.proj_fwd(o[0].contiguous(), w, bias, t, bs, token_major=True, status_word=self.status.tensor(o))[None]
+            o2d = o[0].contiguous()
+            w, bias, t, bs = self._lora_operands(to_out[0], out_parts, o2d)
+            o = ops.proj_fwd(o2d, w, bias, t, bs, token_major=True, status_word=self.status.tensor(o))[None]
         else:
             o = to_out[0](o)
         if len(to_out) > 1:

@@ -284,6 +284,32 @@ def test_fused_projection_matches_module_calls(setup, wrapper):
 
 
 @torch.no_grad()
+def test_merged_lora_projection_is_one_launch_and_agrees(setup):
+    """merge_lora=True: the LoRA update is folded into a bf16 copy of the base weight once per module; the projection
+    then needs no thin matmul in front.  Results agree with the un-merged form to the rounding of the merged weight."""
+    from pika_h3_flex_b200.processor import B200AttnProcessor
+
+    _, x, pos, _, _ = setup
+    torch.manual_seed(12)
+    attn = StubAttention(256, 2).cuda().bfloat16()
+    attn.to_q, attn.to_k, attn.to_v = (PeftLikeLinear(256, 256).cuda().bfloat16() for _ in range(3))
+    ref = oracle_forward(attn, x, None, pos)
+    apart = B200AttnProcessor(fused_projection=True)
+    merged = B200AttnProcessor(fused_projection=True, merge_lora=True)
+    y_a = apart(attn, x, position_ids=pos.cuda())
+    y_m = merged(attn, x, position_ids=pos.cuda())
+    assert len(merged._merged_w) == 4 and len(merged._scaled_b) == 0 and len(apart._merged_w) == 0  # to_q, to_k, to_v, to_out.0
+    assert float((y_m.float() - ref.float()).abs().max()) < 3e-2
+    assert float((y_m.float() - y_a.float()).abs().max()) < 3e-2
+    w0 = merged._merged_w[next(iter(merged._merged_w))]
+    y_m2 = merged(attn, x, position_ids=pos.cuda())  # the merged weights are reused
+    assert len(merged._merged_w) == 4 and merged._merged_w[next(iter(merged._merged_w))] is w0 and torch.equal(y_m, y_m2)
+    merged.forget_merged()
+    assert len(merged._merged_w) == 0
+    merged.check_status()
+
+
+@torch.no_grad()
 def test_fused_projection_cross_attention(setup):
     from pika_h3_flex_b200.processor import B200AttnProcessor
 
