@@ -545,6 +545,33 @@ def ulysses_with_projections(c, ua, dev, world, rank, barrier, rank_max, steps=5
                        "against": "fp64 oracle attention on operands projected in fp32 (torch, TF32 off) for two heads; worst rank"}}
 
 
+def torch_sdpa_comparison(c):
+    """What a stock PyTorch build gives for the same attention on this GPU: ``scaled_dot_product_attention`` in bf16 on
+    the already prepared operands of the headline workload (torch picks its own library kernel).  A comparison figure
+    only: nothing of this library is involved and nothing of it is timed here."""
+    import pika_h3_flex_b200 as h3
+
+    qh, kh, _, _ = h3.qk_prep(c.q, c.k, c.rope, c.rope)  # prepared as the attention kernels take them: [L, H, 128] views of head-major memory
+    q4, k4 = qh.permute(1, 0, 2)[None], kh.permute(1, 0, 2)[None]  # [1, H, L, 128], contiguous
+    v4 = c.v.permute(1, 0, 2).contiguous()[None]
+    f = torch.nn.functional.scaled_dot_product_attention
+    n = 20  # as many launches as the headline's timed steps, so that the 1 kW power cap weighs on both alike
+    for _ in range(3):
+        f(q4, k4, v4)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(n):
+        o = f(q4, k4, v4)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / n
+    del o, q4, k4, v4, qh, kh
+    return {"workload": "cfg1_dense_torch_sdpa", "kernel": "torch.nn.functional.scaled_dot_product_attention (bf16, torch's choice of backend)",
+            "kernel_ms": ms, "kernel_tflops": c.flops / (ms * 1e-3) / 1e12, "steps": n,
+            "note": "stock PyTorch on the same prepared operands, attention only: a comparison figure, not this library"}
+
+
 def run_also(name, dev, online_max=False):
     """A short run (3 warm-up + 5 timed steps) of another configuration on this GPU, with its parity verdict."""
     import pika_h3_flex_b200 as h3
@@ -757,6 +784,11 @@ def run_ours(args):
             also.append(run_also("cfg1_dense", dev, online_max=True))
         except (RuntimeError, ValueError) as exc:
             also.append({"workload": "cfg1_dense_online_max", "error": repr(exc)})
+        try:
+            also.append(torch_sdpa_comparison(c))
+        except (RuntimeError, ValueError, TypeError) as exc:
+            also.append({"workload": "cfg1_dense_torch_sdpa", "error": repr(exc)})
+        torch.cuda.empty_cache()
 
     if world > 1 and not args.no_also and name == "cfg1_dense" and ua.transport == "peer":
         try:

@@ -57,10 +57,15 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 #define H3A_FULL_S 0
 #endif
 constexpr bool kFullS = H3A_FULL_S != 0;
+// Of every 4 element pairs, how many take the polynomial exp2 on the FMA pipe instead of the MUFU (0..4).  One in four
+// is the fastest in CLOCK CYCLES (the MUFU is the busier pipe), but the polynomial's five FMAs cost more energy than one
+// MUFU operation, and the long launches run under the board's power cap: with none the clock settles 4-5 % higher and
+// the launch is shorter (dense config 1: 37.3 against 38.0 ms, block-sparse 20.2 against 20.8 ms, same box, alternating
+// runs).  So the default is 0; kernels that are not power-limited ask for 1 (exp_half_tile's second argument).
 #ifndef H3A_POLY_PAIRS
-#define H3A_POLY_PAIRS 1
+#define H3A_POLY_PAIRS 0
 #endif
-constexpr int kPolyPairsBf16 = H3A_POLY_PAIRS;  // of every 4 element pairs, how many use the polynomial exp2 (0..4)
+constexpr int kPolyPairsBf16 = H3A_POLY_PAIRS;
 #ifndef H3A_POLY_FP8
 #define H3A_POLY_FP8 0
 #endif
@@ -80,10 +85,10 @@ constexpr int kPackedExpFp8 = H3A_BF16X2_FP8, kPackedExpBf16 = H3A_BF16X2_BF16;
 // P = 2^(s c - m) for the 64 logits in s[] (one half tile, one row per thread): the packed bf16 results replace
 // s[0..31]; returns the row-sum share.  Pair i uses, by (i & 3): the packed-bf16 MUFU path, the FMA-pipe polynomial,
 // or two fp32 MUFU operations.
-template <bool kFp8>
+template <bool kFp8, int kPolyShare = -1>
 __device__ __forceinline__ float exp_half_tile(uint32_t (&s)[64], float c, float m_ref) {
   constexpr int kPacked = kFp8 ? kPackedExpFp8 : kPackedExpBf16;
-  constexpr int kPoly = kFp8 ? kPolyPairsFp8 : kPolyPairsBf16;
+  constexpr int kPoly = kPolyShare >= 0 ? kPolyShare : (kFp8 ? kPolyPairsFp8 : kPolyPairsBf16);
   uint64_t acc0 = 0, acc1 = 0;  // two packed accumulators = four partial row sums (bit pattern 0 == 0.0f)
   uint32_t accb[4] = {0u, 0u, 0u, 0u};
   const uint64_t c2 = pack2(c, c), nm2 = pack2(-m_ref, -m_ref);

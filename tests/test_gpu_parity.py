@@ -683,8 +683,11 @@ def test_persistent_ctas_give_the_same_rows_as_one_cta_per_item(h, tmp_path):
         assert ch["persistent"] and ch["fixed_reference"] and ch["cta_pairs"] == (Lk <= 512 and not fp8), ch
         if Lk > 512:  # the same kernel, persistent or not: the same arithmetic in the same order
             assert torch.equal(out.cpu(), per_item[i]), (Lq, Lk, H, fp8)
-        else:         # CTA pairs with resident K / V against the single-CTA kernel
-            assert float((out.cpu().float() - per_item[i].float()).abs().max()) <= 1e-3, (Lq, Lk, H)
+        else:         # CTA pairs with resident K / V against the single-CTA kernel: another MMA shape, and a quarter of the
+            # exponentials on the polynomial there against none here: an output may differ by one bf16 step (2^-8 of its size)
+            want = per_item[i].float()
+            d = (out.cpu().float() - want).abs()
+            assert bool((d <= 2.0 ** -6 * want.abs().clamp_min(0.25)).all()) and float(d.mean()) <= 1e-4, (Lq, Lk, H, float(d.max()), float(d.mean()))  # a step either side of a power of two
         rows = torch.cat([torch.arange(0, Lq, 397), torch.tensor([Lq - 1, Lq - 129, 255, 256, 511, 512])])
         ref = O.attention(O.rms_norm(q[rows].float()), O.rms_norm(k.float()), v.float())
         if fp8:
