@@ -53,6 +53,8 @@ WORKLOADS = {
     "prof_sparse": ((31, 32, 32), 1024, 16, "block_sparse", (3, 32, 32), 2003),
     "prof_sparse7": ((31, 48, 64), 1024, 8, "block_sparse", (2, 8, 8), 2003),  # 7.3 % of tiles: the single-CTA kernel
     "prof_cross": ((15, 32, 32), 1024, 16, "cross_bf16", None, 2004),
+    # one rank's share of config 1 under 8-way sequence parallelism (5 of the 40 heads, all tokens): launches of 4.5 ms
+    "prof_rank8": ((31, 30, 52), 1024, 5, "dense_bf16", None, 1001),
 }
 ALSO = ("cfg2_fp8", "cfg3_sparse", "cfg3_sparse20", "cfg4_cross")  # N = 1: short runs next to the headline workload
 
